@@ -12,6 +12,28 @@ int aeris_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
                     int rows_per_gate, void* aux, int ld_aux, int swiglu_f, int k_splits, int bn, int* status,
                     void* stream);
 
+int aeris_attn_fwd(const void* q, int ldq, int q_col0, const void* k, int ldk, int k_col0, const void* v, int ldv,
+                   int v_col0, void* o, int ldo, float* lse, int n_win, int N, int H, int head_dim, float scale,
+                   int* status, void* stream);
+
+int aeris_modnorm_fwd(const void* x, const void* gidx, const void* const* peer_ptrs, int n_peers, void* x_out,
+                      const float* scale, const float* shift, const void* w, void* h, int rows, int D, int mode,
+                      float eps, void* stream);
+int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres, const float* scale, const float* shift,
+                      const void* w, void* dx, float* dscale, float* dshift, float* dw, int rows, int D, int mode,
+                      float eps, void* stream);
+int aeris_gather_rows(const void* gidx, const void* const* peer_ptrs, int n_peers, void* out, long long rows, int D,
+                      void* stream);
+int aeris_swiglu_fwd(const void* u, void* act, long long rows, int F, void* stream);
+int aeris_swiglu_bwd(const void* u, const void* dact, void* du, long long rows, int F, void* stream);
+int aeris_scale_rows(const void* W, const float* g, void* Wg, int R, int C, void* stream);
+int aeris_gate_grad_finalize(float* G, const void* W, const float* g, float* dW, float* dg, int R, int C,
+                             void* stream);
+int aeris_sumsq(const float* x, long long n, double* out, void* stream);
+int aeris_adamw(float* master, float* grad, float* m, float* v, void* wbf16, float* ema, const double* norm_sq,
+                long long n, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+                float grad_scale, float max_norm, float ema_beta, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

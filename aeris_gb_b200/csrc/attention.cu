@@ -1,0 +1,343 @@
+// Windowed multi-head attention for sm_100a: softmax(Q K^T * scale) V per (window, head), non-causal and unmasked,
+// forward and backward, flash-style (no N x N matrix in memory), on tcgen05 tensor cores with TMEM accumulators.
+//
+// Reference semantics: src/aeris/models/parallel_swin.py:257-258 (F.scaled_dot_product_attention, is_causal=False)
+// and src/aeris_wp_inference/model.py:289-309 (naive softmax(QK^T)V over each window's tokens).
+//
+// Data layout: tokens are window-major, rows [w*N, (w+1)*N) belong to window w; Q, K, V are column slices of a
+// row-major [T, ld] bf16 tensor (the fused qkv projection output, columns ordered (q|k|v, head, d)).
+//
+// Every kernel has the same skeleton (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2..5 = one thread per tile row doing the softmax-side math straight out of TMEM.
+#include "common.cuh"
+#include "api.h"
+#include "host.h"
+
+namespace aeris {
+
+constexpr int ATT_THREADS = 192;
+constexpr int TILE = 128;
+
+struct AttnFwdParams {
+  __nv_bfloat16* O;
+  int ldo;
+  float* lse;  // [n_win * H * N], log2 domain: m + log2(l)
+  int N, H, n_win;
+  int q_col0, k_col0, v_col0;
+  float scale_log2;
+  int* status;
+};
+
+// Byte offset of 16-byte vector `v` (0..7) of row `r` inside a [rows x 64] bf16 tile stored with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz128(int r, int v) { return r * 128 + (((v ^ (r & 7)) & 7) << 4); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// -------------------------------------------------------------------------------------------------------- forward
+// grid = (q_tiles, H, n_win). One CTA owns a 128-row Q tile and streams the window's K/V in 128-row tiles.
+// TMEM: S [128 x 128] fp32, O_part[2] [128 x d] fp32 (fresh P V product per tile; the running output lives in
+// registers so that no TMEM read-modify-write is needed for the online-softmax rescale).
+template <int DCH>
+__global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 2 : 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
+  constexpr int HD = 64 * DCH;
+  constexpr int Q_BYTES = DCH * 16384;
+  constexpr int KV_BYTES = 2 * DCH * 16384;  // K tile + V tile
+  constexpr int P_BYTES = 32768;
+  constexpr int TMEM_COLS = (DCH == 1) ? 256 : 512;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + Q_BYTES;
+  uint8_t* sP = sKV + 2 * KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* o_full = bars + 7;    // [2]
+  uint64_t* o_free = bars + 9;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = blockIdx.x, head = blockIdx.y, win = blockIdx.z;
+  const int N = p.N;
+  const int nfull = N / TILE, rem = N - nfull * TILE;
+  const int nkv = nfull + (rem ? 1 : 0);
+  const int n_last = rem ? ((rem + 15) & ~15) : TILE;  // MMA N of the last K/V tile
+
+  if (threadIdx.x == 0) {
+    int ab = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    if ((smem_u32(smem) & 1023u) != 0) {
+      ab = 1;
+      if (p.status) atomicCAS(p.status, 0, ERR_BOUNDS);
+    }
+    *s_abort = ab;
+  }
+  __syncthreads();
+  if (*s_abort) return;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
+      mbar_init(&o_full[i], 1);  mbar_init(&o_free[i], 4);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;
+  const uint32_t tO0 = tmem_base + 128;
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c)
+        tma_load_3d(sQ + c * 16384, &tm_q, q_full, p.q_col0 + head * HD + c * 64, qt * TILE, win);
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
+        uint8_t* sK = sKV + s * KV_BYTES;
+        uint8_t* sV = sK + DCH * 16384;
+        mbar_expect_tx(&kv_full[s], KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) {
+          tma_load_3d(sK + c * 16384, &tm_k, &kv_full[s], p.k_col0 + head * HD + c * 64, j * TILE, win);
+          tma_load_3d(sV + c * 16384, &tm_v, &kv_full[s], p.v_col0 + head * HD + c * 64, j * TILE, win);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one_sync()) {
+      bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_ATTN);
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int s = j & 1;
+        const int ncur = (j == nkv - 1) ? n_last : TILE;
+        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sKV + s * KV_BYTES), aV = aK + DCH * 16384;
+        // S = Q K^T  (A = Q K-major, B = K K-major, reduction over d)
+        const uint32_t idesc_qk = make_idesc_bf16(TILE, ncur, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < 4 * DCH; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(tS, make_smem_desc(aQ + off, 0, 1024), make_smem_desc(aK + off, 0, 1024), idesc_qk, kk > 0);
+        }
+        tc_commit(s_full);
+        // O_part = P V  (A = P K-major over kv, B = V MN-major: d contiguous, kv rows strided)
+        if (!mbar_wait(p_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        if (!mbar_wait(&o_free[j & 1], ((j >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t idesc_pv = make_idesc_bf16(TILE, HD, 0, 1);
+        const uint32_t tO = tO0 + (j & 1) * HD;
+        for (int kk = 0; kk < ncur / 16; ++kk) {
+          const uint32_t poff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(tO, make_smem_desc(aP + poff, 0, 1024), make_smem_desc(aV + kk * 2048, 16384, 1024), idesc_pv,
+                  kk > 0);
+        }
+        tc_commit(&o_full[j & 1]);
+        tc_commit(&kv_empty[s]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;            // row inside the Q tile == TMEM lane
+    const int grow = qt * TILE + row;         // row inside the window
+    const bool warp_valid = (qt * TILE + q * 32) < N;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    float acc[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv && ok; ++j) {
+      const bool last = (j == nkv - 1);
+      const int ncur = last ? n_last : TILE;
+      const int valid = (last && rem) ? rem : TILE;
+      if (!mbar_wait(s_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      tc_fence_after();
+      float alpha = 1.f;
+      if (warp_valid) {
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < ncur; c += 32) {
+          if (ncur - c >= 32) {
+            uint32_t v[32];
+            tmem_ld32(tS + lane_addr + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+          } else {
+            uint32_t v[16];
+            tmem_ld16(tS + lane_addr + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (c + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+          }
+        }
+        const float m_new = fmaxf(m, mx * p.scale_log2);
+        alpha = fast_exp2(m - m_new);  // first tile: exp2(-inf) = 0
+        float rs = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < ncur; c += 32) {
+          uint32_t pk[16];
+          if (ncur - c >= 32) {
+            uint32_t v[32];
+            tmem_ld32(tS + lane_addr + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -m_new));
+              float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_new));
+              if (c + 2 * i >= valid) p0 = 0.f;
+              if (c + 2 * i + 1 >= valid) p1 = 0.f;
+              rs += p0 + p1;
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = c + g * 8;
+              uint8_t* dst = sP + (col >> 6) * 16384 + swz128(row, (col & 63) >> 3);
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+            }
+          } else {
+            uint32_t v[16];
+            tmem_ld16(tS + lane_addr + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -m_new));
+              float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_new));
+              if (c + 2 * i >= valid) p0 = 0.f;
+              if (c + 2 * i + 1 >= valid) p1 = 0.f;
+              rs += p0 + p1;
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+              const int col = c + g * 8;
+              uint8_t* dst = sP + (col >> 6) * 16384 + swz128(row, (col & 63) >> 3);
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+            }
+          }
+        }
+        l = l * alpha + rs;
+        m = m_new;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      // fold in the previous tile's P V product
+      if (j > 0) {
+        const int b = (j - 1) & 1;
+        if (!mbar_wait(&o_full[b], ((j - 1) >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after();
+        if (warp_valid) {
+#pragma unroll
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(tO0 + b * HD + lane_addr + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(acc[c + i], alpha_prev, __uint_as_float(v[i]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_free[b]);
+      }
+      alpha_prev = alpha;
+    }
+    if (ok) {
+      const int b = (nkv - 1) & 1;
+      if (mbar_wait(&o_full[b], ((nkv - 1) >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) {
+        tc_fence_after();
+        if (warp_valid) {
+#pragma unroll
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(tO0 + b * HD + lane_addr + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(acc[c + i], alpha_prev, __uint_as_float(v[i]));
+          }
+          if (grow < N) {
+            const float inv = 1.f / l;
+            const size_t trow = static_cast<size_t>(win) * N + grow;
+            __nv_bfloat16* dst = p.O + trow * p.ldo + head * HD;
+#pragma unroll
+            for (int c = 0; c < HD; c += 8) {
+              uint4 u;
+              u.x = pack_bf16x2(acc[c] * inv, acc[c + 1] * inv);
+              u.y = pack_bf16x2(acc[c + 2] * inv, acc[c + 3] * inv);
+              u.z = pack_bf16x2(acc[c + 4] * inv, acc[c + 5] * inv);
+              u.w = pack_bf16x2(acc[c + 6] * inv, acc[c + 7] * inv);
+              *reinterpret_cast<uint4*>(dst + c) = u;
+            }
+            if (p.lse) p.lse[(static_cast<size_t>(win) * p.H + head) * N + grow] = m + log2f(l);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+template <int DCH>
+static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const AttnFwdParams& p, cudaStream_t stream) {
+  constexpr int SMEM = DCH * 16384 + 2 * 2 * DCH * 16384 + 32768 + 128;
+  static bool configured = false;
+  auto kern = attn_fwd_kernel<DCH>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -20;
+    configured = true;
+  }
+  dim3 grid((p.N + TILE - 1) / TILE, p.H, p.n_win);
+  kern<<<grid, ATT_THREADS, SMEM, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace aeris
+
+using namespace aeris;
+
+// q, k, v: base pointers of row-major [n_win * N, ld*] bf16 tensors; *_col0 = column of head 0.
+extern "C" int aeris_attn_fwd(const void* q, int ldq, int q_col0, const void* k, int ldk, int k_col0, const void* v,
+                              int ldv, int v_col0, void* o, int ldo, float* lse, int n_win, int N, int H,
+                              int head_dim, float scale, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (head_dim != 64 && head_dim != 128) return -1;
+  if (n_win <= 0 || N <= 0 || H <= 0 || n_win > 65535 || H > 65535) return -2;
+  AttnFwdParams p{};
+  p.O = reinterpret_cast<__nv_bfloat16*>(o); p.ldo = ldo; p.lse = lse; p.N = N; p.H = H; p.n_win = n_win;
+  p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_tmap_3d_bf16(&tq, q, ldq, N, n_win, ldq, static_cast<uint64_t>(N) * ldq, 64, TILE))) return r;
+  if ((r = make_tmap_3d_bf16(&tk, k, ldk, N, n_win, ldk, static_cast<uint64_t>(N) * ldk, 64, TILE))) return r;
+  if ((r = make_tmap_3d_bf16(&tv, v, ldv, N, n_win, ldv, static_cast<uint64_t>(N) * ldv, 64, TILE))) return r;
+  return head_dim == 64 ? launch_attn_fwd<1>(tq, tk, tv, p, stream) : launch_attn_fwd<2>(tq, tk, tv, p, stream);
+}

@@ -1,0 +1,498 @@
+// Memory-bound kernels of the Swin block and the optimizer:
+//   * AdaLN modulate + RMSNorm, both orderings, forward and backward, with an optional row gather that pulls
+//     rows from this GPU or from a peer GPU's buffer (window re-partition / halo exchange for the shifted
+//     layers: reference src/aeris_wp_inference/model.py:18-119 does this with blocking send/recv + roll)
+//   * SwiGLU forward / backward, gate-weight scaling and gate-gradient finalisation
+//   * row gather (re-partition of gradients), sum of squares, fused AdamW (+clip, NaN guard, bf16 cast, EMA)
+// Reference math: src/aeris/models/parallel_swin.py:55-59 (modulate), :454-472 (block orderings), :99-100 (SwiGLU);
+// optimizer semantics: src/aeris/parallelism/parallel_engine.py:709-738, 832, 862-884.
+#include "common.cuh"
+#include "api.h"
+
+namespace aeris {
+
+struct PeerPtrs {
+  const __nv_bfloat16* p[16];
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack_bf16x2(w[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void loadf8(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// Block-wide sum of NRED values per thread. `red` holds 2 * NRED * 32 floats (double buffered by `parity`, so one
+// __syncthreads per call is enough when calls alternate parity).
+template <int NRED>
+__device__ __forceinline__ void block_sum(float (&v)[NRED], float* red, int parity) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int k = 0; k < NRED; ++k) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v[k] += __shfl_xor_sync(0xffffffffu, v[k], o);
+  }
+  float* slot = red + parity * NRED * 32;
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < NRED; ++k) slot[k * 32 + warp] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < NRED; ++k) {
+    float s = 0.f;
+    for (int w = 0; w < nwarps; ++w) s += slot[k * 32 + w];
+    v[k] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ modulate + RMSNorm
+// One CTA streams over rows; thread t owns columns [8t, 8t+8). mode 0: h = RMSNorm(x*(1+scale)+shift)*w
+// (modulate -> norm); mode 1: h = (RMSNorm(x)*w)*(1+scale)+shift (norm -> modulate). scale/shift may be null
+// (plain RMSNorm). With `gidx`, source row r comes from peers.p[gidx[r] >> 28] at row (gidx[r] & 0x0fffffff), and
+// the gathered row is also written to x_out.
+__global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ gidx,
+                                   PeerPtrs peers, __nv_bfloat16* __restrict__ x_out,
+                                   const float* __restrict__ scale, const float* __restrict__ shift,
+                                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h, int rows,
+                                   int D, int mode, float eps, int rows_per_cta) {
+  __shared__ float red[2 * 1 * 32];
+  const int c0 = threadIdx.x * 8;
+  const bool active = c0 < D;
+  float sc[8], sh[8], wv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { sc[i] = 0.f; sh[i] = 0.f; wv[i] = 0.f; }
+  if (active) {
+    if (scale) loadf8(scale + c0, sc);
+    if (shift) loadf8(shift + c0, sh);
+    load8(w + c0, wv);
+  }
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int r1 = min(rows, r0 + rows_per_cta);
+  int parity = 0;
+  for (int r = r0; r < r1; ++r, parity ^= 1) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (active) {
+      const __nv_bfloat16* src;
+      if (gidx) {
+        const uint32_t code = gidx[r];
+        src = peers.p[code >> 28] + static_cast<size_t>(code & 0x0fffffffu) * D + c0;
+      } else {
+        src = x + static_cast<size_t>(r) * D + c0;
+      }
+      load8(src, v);
+      if (x_out) store8(x_out + static_cast<size_t>(r) * D + c0, v);
+    }
+    float y[8];
+    float ss[1] = {0.f};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      y[i] = (mode == 0) ? fmaf(v[i], sc[i], v[i]) + sh[i] : v[i];
+      ss[0] += y[i] * y[i];
+    }
+    if (!active) ss[0] = 0.f;
+    block_sum<1>(ss, red, parity);
+    const float rinv = rsqrtf(ss[0] / D + eps);
+    if (active) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float n = y[i] * rinv * wv[i];
+        o[i] = (mode == 0) ? n : fmaf(n, sc[i], n) + sh[i];
+      }
+      store8(h + static_cast<size_t>(r) * D + c0, o);
+    }
+  }
+}
+
+// Backward of the above. dx = dres + d(norm path). Column sums are kept in registers over the CTA's rows and
+// flushed with atomics at the end: dscale, dshift (fp32 [D], one modulation vector per launch) and dw (fp32 [D]).
+__global__ void modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dh,
+                                   const __nv_bfloat16* __restrict__ dres, const float* __restrict__ scale,
+                                   const float* __restrict__ shift, const __nv_bfloat16* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dscale,
+                                   float* __restrict__ dshift, float* __restrict__ dw, int rows, int D, int mode,
+                                   float eps, int rows_per_cta) {
+  __shared__ float red[2 * 2 * 32];
+  const int c0 = threadIdx.x * 8;
+  const bool active = c0 < D;
+  float sc[8], sh[8], wv[8], a_sc[8], a_sh[8], a_w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { sc[i] = 0.f; sh[i] = 0.f; wv[i] = 0.f; a_sc[i] = 0.f; a_sh[i] = 0.f; a_w[i] = 0.f; }
+  if (active) {
+    if (scale) loadf8(scale + c0, sc);
+    if (shift) loadf8(shift + c0, sh);
+    load8(w + c0, wv);
+  }
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int r1 = min(rows, r0 + rows_per_cta);
+  int parity = 0;
+  for (int r = r0; r < r1; ++r, parity ^= 1) {
+    float v[8], g[8], dr[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[i] = 0.f; g[i] = 0.f; dr[i] = 0.f; }
+    if (active) {
+      const size_t off = static_cast<size_t>(r) * D + c0;
+      load8(x + off, v);
+      load8(dh + off, g);
+      if (dres) load8(dres + off, dr);
+    }
+    float o[8];
+    if (mode == 0) {
+      // y = x(1+sc)+sh ; h = y * rinv * w
+      float y[8], gy[8];
+      float s[2] = {0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        y[i] = fmaf(v[i], sc[i], v[i]) + sh[i];
+        gy[i] = g[i] * wv[i];
+        s[0] += y[i] * y[i];
+        s[1] += y[i] * gy[i];
+      }
+      if (!active) { s[0] = 0.f; s[1] = 0.f; }
+      block_sum<2>(s, red, parity);
+      const float rinv = rsqrtf(s[0] / D + eps);
+      const float coef = rinv * rinv * rinv * (s[1] / D);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float dy = rinv * gy[i] - y[i] * coef;
+        a_w[i] += g[i] * y[i] * rinv;
+        a_sc[i] += dy * v[i];
+        a_sh[i] += dy;
+        o[i] = dr[i] + fmaf(dy, sc[i], dy);
+      }
+    } else {
+      // n = x * rinv ; hn = n * w ; h = hn(1+sc)+sh
+      float gn[8];
+      float s[2] = {0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float dhn = fmaf(g[i], sc[i], g[i]);
+        gn[i] = dhn * wv[i];
+        s[0] += v[i] * v[i];
+        s[1] += v[i] * gn[i];
+      }
+      if (!active) { s[0] = 0.f; s[1] = 0.f; }
+      block_sum<2>(s, red, parity);
+      const float rinv = rsqrtf(s[0] / D + eps);
+      const float coef = rinv * rinv * rinv * (s[1] / D);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float n = v[i] * rinv;
+        const float dhn = fmaf(g[i], sc[i], g[i]);
+        a_sc[i] += g[i] * n * wv[i];
+        a_sh[i] += g[i];
+        a_w[i] += dhn * n;
+        o[i] = dr[i] + rinv * gn[i] - v[i] * coef;
+      }
+    }
+    if (active) store8(dx + static_cast<size_t>(r) * D + c0, o);
+  }
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (dscale) atomicAdd(dscale + c0 + i, a_sc[i]);
+      if (dshift) atomicAdd(dshift + c0 + i, a_sh[i]);
+      if (dw) atomicAdd(dw + c0 + i, a_w[i]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ row gather
+__global__ void gather_rows_kernel(const uint32_t* __restrict__ gidx, PeerPtrs peers,
+                                   __nv_bfloat16* __restrict__ out, long long rows, int D) {
+  const int vec_per_row = D / 8;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int v = static_cast<int>(i - r * vec_per_row);
+    const uint32_t code = gidx[r];
+    const uint4* src = reinterpret_cast<const uint4*>(peers.p[code >> 28] +
+                                                      static_cast<size_t>(code & 0x0fffffffu) * D) + v;
+    reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * D)[v] = *src;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ SwiGLU
+// u = [gate | up] of width 2F per row. act = silu(gate) * up.
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ act,
+                                  long long rows, int F) {
+  const int vec = F / 8;
+  const long long total = rows * vec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec;
+    const int c = static_cast<int>(i - r * vec) * 8;
+    float g[8], up[8], o[8];
+    load8(u + r * 2 * F + c, g);
+    load8(u + r * 2 * F + F + c, up);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * up[k];
+    store8(act + r * F + c, o);
+  }
+}
+// du = [dact * up * dsilu(gate) | dact * silu(gate)]
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ u, const __nv_bfloat16* __restrict__ dact,
+                                  __nv_bfloat16* __restrict__ du, long long rows, int F) {
+  const int vec = F / 8;
+  const long long total = rows * vec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec;
+    const int c = static_cast<int>(i - r * vec) * 8;
+    float g[8], up[8], d[8], dg[8], dup[8];
+    load8(u + r * 2 * F + c, g);
+    load8(u + r * 2 * F + F + c, up);
+    load8(dact + r * F + c, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float s = 1.f / (1.f + __expf(-g[k]));
+      const float silu = g[k] * s;
+      dup[k] = d[k] * silu;
+      dg[k] = d[k] * up[k] * (s + silu * (1.f - s));
+    }
+    store8(du + r * 2 * F + c, dg);
+    store8(du + r * 2 * F + F + c, dup);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ gate helpers
+// Wg[r, :] = g[r] * W[r, :]  (bf16), used as the B operand of the gated data-gradient GEMMs.
+__global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ W, const float* __restrict__ g,
+                                  __nv_bfloat16* __restrict__ Wg, int R, int C) {
+  const int vec = C / 8;
+  const long long total = static_cast<long long>(R) * vec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / vec);
+    const int c = static_cast<int>(i - static_cast<long long>(r) * vec) * 8;
+    float v[8];
+    load8(W + static_cast<size_t>(r) * C + c, v);
+    const float s = g[r];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] *= s;
+    store8(Wg + static_cast<size_t>(r) * C + c, v);
+  }
+}
+// G = dY^T A (ungated weight gradient of out = resid + g * (A W^T)). Then
+//   dW[r, :] += g[r] * G[r, :]   and   dg[r] += sum_c W[r, c] * G[r, c];   G is zeroed for the next sample.
+__global__ void gate_grad_finalize_kernel(float* __restrict__ G, const __nv_bfloat16* __restrict__ W,
+                                          const float* __restrict__ g, float* __restrict__ dW,
+                                          float* __restrict__ dg, int R, int C) {
+  __shared__ float red[2 * 1 * 32];
+  const int r = blockIdx.x;
+  const float s = g[r];
+  float acc[1] = {0.f};
+  for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+    const size_t off = static_cast<size_t>(r) * C + c;
+    const float4 gv = *reinterpret_cast<const float4*>(G + off);
+    const uint2 wu = *reinterpret_cast<const uint2*>(W + off);
+    const float2 w01 = unpack_bf16x2(wu.x), w23 = unpack_bf16x2(wu.y);
+    acc[0] += gv.x * w01.x + gv.y * w01.y + gv.z * w23.x + gv.w * w23.y;
+    float4 d = *reinterpret_cast<float4*>(dW + off);
+    d.x = fmaf(s, gv.x, d.x); d.y = fmaf(s, gv.y, d.y); d.z = fmaf(s, gv.z, d.z); d.w = fmaf(s, gv.w, d.w);
+    *reinterpret_cast<float4*>(dW + off) = d;
+    *reinterpret_cast<float4*>(G + off) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  block_sum<1>(acc, red, 0);
+  if (threadIdx.x == 0) dg[r] += acc[0];
+}
+
+// ------------------------------------------------------------------------------------------------ optimizer
+// Sum of squares of a flat fp32 buffer into out[0] (double), |x| finite check folded in by the caller.
+__global__ void sumsq_kernel(const float* __restrict__ x, long long n, double* __restrict__ out) {
+  __shared__ float red[2 * 1 * 32];
+  float acc[1] = {0.f};
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    acc[0] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long i = n4 * 4; i < n; ++i) acc[0] += x[i] * x[i];
+  block_sum<1>(acc, red, 0);
+  if (threadIdx.x == 0) atomicAdd(out, static_cast<double>(acc[0]));
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias1, bias2;       // 1 - beta^t
+  float grad_scale;         // multiplies the raw accumulated gradient (1 / (DP * GAS))
+  float max_norm;           // <= 0: no clipping
+  float ema_beta;           // < 0: no EMA
+  float nan_clamp;          // +-inf replacement magnitude, NaN -> 0
+};
+// One fused pass over a flat shard: g = nan_to_num(grad * grad_scale * clip); AdamW on the fp32 master; bf16 copy of
+// the new weight; EMA lerp; gradient buffer zeroed. `norm_sq` is the global sum of squares of (grad * grad_scale).
+__global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ grad, float* __restrict__ m,
+                             float* __restrict__ v, __nv_bfloat16* __restrict__ wbf16, float* __restrict__ ema,
+                             const double* __restrict__ norm_sq, long long n, AdamArgs a) {
+  float clip = 1.f;
+  if (a.max_norm > 0.f && norm_sq) {
+    const float total = static_cast<float>(sqrt(*norm_sq));
+    const float c = a.max_norm / (total + 1.0e-6f);
+    if (c < 1.f) clip = c;
+  }
+  const float gs = a.grad_scale * clip;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float g = grad[i] * gs;
+    if (g != g) g = 0.f;
+    else if (g > 3.0e38f) g = a.nan_clamp;
+    else if (g < -3.0e38f) g = -a.nan_clamp;
+    float p = master[i];
+    const float mi = a.beta1 * m[i] + (1.f - a.beta1) * g;
+    const float vi = a.beta2 * v[i] + (1.f - a.beta2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    p *= (1.f - a.lr * a.weight_decay);
+    const float denom = sqrtf(vi / a.bias2) + a.eps;
+    p -= a.lr * (mi / a.bias1) / denom;
+    master[i] = p;
+    if (wbf16) wbf16[i] = __float2bfloat16_rn(p);
+    if (ema && a.ema_beta >= 0.f) ema[i] = p + a.ema_beta * (ema[i] - p);  // lerp(p, ema, beta)
+    grad[i] = 0.f;
+  }
+}
+
+static inline int grid_for(long long work, int threads, int max_blocks) {
+  long long b = (work + threads - 1) / threads;
+  if (b > max_blocks) b = max_blocks;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+static inline int row_threads(int D) {
+  int t = (D / 8 + 31) / 32 * 32;
+  return t < 32 ? 32 : t;
+}
+
+}  // namespace aeris
+
+using namespace aeris;
+extern int aeris_num_sms();
+
+static int pick_rows_per_cta(int rows) {
+  const int target_ctas = aeris_num_sms() * 8;
+  int rpc = (rows + target_ctas - 1) / target_ctas;
+  if (rpc < 1) rpc = 1;
+  return rpc;
+}
+
+extern "C" int aeris_modnorm_fwd(const void* x, const void* gidx, const void* const* peer_ptrs, int n_peers,
+                                 void* x_out, const float* scale, const float* shift, const void* w, void* h,
+                                 int rows, int D, int mode, float eps, void* stream) {
+  if (D % 8 || D > 8192 || rows <= 0) return -1;
+  PeerPtrs pp{};
+  for (int i = 0; i < n_peers && i < 16; ++i) pp.p[i] = reinterpret_cast<const __nv_bfloat16*>(peer_ptrs[i]);
+  if (gidx && n_peers <= 0) return -2;
+  const int rpc = pick_rows_per_cta(rows);
+  const int grid = (rows + rpc - 1) / rpc;
+  modnorm_fwd_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const uint32_t*>(gidx), pp,
+      reinterpret_cast<__nv_bfloat16*>(x_out), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
+      reinterpret_cast<__nv_bfloat16*>(h), rows, D, mode, eps, rpc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres, const float* scale,
+                                 const float* shift, const void* w, void* dx, float* dscale, float* dshift,
+                                 float* dw, int rows, int D, int mode, float eps, void* stream) {
+  if (D % 8 || D > 8192 || rows <= 0) return -1;
+  int rpc = pick_rows_per_cta(rows);
+  if (rpc < 16) rpc = rows < 16 ? rows : 16;  // amortise the atomic flush of the column sums
+  const int grid = (rows + rpc - 1) / rpc;
+  modnorm_bwd_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(dh),
+      reinterpret_cast<const __nv_bfloat16*>(dres), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
+      reinterpret_cast<__nv_bfloat16*>(dx), dscale, dshift, dw, rows, D, mode, eps, rpc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_gather_rows(const void* gidx, const void* const* peer_ptrs, int n_peers, void* out,
+                                 long long rows, int D, void* stream) {
+  if (D % 8 || rows <= 0 || n_peers <= 0) return -1;
+  PeerPtrs pp{};
+  for (int i = 0; i < n_peers && i < 16; ++i) pp.p[i] = reinterpret_cast<const __nv_bfloat16*>(peer_ptrs[i]);
+  const int grid = grid_for(rows * (D / 8), 256, aeris_num_sms() * 16);
+  gather_rows_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(gidx), pp, reinterpret_cast<__nv_bfloat16*>(out), rows, D);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_swiglu_fwd(const void* u, void* act, long long rows, int F, void* stream) {
+  if (F % 8 || rows <= 0) return -1;
+  const int grid = grid_for(rows * (F / 8), 256, aeris_num_sms() * 16);
+  swiglu_fwd_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(u), reinterpret_cast<__nv_bfloat16*>(act), rows, F);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_swiglu_bwd(const void* u, const void* dact, void* du, long long rows, int F, void* stream) {
+  if (F % 8 || rows <= 0) return -1;
+  const int grid = grid_for(rows * (F / 8), 256, aeris_num_sms() * 16);
+  swiglu_bwd_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(u), reinterpret_cast<const __nv_bfloat16*>(dact),
+      reinterpret_cast<__nv_bfloat16*>(du), rows, F);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_scale_rows(const void* W, const float* g, void* Wg, int R, int C, void* stream) {
+  if (C % 8) return -1;
+  const int grid = grid_for(static_cast<long long>(R) * (C / 8), 256, aeris_num_sms() * 8);
+  scale_rows_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(W), g, reinterpret_cast<__nv_bfloat16*>(Wg), R, C);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_gate_grad_finalize(float* G, const void* W, const float* g, float* dW, float* dg, int R,
+                                        int C, void* stream) {
+  if (C % 4) return -1;
+  gate_grad_finalize_kernel<<<R, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      G, reinterpret_cast<const __nv_bfloat16*>(W), g, dW, dg, R, C);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_sumsq(const float* x, long long n, double* out, void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for(n / 4 + 1, 256, aeris_num_sms() * 8);
+  sumsq_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, n, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_adamw(float* master, float* grad, float* m, float* v, void* wbf16, float* ema,
+                           const double* norm_sq, long long n, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, int step, float grad_scale, float max_norm, float ema_beta,
+                           void* stream) {
+  if (n <= 0) return 0;
+  AdamArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
+  a.bias1 = 1.f - powf(beta1, static_cast<float>(step));
+  a.bias2 = 1.f - powf(beta2, static_cast<float>(step));
+  a.grad_scale = grad_scale; a.max_norm = max_norm; a.ema_beta = ema_beta; a.nan_clamp = 1.0e5f;
+  const int grid = grid_for(n, 256, aeris_num_sms() * 16);
+  adamw_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      master, grad, m, v, reinterpret_cast<__nv_bfloat16*>(wbf16), ema, norm_sq, n, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

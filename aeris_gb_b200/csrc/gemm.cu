@@ -12,6 +12,7 @@
 // to_qkv / wo / w1 / w2) with the SwiGLU and gated-residual tails of parallel_swin.py:99-100,460-461 fused in.
 #include "common.cuh"
 #include "api.h"
+#include "host.h"
 
 #include <mutex>
 #include <stdio.h>
@@ -68,6 +69,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  {  // an earlier kernel already failed: leave before touching TMEM (decision made once per CTA)
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    __syncthreads();
+    if (s_abort) return;
+  }
 
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = p.N / BN;
@@ -353,6 +360,21 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
+int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
+                      uint64_t pitch2, uint32_t b0, uint32_t b1) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return -10;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((pitch1 * 2) & 15) || ((pitch2 * 2) & 15)) return -11;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {pitch1 * 2, pitch2 * 2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
 static int g_num_sms = 0;
 int num_sms() {
   if (!g_num_sms) {
@@ -383,6 +405,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 }  // namespace aeris
 
 using namespace aeris;
+
+int aeris_num_sms() { return aeris::num_sms(); }
 
 extern "C" int aeris_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                                int ldc, int a_mn, int b_mn, int epi, const void* resid, int ldr,

@@ -1,0 +1,38 @@
+"""Python front end of the windowed flash attention kernels (``csrc/attention.cu``)."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import lib as _l
+
+
+def attn_fwd(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int, *, out: torch.Tensor | None = None,
+             lse: torch.Tensor | None = None, scale: float | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """softmax(Q K^T * scale) V for every (window, head).
+
+    ``qkv`` is ``[n_win * N, 3 * H * d]`` bf16 with columns ordered (q|k|v, head, d) and rows window-major.
+    Returns ``(o [n_win * N, H * d] bf16, lse [n_win, H, N] fp32 in the log2 domain)``.
+    """
+    T, C = qkv.shape
+    assert T == n_win * N and C == 3 * H * d and qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
+    if out is None:
+        out = torch.empty((T, H * d), dtype=torch.bfloat16, device=qkv.device)
+    if lse is None:
+        lse = torch.empty((n_win, H, N), dtype=torch.float32, device=qkv.device)
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    ld = qkv.stride(0)
+    rc = _l.lib().aeris_attn_fwd(_l.ptr(qkv), ld, 0, _l.ptr(qkv), ld, H * d, _l.ptr(qkv), ld, 2 * H * d,
+                                 _l.ptr(out), out.stride(0), _l.ptr(lse), n_win, N, H, d,
+                                 _l._c_float(scale), _l.ptr(_l.status_word()), _l.stream_ptr())
+    _l.check(rc, "aeris_attn_fwd")
+    return out, lse
+
+
+def attn_reference(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int) -> torch.Tensor:
+    """Plain PyTorch fp32 restatement (used by tests and by the CPU oracle)."""
+    q, k, v = qkv.float().view(n_win, N, 3, H, d).permute(2, 0, 3, 1, 4)
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(d)
+    o = s.softmax(-1) @ v
+    return o.permute(0, 2, 1, 3).reshape(n_win * N, H * d)
