@@ -16,6 +16,10 @@ int aeris_attn_fwd(const void* q, int ldq, int q_col0, const void* k, int ldk, i
                    int v_col0, void* o, int ldo, float* lse, int n_win, int N, int H, int head_dim, float scale,
                    int* status, void* stream);
 
+int aeris_attn_bwd(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0, const void* o, const void* d_o,
+                   int ldo, const float* lse, float* delta, void* dqkv, int ldg, int n_win, int N, int H,
+                   int head_dim, float scale, int* status, void* stream);
+
 int aeris_modnorm_fwd(const void* x, const void* gidx, const void* const* peer_ptrs, int n_peers, void* x_out,
                       const float* scale, const float* shift, const void* w, void* h, int rows, int D, int mode,
                       float eps, void* stream);

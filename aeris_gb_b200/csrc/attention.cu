@@ -319,6 +319,448 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
+
+// -------------------------------------------------------------------------------------------------------- backward
+// Two kernels, neither needs atomics:
+//   attn_bwd_dq : one CTA per 128-row Q tile, streams K/V in 64-row tiles.  S = Q K^T, dP = dO V^T,
+//                 dS = P * (dP - delta) * scale, dQ += dS K.   Also writes delta = rowsum(dO * O).
+//   attn_bwd_dkv: one CTA per 128-row K/V tile, streams Q/dO in 64-row tiles. S^T = K Q^T, dP^T = V dO^T,
+//                 dV += P^T dO, dK += dS^T Q.
+struct AttnBwdParams {
+  const __nv_bfloat16* O;   // forward output, [T, ldo]
+  const __nv_bfloat16* dO;  // [T, ldo]
+  int ldo;
+  const float* lse;         // [n_win*H*N] log2 domain
+  float* delta;             // [n_win*H*N]
+  __nv_bfloat16* dQKV;      // [T, ldg] gradient of the fused qkv tensor
+  int ldg;
+  int N, H, n_win;
+  int q_col0, k_col0, v_col0;
+  float scale_log2, scale;
+  int* status;
+};
+constexpr int BT = 64;  // streamed tile rows in the backward kernels
+
+template <int DCH>
+__global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 2 : 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                   const AttnBwdParams p) {
+  constexpr int HD = 64 * DCH;
+  constexpr int QB = DCH * 16384;       // Q tile, dO tile (128 rows)
+  constexpr int KB = DCH * 8192;        // K tile, V tile (64 rows)
+  constexpr int STAGE = 2 * KB;
+  constexpr int TMEM_COLS = 256;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + QB;
+  uint8_t* sKV = sdO + QB;
+  uint8_t* sdS = sKV + 2 * STAGE;  // [128 x 64] bf16
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 16384);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = bars + 3;
+  uint64_t* sp_full = bars + 5;
+  uint64_t* ds_full = bars + 6;
+  uint64_t* dq_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = blockIdx.x, head = blockIdx.y, win = blockIdx.z;
+  const int N = p.N;
+  const int nfull = N / BT, rem = N - nfull * BT;
+  const int nkv = nfull + (rem ? 1 : 0);
+  const int n_last = rem ? ((rem + 15) & ~15) : BT;
+
+  if (threadIdx.x == 0) {
+    int ab = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    if ((smem_u32(smem) & 1023u) != 0) { ab = 1; if (p.status) atomicCAS(p.status, 0, ERR_BOUNDS); }
+    *s_abort = ab;
+  }
+  __syncthreads();
+  if (*s_abort) return;
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    mbar_init(sp_full, 1); mbar_init(ds_full, 4); mbar_init(dq_full, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tdQ = tmem_base + 128;
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      mbar_expect_tx(q_full, 2 * QB);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c) {
+        tma_load_3d(sQ + c * 16384, &tm_q, q_full, p.q_col0 + head * HD + c * 64, qt * TILE, win);
+        tma_load_3d(sdO + c * 16384, &tm_do, q_full, head * HD + c * 64, qt * TILE, win);
+      }
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
+        uint8_t* sK = sKV + s * STAGE;
+        uint8_t* sV = sK + KB;
+        mbar_expect_tx(&kv_full[s], STAGE);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) {
+          tma_load_3d(sK + c * 8192, &tm_k, &kv_full[s], p.k_col0 + head * HD + c * 64, j * BT, win);
+          tma_load_3d(sV + c * 8192, &tm_v, &kv_full[s], p.v_col0 + head * HD + c * 64, j * BT, win);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one_sync()) {
+      bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_ATTN);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), adS = smem_u32(sdS);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int s = j & 1;
+        const int ncur = (j == nkv - 1) ? n_last : BT;
+        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sKV + s * STAGE), aV = aK + KB;
+        const uint32_t idesc_s = make_idesc_bf16(TILE, ncur, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < 4 * DCH; ++kk) {
+          const uint32_t qoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t koff = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(tS, make_smem_desc(aQ + qoff, 0, 1024), make_smem_desc(aK + koff, 0, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4 * DCH; ++kk) {
+          const uint32_t qoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t koff = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(tdP, make_smem_desc(adO + qoff, 0, 1024), make_smem_desc(aV + koff, 0, 1024), idesc_s, kk > 0);
+        }
+        tc_commit(sp_full);
+        if (!mbar_wait(ds_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after();
+        // dQ += dS K : A = dS (K-major over kv), B = K MN-major (d contiguous, kv rows strided)
+        const uint32_t idesc_dq = make_idesc_bf16(TILE, HD, 0, 1);
+        for (int kk = 0; kk < ncur / 16; ++kk)
+          umma_ss(tdQ, make_smem_desc(adS + kk * 32, 0, 1024), make_smem_desc(aK + kk * 2048, 8192, 1024), idesc_dq,
+                  (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&kv_empty[s]);
+      }
+      if (ok) tc_commit(dq_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int grow = qt * TILE + row;
+    const bool row_ok = grow < N;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const size_t trow = static_cast<size_t>(win) * N + (row_ok ? grow : 0);
+    const size_t sidx = (static_cast<size_t>(win) * p.H + head) * N + (row_ok ? grow : 0);
+    float lse = 0.f, delta = 0.f;
+    if (row_ok) {
+      lse = p.lse[sidx];
+      const __nv_bfloat16* o = p.O + trow * p.ldo + head * HD;
+      const __nv_bfloat16* go = p.dO + trow * p.ldo + head * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 8) {
+        const uint4 a = *reinterpret_cast<const uint4*>(o + c), b = *reinterpret_cast<const uint4*>(go + c);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 x = unpack_bf16x2(aw[i]), y = unpack_bf16x2(bw[i]);
+          delta = fmaf(x.x, y.x, delta);
+          delta = fmaf(x.y, y.y, delta);
+        }
+      }
+      p.delta[sidx] = delta;
+    }
+    bool ok = true;
+    for (int j = 0; j < nkv && ok; ++j) {
+      const bool last = (j == nkv - 1);
+      const int ncur = last ? n_last : BT;
+      const int valid = (last && rem) ? rem : BT;
+      if (!mbar_wait(sp_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < ncur; c += 16) {
+        uint32_t sv[16], dv[16], pk[8];
+        tmem_ld16(tS + lane_addr + c, sv);
+        tmem_ld16(tdP + lane_addr + c, dv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -lse));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -lse));
+          float d0 = p0 * (__uint_as_float(dv[2 * i]) - delta) * p.scale;
+          float d1 = p1 * (__uint_as_float(dv[2 * i + 1]) - delta) * p.scale;
+          if (c + 2 * i >= valid || !row_ok) d0 = 0.f;
+          if (c + 2 * i + 1 >= valid || !row_ok) d1 = 0.f;
+          pk[i] = pack_bf16x2(d0, d1);
+        }
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+          *reinterpret_cast<uint4*>(sdS + swz128(row, (c >> 3) + g)) =
+              make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+    }
+    if (ok && mbar_wait(dq_full, 0, p.status, ERR_TIMEOUT_ATTN)) {
+      tc_fence_after();
+      __nv_bfloat16* dst = p.dQKV + trow * p.ldg + p.q_col0 + head * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(tdQ + lane_addr + c, v);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(dst + c + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+                pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+template <int DCH>
+__global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 2 : 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                    const AttnBwdParams p) {
+  constexpr int HD = 64 * DCH;
+  constexpr int KB = DCH * 16384;  // K tile, V tile (128 rows)
+  constexpr int QB = DCH * 8192;   // Q tile, dO tile (64 rows)
+  constexpr int STAGE = 2 * QB;
+  constexpr int TMEM_COLS = (DCH == 1) ? 256 : 512;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + KB;
+  uint8_t* sQD = sV + KB;
+  uint8_t* sPT = sQD + 2 * STAGE;  // [128 x 64] bf16
+  uint8_t* sdST = sPT + 16384;     // [128 x 64] bf16
+  float* s_stat = reinterpret_cast<float*>(sdST + 16384);  // [2 parities][lse 64 | delta 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_stat + 256);
+  uint64_t* k_full = bars;
+  uint64_t* qd_full = bars + 1;
+  uint64_t* qd_empty = bars + 3;
+  uint64_t* sp_full = bars + 5;
+  uint64_t* pd_full = bars + 6;
+  uint64_t* acc_full = bars + 7;
+  uint64_t* stat_bar = bars + 8;  // lse/delta of the current Q tile staged in shared memory (128 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, head = blockIdx.y, win = blockIdx.z;
+  const int N = p.N;
+  const int nfull = N / BT, rem = N - nfull * BT;
+  const int nq = nfull + (rem ? 1 : 0);
+  const int n_last = rem ? ((rem + 15) & ~15) : BT;
+
+  if (threadIdx.x == 0) {
+    int ab = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    if ((smem_u32(smem) & 1023u) != 0) { ab = 1; if (p.status) atomicCAS(p.status, 0, ERR_BOUNDS); }
+    *s_abort = ab;
+  }
+  __syncthreads();
+  if (*s_abort) return;
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
+    mbar_init(k_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&qd_full[i], 1); mbar_init(&qd_empty[i], 1); }
+    mbar_init(sp_full, 1); mbar_init(pd_full, 4); mbar_init(acc_full, 1); mbar_init(stat_bar, 128);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tdK = tmem_base + 128, tdV = tmem_base + 128 + HD;
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      mbar_expect_tx(k_full, 2 * KB);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c) {
+        tma_load_3d(sK + c * 16384, &tm_k, k_full, p.k_col0 + head * HD + c * 64, kt * TILE, win);
+        tma_load_3d(sV + c * 16384, &tm_v, k_full, p.v_col0 + head * HD + c * 64, kt * TILE, win);
+      }
+      for (int i = 0; i < nq; ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&qd_empty[s], ((i >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
+        uint8_t* sQ = sQD + s * STAGE;
+        uint8_t* sdO = sQ + QB;
+        mbar_expect_tx(&qd_full[s], STAGE);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) {
+          tma_load_3d(sQ + c * 8192, &tm_q, &qd_full[s], p.q_col0 + head * HD + c * 64, i * BT, win);
+          tma_load_3d(sdO + c * 8192, &tm_do, &qd_full[s], head * HD + c * 64, i * BT, win);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one_sync()) {
+      bool ok = mbar_wait(k_full, 0, p.status, ERR_TIMEOUT_ATTN);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), adST = smem_u32(sdST);
+      for (int i = 0; i < nq && ok; ++i) {
+        const int s = i & 1;
+        const int ncur = (i == nq - 1) ? n_last : BT;
+        if (!mbar_wait(&qd_full[s], (i >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQD + s * STAGE), adO = aQ + QB;
+        const uint32_t idesc_s = make_idesc_bf16(TILE, ncur, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < 4 * DCH; ++kk) {
+          const uint32_t koff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t qoff = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(tS, make_smem_desc(aK + koff, 0, 1024), make_smem_desc(aQ + qoff, 0, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4 * DCH; ++kk) {
+          const uint32_t koff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t qoff = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(tdP, make_smem_desc(aV + koff, 0, 1024), make_smem_desc(adO + qoff, 0, 1024), idesc_s, kk > 0);
+        }
+        tc_commit(sp_full);
+        if (!mbar_wait(pd_full, i & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t idesc_acc = make_idesc_bf16(TILE, HD, 0, 1);
+        for (int kk = 0; kk < ncur / 16; ++kk) {
+          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+          umma_ss(tdV, make_smem_desc(aPT + kk * 32, 0, 1024), make_smem_desc(adO + kk * 2048, 8192, 1024),
+                  idesc_acc, acc);
+          umma_ss(tdK, make_smem_desc(adST + kk * 32, 0, 1024), make_smem_desc(aQ + kk * 2048, 8192, 1024),
+                  idesc_acc, acc);
+        }
+        tc_commit(&qd_empty[s]);
+      }
+      if (ok) tc_commit(acc_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;  // kv row within the tile
+    const int grow = kt * TILE + row;
+    const bool row_ok = grow < N;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const int t128 = threadIdx.x - 64;  // 0..127 among the four math warps
+    const size_t sbase = (static_cast<size_t>(win) * p.H + head) * N;
+    bool ok = true;
+    for (int i = 0; i < nq && ok; ++i) {
+      const bool last = (i == nq - 1);
+      const int ncur = last ? n_last : BT;
+      const int valid = (last && rem) ? rem : BT;
+      float* st = s_stat + (i & 1) * 128;
+      {
+        const int col = t128 & 63;
+        const int gq = i * BT + col;
+        float v = 0.f;
+        if (gq < N) v = (t128 < 64) ? p.lse[sbase + gq] : p.delta[sbase + gq];
+        st[t128] = v;
+      }
+      mbar_arrive(stat_bar);
+      if (!mbar_wait(stat_bar, i & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      if (!mbar_wait(sp_full, i & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < ncur; c += 16) {
+        uint32_t sv[16], dv[16], pp[8], dd[8];
+        tmem_ld16(tS + lane_addr + c, sv);
+        tmem_ld16(tdP + lane_addr + c, dv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float l0 = st[c + 2 * k], l1 = st[c + 2 * k + 1];
+          const float e0 = st[64 + c + 2 * k], e1 = st[64 + c + 2 * k + 1];
+          float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * k]), p.scale_log2, -l0));
+          float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * k + 1]), p.scale_log2, -l1));
+          if (c + 2 * k >= valid || !row_ok) p0 = 0.f;
+          if (c + 2 * k + 1 >= valid || !row_ok) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(dv[2 * k]) - e0) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dv[2 * k + 1]) - e1) * p.scale;
+          pp[k] = pack_bf16x2(p0, p1);
+          dd[k] = pack_bf16x2(d0, d1);
+        }
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t off = swz128(row, (c >> 3) + g);
+          *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
+          *reinterpret_cast<uint4*>(sdST + off) = make_uint4(dd[4 * g], dd[4 * g + 1], dd[4 * g + 2], dd[4 * g + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pd_full);
+    }
+    if (ok && mbar_wait(acc_full, 0, p.status, ERR_TIMEOUT_ATTN)) {
+      tc_fence_after();
+      const size_t trow = static_cast<size_t>(win) * N + (row_ok ? grow : 0);
+      __nv_bfloat16* dk = p.dQKV + trow * p.ldg + p.k_col0 + head * HD;
+      __nv_bfloat16* dv = p.dQKV + trow * p.ldg + p.v_col0 + head * HD;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t t = which ? tdV : tdK;
+        __nv_bfloat16* dst = which ? dv : dk;
+#pragma unroll
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(t + lane_addr + c, v);
+          tmem_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              *reinterpret_cast<uint4*>(dst + c + g * 8) = make_uint4(
+                  pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+                  pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                  pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                  pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+template <int DCH>
+static int launch_attn_bwd(const CUtensorMap& tq128, const CUtensorMap& tk64, const CUtensorMap& tv64,
+                           const CUtensorMap& tdo128, const CUtensorMap& tq64, const CUtensorMap& tk128,
+                           const CUtensorMap& tv128, const CUtensorMap& tdo64, const AttnBwdParams& p,
+                           cudaStream_t stream) {
+  constexpr int SMEM_DQ = 2 * DCH * 16384 + 2 * 2 * DCH * 8192 + 16384 + 128;
+  constexpr int SMEM_DKV = 2 * DCH * 16384 + 2 * 2 * DCH * 8192 + 2 * 16384 + 1024 + 128;
+  static bool configured = false;
+  auto k1 = attn_bwd_dq_kernel<DCH>;
+  auto k2 = attn_bwd_dkv_kernel<DCH>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ) != cudaSuccess) return -20;
+    if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DKV) != cudaSuccess) return -20;
+    configured = true;
+  }
+  dim3 grid((p.N + TILE - 1) / TILE, p.H, p.n_win);
+  k1<<<grid, ATT_THREADS, SMEM_DQ, stream>>>(tq128, tk64, tv64, tdo128, p);
+  if (cudaGetLastError() != cudaSuccess) return -21;
+  k2<<<grid, ATT_THREADS, SMEM_DKV, stream>>>(tq64, tk128, tv128, tdo64, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -22;
+}
+
 }  // namespace aeris
 
 using namespace aeris;
@@ -340,4 +782,28 @@ extern "C" int aeris_attn_fwd(const void* q, int ldq, int q_col0, const void* k,
   if ((r = make_tmap_3d_bf16(&tk, k, ldk, N, n_win, ldk, static_cast<uint64_t>(N) * ldk, 64, TILE))) return r;
   if ((r = make_tmap_3d_bf16(&tv, v, ldv, N, n_win, ldv, static_cast<uint64_t>(N) * ldv, 64, TILE))) return r;
   return head_dim == 64 ? launch_attn_fwd<1>(tq, tk, tv, p, stream) : launch_attn_fwd<2>(tq, tk, tv, p, stream);
+}
+
+// Backward. qkv: fused [T, ldq] tensor (q/k/v column blocks at *_col0); o, d_o: [T, ldo]; dqkv: [T, ldg] (same
+// column layout as qkv); lse from the forward; delta: scratch [n_win*H*N] fp32 written by the first kernel.
+extern "C" int aeris_attn_bwd(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0, const void* o,
+                              const void* d_o, int ldo, const float* lse, float* delta, void* dqkv, int ldg,
+                              int n_win, int N, int H, int head_dim, float scale, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (head_dim != 64 && head_dim != 128) return -1;
+  if (n_win <= 0 || N <= 0 || H <= 0 || n_win > 65535 || H > 65535) return -2;
+  AttnBwdParams p{};
+  p.O = reinterpret_cast<const __nv_bfloat16*>(o); p.dO = reinterpret_cast<const __nv_bfloat16*>(d_o); p.ldo = ldo;
+  p.lse = lse; p.delta = delta; p.dQKV = reinterpret_cast<__nv_bfloat16*>(dqkv); p.ldg = ldg;
+  p.N = N; p.H = H; p.n_win = n_win; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  CUtensorMap t128, t64, d128, d64;
+  int r;
+  const uint64_t wq = static_cast<uint64_t>(N) * ldq, wo = static_cast<uint64_t>(N) * ldo;
+  if ((r = make_tmap_3d_bf16(&t128, qkv, ldq, N, n_win, ldq, wq, 64, TILE))) return r;
+  if ((r = make_tmap_3d_bf16(&t64, qkv, ldq, N, n_win, ldq, wq, 64, BT))) return r;
+  if ((r = make_tmap_3d_bf16(&d128, d_o, ldo, N, n_win, ldo, wo, 64, TILE))) return r;
+  if ((r = make_tmap_3d_bf16(&d64, d_o, ldo, N, n_win, ldo, wo, 64, BT))) return r;
+  return head_dim == 64 ? launch_attn_bwd<1>(t128, t64, t64, d128, t64, t128, t128, d64, p, stream)
+                        : launch_attn_bwd<2>(t128, t64, t64, d128, t64, t128, t128, d64, p, stream);
 }

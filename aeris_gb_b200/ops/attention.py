@@ -36,3 +36,21 @@ def attn_reference(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int) -> tor
     s = (q @ k.transpose(-1, -2)) / math.sqrt(d)
     o = s.softmax(-1) @ v
     return o.permute(0, 2, 1, 3).reshape(n_win * N, H * d)
+
+
+def attn_bwd(qkv: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor, lse: torch.Tensor, n_win: int, N: int, H: int,
+             d: int, *, dqkv: torch.Tensor | None = None, delta: torch.Tensor | None = None,
+             scale: float | None = None) -> torch.Tensor:
+    """Gradient of :func:`attn_fwd` with respect to the fused qkv tensor (same layout as ``qkv``)."""
+    T, C = qkv.shape
+    assert o.shape == (T, H * d) and d_o.shape == (T, H * d) and d_o.stride(1) == 1 and o.stride(0) == d_o.stride(0)
+    if dqkv is None:
+        dqkv = torch.empty_like(qkv)
+    if delta is None:
+        delta = torch.empty((n_win, H, N), dtype=torch.float32, device=qkv.device)
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    rc = _l.lib().aeris_attn_bwd(_l.ptr(qkv), qkv.stride(0), 0, H * d, 2 * H * d, _l.ptr(o), _l.ptr(d_o),
+                                 o.stride(0), _l.ptr(lse), _l.ptr(delta), _l.ptr(dqkv), dqkv.stride(0), n_win, N, H,
+                                 d, _l._c_float(scale), _l.ptr(_l.status_word()), _l.stream_ptr())
+    _l.check(rc, "aeris_attn_bwd")
+    return dqkv
