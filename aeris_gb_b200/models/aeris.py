@@ -1,0 +1,331 @@
+"""AERIS pixel-level Swin diffusion transformer: stage modules with the reference's state-dict key layout.
+
+Module / key parity with the reference (so per-stage checkpoints load unchanged):
+  * input stage  ``proj.{weight,bias}``, ``latent_embed.w{1,2}.{weight,bias}``, ``ape.inv_freq``
+    (src/aeris/models/parallel_swin.py:339-399)
+  * Swin layer   ``modulelist.{j}.0.weight`` (RMSNorm), ``.1.norm.weight`` (unused, kept for key parity),
+    ``.1.to_qkv.weight``, ``.1.wo.weight``, ``.2.weight``, ``.3.w1.weight``, ``.3.w2.weight``,
+    ``.4.modulation.{0,2}.{weight,bias}`` (parallel_swin.py:401-472)
+  * output stage ``norm.weight``, ``modulation.{0,2}.{weight,bias}``, ``head.weight`` (parallel_swin.py:490-532)
+  * monolithic model ``input_stage.* / layers.{i}.* / output_stage.*`` and the per-stage -> monolithic conversion of
+    src/aeris_wp_inference/model.py:431-495.
+
+The modules operate on a *window-major token stream* (see :mod:`.layout`). On a CUDA device the blocks run on the
+hand-written sm_100a kernels (:mod:`.fused`); on CPU they run the PyTorch oracle (:mod:`.oracle`).
+"""
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import layout as LY
+from . import oracle as O
+
+
+@dataclass
+class AerisConfig:
+    img: tuple[int, int] = (720, 1440)
+    window: tuple[int, int] = (60, 60)
+    in_channels: int = 144          # noisy target + condition channels
+    out_channels: int = 70
+    dim: int = 1536
+    heads: int = 12
+    head_dim: int = 128
+    mlp_dim: int = 6144
+    n_layers: int = 8               # Swin layers (= PP_stages - 2 in the reference)
+    sublayers: int = 3              # transformer blocks per layer
+    layerwise_t_emb: bool = True
+    after_mod_norm: bool = True     # modulate -> norm (True) or norm -> modulate (False)
+    max_period: float = 10_000.0
+    norm_eps: float | None = None   # None: machine epsilon of the block dtype (what nn.RMSNorm(eps=None) does)
+    ape_row_offset: int | None = None  # None: 1 for 720-row grids (reference builds the APE on 721 rows, drops row 0)
+    model_dtype: torch.dtype = torch.bfloat16
+    data_dtype: torch.dtype = torch.float32
+    wp: tuple[int, int] = (1, 1)
+    chunk_windows: int = 64
+    shift_layers: str = "odd"       # which layers use the half-window shift: "odd" | "none"
+
+    @property
+    def n_blocks(self) -> int:
+        return self.n_layers * self.sublayers
+
+    def grid(self) -> LY.Grid:
+        return LY.Grid(self.img[0], self.img[1], self.window[0], self.window[1], self.wp[0], self.wp[1])
+
+    def eps(self, dtype: torch.dtype) -> float:
+        return self.norm_eps if self.norm_eps is not None else float(torch.finfo(dtype).eps)
+
+    def layer_shift(self, i: int) -> tuple[int, int]:
+        if self.shift_layers == "odd" and i % 2 == 1:
+            return (self.window[0] // 2, self.window[1] // 2)
+        return (0, 0)
+
+    def param_count(self) -> int:
+        d, hd, f = self.dim, self.heads * self.head_dim, self.mlp_dim
+        mod = (d * d + d if self.layerwise_t_emb else 0) + d * 6 * d + 6 * d
+        block = 2 * d + hd + 3 * hd * d + d * hd + 3 * d * f + mod
+        inp = self.in_channels * d + d + 2 * (d * d + d)
+        outp = d + (d * d + d if self.layerwise_t_emb else 0) + d * 2 * d + 2 * d + d * self.out_channels
+        return block * self.n_blocks + inp + outp
+
+    def flops_per_sample(self) -> float:
+        return O.get_swin_flop_count(self.img, 1, self.n_blocks, self.in_channels, self.dim, self.mlp_dim, (1, 1),
+                                     self.window)
+
+
+class StreamContext:
+    """Per-forward information the stage modules need about the token stream."""
+
+    def __init__(self, cfg: AerisConfig, batch: int, rank: int = 0, peer_fn=None):
+        self.cfg = cfg
+        self.grid = cfg.grid()
+        self.batch = batch
+        self.rank = rank
+        self.peer_fn = peer_fn        # callable(tensor, direction) -> list of peer base addresses (WP) or None
+        self._tables: dict = {}
+
+    def table(self, src_shift, dst_shift, device) -> torch.Tensor:
+        key = (src_shift, dst_shift, str(device))
+        if key not in self._tables:
+            self._tables[key] = LY.gather_table(self.grid, src_shift, dst_shift, self.rank, self.batch).to(device)
+        return self._tables[key]
+
+
+def use_fused(t: torch.Tensor) -> bool:
+    return t.is_cuda and os.environ.get("AERIS_FORCE_ORACLE") != "1"
+
+
+# ---------------------------------------------------------------------------------------------------- sub-modules
+class LatentEmbedding(nn.Module):
+    def __init__(self, dim):
+        super().__init__()
+        self.w1 = nn.Linear(dim, dim, bias=True)
+        self.w2 = nn.Linear(dim, dim, bias=True)
+        self.w1.is_time_emb = True
+        self.w2.is_time_emb = True
+
+    def forward(self, emb):
+        return F.silu(self.w2(F.silu(self.w1(emb))))
+
+
+class ApeBuffer(nn.Module):
+    """Holds ``inv_freq`` for key parity; the encoding itself is produced by :func:`oracle.positional_encoding_2d`."""
+
+    def __init__(self, channels, max_positions=10_000):
+        super().__init__()
+        ch = int(math.ceil(channels / 4) * 2)
+        self.register_buffer("inv_freq", 1.0 / (max_positions ** (torch.arange(0, ch, 2).float() / ch)))
+
+
+class AttentionParams(nn.Module):
+    def __init__(self, dim, heads, head_dim):
+        super().__init__()
+        self.norm = nn.RMSNorm(dim)       # present in reference checkpoints, never applied in diffusion mode
+        self.norm.weight.requires_grad_(False)
+        self.to_qkv = nn.Linear(dim, 3 * heads * head_dim, bias=False)
+        self.wo = nn.Linear(heads * head_dim, dim, bias=False)
+
+
+class FeedForwardParams(nn.Module):
+    def __init__(self, dim, hidden):
+        super().__init__()
+        self.w1 = nn.Linear(dim, 2 * hidden, bias=False)
+        self.w2 = nn.Linear(hidden, dim, bias=False)
+
+
+class ModulationLinear(nn.Module):
+    def __init__(self, dim, out_dim, layerwise):
+        super().__init__()
+        if layerwise:
+            self.modulation = nn.Sequential(nn.Linear(dim, dim, bias=True), nn.SiLU(), nn.Linear(dim, out_dim, bias=True))
+        else:
+            # same indices as the reference's two-element Sequential (SiLU at 0, Linear at 1)
+            self.modulation = nn.Sequential(nn.SiLU(), nn.Linear(dim, out_dim, bias=True))
+
+    def forward(self, x):
+        return self.modulation(x)
+
+
+# ---------------------------------------------------------------------------------------------------- stages
+class InputStage(nn.Module):
+    """fp32: (x + APE) -> Linear(in_channels -> dim) -> model dtype; sinusoidal noise-level embedding."""
+
+    def __init__(self, cfg: AerisConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.proj = nn.Linear(cfg.in_channels, cfg.dim).to(cfg.data_dtype)
+        self.proj.is_emb = True
+        self.latent_embed = LatentEmbedding(cfg.dim).to(cfg.data_dtype)
+        self.ape = ApeBuffer(cfg.in_channels)
+        self._ape_tok: dict = {}
+
+    def ape_tokens(self, ctx: StreamContext, device) -> torch.Tensor:
+        key = (ctx.rank, str(device))
+        if key not in self._ape_tok:
+            cfg = self.cfg
+            off = cfg.ape_row_offset if cfg.ape_row_offset is not None else (1 if cfg.img[0] == 720 else 0)
+            pe = O.positional_encoding_2d(cfg.in_channels, cfg.img[0] + off, cfg.img[1], dtype=cfg.data_dtype)[off:]
+            tok = LY.image_to_tokens(pe.unsqueeze(0), ctx.grid, (0, 0), ctx.rank)
+            self._ape_tok[key] = tok.to(device)
+        return self._ape_tok[key]
+
+    def forward(self, x_tok: torch.Tensor, t: torch.Tensor, ctx: StreamContext):
+        """x_tok: [B * tokens_per_rank, in_channels] fp32 in the unshifted layout; t: [B] noise level (radians)."""
+        cfg = self.cfg
+        B = t.shape[0]
+        ape = self.ape_tokens(ctx, x_tok.device)
+        rows = ape.shape[0]
+        out = torch.empty((x_tok.shape[0], cfg.dim), dtype=cfg.model_dtype, device=x_tok.device)
+        step = 1 << 16
+        for b in range(B):
+            for r in range(0, rows, step):
+                sl = slice(b * rows + r, b * rows + min(rows, r + step))
+                out[sl] = self.proj(x_tok[sl].to(cfg.data_dtype) + ape[r:r + step]).to(cfg.model_dtype)
+        emb = O.timestep_embedding(t.to(cfg.data_dtype), cfg.dim, cfg.max_period)
+        if not cfg.layerwise_t_emb:
+            emb = self.latent_embed(emb)
+        return out, emb.to(cfg.model_dtype)
+
+
+class SwinLayer(nn.Module):
+    """``sublayers`` transformer blocks that share one window partition."""
+
+    def __init__(self, cfg: AerisConfig):
+        super().__init__()
+        self.cfg = cfg
+        d = cfg.dim
+        self.modulelist = nn.ModuleList([
+            nn.ModuleList([
+                nn.RMSNorm(d),
+                AttentionParams(d, cfg.heads, cfg.head_dim),
+                nn.RMSNorm(d),
+                FeedForwardParams(d, cfg.mlp_dim),
+                ModulationLinear(d, 6 * d, cfg.layerwise_t_emb),
+            ]) for _ in range(cfg.sublayers)
+        ])
+
+    def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
+        cfg = self.cfg
+        eps = cfg.eps(x.dtype)
+        for n1, attn, n2, ff, mod in self.modulelist:
+            m = mod(dt.to(mod.modulation[-1].weight.dtype))
+            if use_fused(x):
+                from . import fused
+                from ..ops import elementwise as E
+                meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.L, cfg.heads, cfg.head_dim,
+                                       E.MODE_MOD_THEN_NORM if cfg.after_mod_norm else E.MODE_NORM_THEN_MOD,
+                                       eps, cfg.chunk_windows)
+                x = fused.FusedBlock.apply(x, m, meta, n1.weight, attn.to_qkv.weight, attn.wo.weight, n2.weight,
+                                           ff.w1.weight, ff.w2.weight)
+            else:
+                p = {"n1": n1.weight, "to_qkv": attn.to_qkv.weight, "wo": attn.wo.weight, "n2": n2.weight,
+                     "w1": ff.w1.weight, "w2": ff.w2.weight}
+                x = O.block_forward(x, m, p, n_win_per_sample=ctx.grid.windows_per_rank, L=ctx.grid.L,
+                                    heads=cfg.heads, head_dim=cfg.head_dim, after_mod_norm=cfg.after_mod_norm,
+                                    eps=eps)
+        return x
+
+
+class OutputStage(nn.Module):
+    """fp32: RMSNorm -> modulate(shift, scale) -> Linear(dim -> out_channels, no bias)."""
+
+    def __init__(self, cfg: AerisConfig):
+        super().__init__()
+        self.cfg = cfg
+        d = cfg.dim
+        self.norm = nn.RMSNorm(d).to(cfg.data_dtype)
+        self.norm.is_head = True
+        if cfg.layerwise_t_emb:
+            self.modulation = nn.Sequential(nn.Linear(d, d, bias=True), nn.SiLU(), nn.Linear(d, 2 * d, bias=True))
+        else:
+            self.modulation = nn.Sequential(nn.SiLU(), nn.Linear(d, 2 * d, bias=True))
+        self.modulation.to(cfg.data_dtype)
+        self.head = nn.Linear(d, cfg.out_channels, bias=False).to(cfg.data_dtype)
+
+    def forward_rows(self, x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        xf = x.to(cfg.data_dtype)
+        xn = O.rms_norm(xf, self.norm.weight, cfg.eps(cfg.data_dtype))
+        return self.head(xn * (1 + scale) + shift)
+
+    def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
+        cfg = self.cfg
+        B = dt.shape[0]
+        shift, scale = self.modulation(dt.to(cfg.data_dtype)).chunk(2, dim=1)
+        rows = x.shape[0] // B
+        outs = []
+        step = 1 << 16
+        for b in range(B):
+            for r in range(0, rows, step):
+                sl = slice(b * rows + r, b * rows + min(rows, r + step))
+                outs.append(self.forward_rows(x[sl], shift[b:b + 1], scale[b:b + 1]))
+        return torch.cat(outs, dim=0)
+
+
+# ---------------------------------------------------------------------------------------------------- full model
+class AerisModel(nn.Module):
+    """Input stage + ``n_layers`` Swin layers (odd ones on the half-window-shifted partition) + output stage."""
+
+    def __init__(self, cfg: AerisConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.input_stage = InputStage(cfg)
+        self.layers = nn.ModuleList([SwinLayer(cfg) for _ in range(cfg.n_layers)]).to(cfg.model_dtype)
+        self.output_stage = OutputStage(cfg)
+
+    def regroup(self, x: torch.Tensor, src, dst, ctx: StreamContext) -> torch.Tensor:
+        if src == dst:
+            return x
+        fwd = ctx.table(src, dst, x.device)
+        bwd = ctx.table(dst, src, x.device)
+        if use_fused(x):
+            from . import fused
+            return fused.Regroup.apply(x, fwd, bwd, ctx.peer_fn)
+        assert ctx.grid.n_ranks == 1, "the CPU oracle runs single-rank (multi-rank layouts are tested separately)"
+        _, row = LY.decode_table(fwd)
+        return x[row.to(x.device)]
+
+    def forward_tokens(self, x_tok: torch.Tensor, t: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
+        x, dt = self.input_stage(x_tok, t, ctx)
+        cur = (0, 0)
+        for i, layer in enumerate(self.layers):
+            nxt = self.cfg.layer_shift(i)
+            x = self.regroup(x, cur, nxt, ctx)
+            cur = nxt
+            x = layer(x, dt, ctx)
+        x = self.regroup(x, cur, (0, 0), ctx)
+        return self.output_stage(x, dt, ctx)
+
+    def forward(self, x_img: torch.Tensor, t: torch.Tensor) -> torch.Tensor:
+        """x_img: [B, H, W, in_channels] fp32; t: [B]. Returns [B, H, W, out_channels] fp32 (single rank)."""
+        B = x_img.shape[0]
+        ctx = StreamContext(self.cfg, B)
+        tok = LY.image_to_tokens(x_img, ctx.grid, (0, 0), 0)
+        out = self.forward_tokens(tok, t, ctx)
+        return LY.tokens_to_image([out], ctx.grid, (0, 0), B)
+
+
+# ---------------------------------------------------------------------------------------------------- stage factory
+def init_layer(stage_id: int, n_stages: int, cfg: AerisConfig) -> nn.Module:
+    """Module for one pipeline stage: 0 = input stage, last = output stage, others one Swin layer
+    (reference: ``init_layer`` parallel_swin.py:535-568)."""
+    if stage_id == 0:
+        return InputStage(cfg)
+    if stage_id == n_stages - 1:
+        return OutputStage(cfg)
+    return SwinLayer(cfg).to(cfg.model_dtype)
+
+
+def stage_to_model_key(stage_id: int, n_stages: int, key: str) -> str | None:
+    """Maps a per-stage checkpoint key to the monolithic model key (src/aeris_wp_inference/model.py:479-495);
+    returns None for the keys the reference drops (``latent_embed*`` of stage 0 when layerwise, ``*.1.norm*``)."""
+    if stage_id == 0:
+        return f"input_stage.{key}"
+    if stage_id == n_stages - 1:
+        return f"output_stage.{key}"
+    return f"layers.{stage_id - 1}.{key}"

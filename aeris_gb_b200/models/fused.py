@@ -1,0 +1,229 @@
+"""CUDA execution of one Swin-TrigFlow block (forward and hand-derived backward) on the sm_100a kernels.
+
+The block is processed in *chunks of whole windows* of one sample: inside a block every token only interacts with its
+own window, so a chunk runs modulate+RMSNorm -> QKV GEMM -> window attention -> (wo GEMM + gated residual) ->
+modulate+RMSNorm -> (w1 GEMM + SwiGLU) -> (w2 GEMM + gated residual) with a working set of a few GB no matter how
+large the image is. Training keeps only the block input (activation checkpointing, absent from the reference and
+mandatory for one million tokens per sample); the backward pass recomputes a chunk's internals and immediately
+back-propagates through them, accumulating weight gradients in fp32 directly from the GEMM epilogue.
+
+Math restated from src/aeris/models/parallel_swin.py:453-472 (block), :82-104 (SwiGLU), :261-308 (attention).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import attention as A
+from ..ops import elementwise as E
+from ..ops import gemm as G
+
+
+@dataclass
+class BlockMeta:
+    n_win_per_sample: int      # windows of one sample held by this rank
+    L: int                     # tokens per window
+    heads: int
+    head_dim: int
+    mode: int                  # E.MODE_MOD_THEN_NORM or E.MODE_NORM_THEN_MOD
+    eps: float
+    chunk_windows: int = 64
+
+
+class Workspace:
+    """Named scratch tensors, allocated once at the largest size asked for and reused by every block."""
+
+    def __init__(self):
+        self._buf: dict[str, torch.Tensor] = {}
+
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype, device, zero: bool = False) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        b = self._buf.get(name)
+        if b is None or b.numel() < n or b.dtype != dtype or b.device != torch.device(device):
+            b = torch.empty(n, dtype=dtype, device=device)
+            self._buf[name] = b
+        v = b[:n].view(*shape)
+        if zero:
+            v.zero_()
+        return v
+
+    def clear(self):
+        self._buf.clear()
+
+
+_WS = Workspace()
+
+
+def workspace() -> Workspace:
+    return _WS
+
+
+def _chunks(meta: BlockMeta):
+    step = min(meta.chunk_windows, meta.n_win_per_sample)
+    for w0 in range(0, meta.n_win_per_sample, step):
+        yield w0, min(step, meta.n_win_per_sample - w0)
+
+
+def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv, wo, wn2, w1, w2,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """x: [B * n_win * L, D] bf16 window-major; mod: [B, 6D] fp32 (shift1, scale1, gate1, shift2, scale2, gate2)."""
+    T, D = x.shape
+    B = mod.shape[0]
+    F = w2.shape[1]
+    HD = meta.heads * meta.head_dim
+    rows_per_sample = meta.n_win_per_sample * meta.L
+    assert T == B * rows_per_sample
+    y = out if out is not None else torch.empty_like(x)
+    ws, dev, bf = _WS, x.device, torch.bfloat16
+    cmax = min(meta.chunk_windows, meta.n_win_per_sample) * meta.L
+    h = ws.get("h", (cmax, D), bf, dev)
+    qkv = ws.get("qkv", (cmax, 3 * HD), bf, dev)
+    o = ws.get("o", (cmax, HD), bf, dev)
+    x1 = ws.get("x1", (cmax, D), bf, dev)
+    act = ws.get("act", (cmax, F), bf, dev)
+    lse = ws.get("lse", (cmax * meta.heads,), torch.float32, dev)
+    mod = mod.contiguous()
+    for b in range(B):
+        sh1, sc1, g1, sh2, sc2, g2 = [mod[b, i * D:(i + 1) * D] for i in range(6)]
+        for w0, nw in _chunks(meta):
+            r0 = b * rows_per_sample + w0 * meta.L
+            n = nw * meta.L
+            xc = x[r0:r0 + n]
+            E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h[:n])
+            G.gemm(h[:n], wqkv, out=qkv[:n])
+            A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n],
+                       lse=lse[:n * meta.heads].view(nw, meta.heads, meta.L))
+            G.gemm(o[:n], wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
+            E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=h[:n])
+            G.gemm(h[:n], w1, out=act[:n], epi=G.EPI_SWIGLU)
+            G.gemm(act[:n], w2, out=y[r0:r0 + n], epi=G.EPI_GATE_RESID, resid=x1[:n], gate=g2)
+    return y
+
+
+def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: BlockMeta, wn1, wqkv, wo, wn2, w1, w2,
+                   grads: dict[str, torch.Tensor], dx: torch.Tensor | None = None):
+    """Recompute-and-backpropagate. ``grads`` maps n1, to_qkv, wo, n2, w1, w2 to fp32 accumulators (+=).
+    Returns (dx bf16, dmod [B, 6D] fp32). ``dx`` may alias ``dy``."""
+    T, D = x.shape
+    B = mod.shape[0]
+    F = w2.shape[1]
+    HD = meta.heads * meta.head_dim
+    rows_per_sample = meta.n_win_per_sample * meta.L
+    ws, dev, bf, f32 = _WS, x.device, torch.bfloat16, torch.float32
+    cmax = min(meta.chunk_windows, meta.n_win_per_sample) * meta.L
+    h1 = ws.get("h", (cmax, D), bf, dev)
+    qkv = ws.get("qkv", (cmax, 3 * HD), bf, dev)
+    o = ws.get("o", (cmax, HD), bf, dev)
+    x1 = ws.get("x1", (cmax, D), bf, dev)
+    act = ws.get("act", (cmax, F), bf, dev)
+    lse = ws.get("lse", (cmax * meta.heads,), f32, dev)
+    h2 = ws.get("h2", (cmax, D), bf, dev)
+    u = ws.get("u", (cmax, 2 * F), bf, dev)
+    dact = ws.get("dact", (cmax, F), bf, dev)
+    dh = ws.get("dh", (cmax, D), bf, dev)
+    dx1 = ws.get("dx1", (cmax, D), bf, dev)
+    d_o = ws.get("d_o", (cmax, HD), bf, dev)
+    dqkv = ws.get("dqkv", (cmax, 3 * HD), bf, dev)
+    delta = ws.get("delta", (cmax * meta.heads,), f32, dev)
+    w2g = ws.get("w2g", tuple(w2.shape), bf, dev)
+    wog = ws.get("wog", tuple(wo.shape), bf, dev)
+    G2 = ws.get("G2", tuple(w2.shape), f32, dev, zero=True)   # dy^T act  (ungated w2 gradient of one sample)
+    Go = ws.get("Go", tuple(wo.shape), f32, dev, zero=True)   # dx1^T o
+    dmod = torch.zeros((B, 6 * D), dtype=f32, device=dev)
+    if dx is None:
+        dx = torch.empty_like(x)
+    mod = mod.contiguous()
+    ksplit_tok = 4
+    for b in range(B):
+        sh1, sc1, g1, sh2, sc2, g2 = [mod[b, i * D:(i + 1) * D] for i in range(6)]
+        dsh1, dsc1, dg1, dsh2, dsc2, dg2 = [dmod[b, i * D:(i + 1) * D] for i in range(6)]
+        E.scale_rows(w2, g2, out=w2g)
+        E.scale_rows(wo, g1, out=wog)
+        for w0, nw in _chunks(meta):
+            r0 = b * rows_per_sample + w0 * meta.L
+            n = nw * meta.L
+            xc, dyc = x[r0:r0 + n], dy[r0:r0 + n]
+            lse_c = lse[:n * meta.heads].view(nw, meta.heads, meta.L)
+            # ---- recompute the chunk's forward internals
+            E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h1[:n])
+            G.gemm(h1[:n], wqkv, out=qkv[:n])
+            A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n], lse=lse_c)
+            G.gemm(o[:n], wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
+            E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=h2[:n])
+            G.gemm(h2[:n], w1, out=u[:n])
+            E.swiglu_fwd(u[:n], out=act[:n])
+            # ---- MLP half: y = x1 + g2 * (act @ w2^T)
+            G.gemm(dyc, w2g, b_t=True, out=dact[:n])                                   # dact = (dy * g2) @ w2
+            G.gemm(dyc, act[:n], a_t=True, b_t=True, out=G2, epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+            E.swiglu_bwd(u[:n], dact[:n], du=u[:n])                                    # du overwrites u
+            G.gemm(u[:n], w1, b_t=True, out=dh[:n])                                    # dh2 = du @ w1
+            G.gemm(u[:n], h2[:n], a_t=True, b_t=True, out=grads["w1"], epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+            E.modnorm_bwd(x1[:n], dh[:n], dyc, sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, dx=dx1[:n],
+                          dscale=dsc2, dshift=dsh2, dw=grads["n2"])
+            # ---- attention half: x1 = x + g1 * (o @ wo^T)
+            G.gemm(dx1[:n], wog, b_t=True, out=d_o[:n])                                # do = (dx1 * g1) @ wo
+            G.gemm(dx1[:n], o[:n], a_t=True, b_t=True, out=Go, epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+            A.attn_bwd(qkv[:n], o[:n], d_o[:n], lse_c, nw, meta.L, meta.heads, meta.head_dim, dqkv=dqkv[:n],
+                       delta=delta[:n * meta.heads].view(nw, meta.heads, meta.L))
+            G.gemm(dqkv[:n], wqkv, b_t=True, out=dh[:n])                               # dh1 = dqkv @ wqkv
+            G.gemm(dqkv[:n], h1[:n], a_t=True, b_t=True, out=grads["to_qkv"], epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+            E.modnorm_bwd(xc, dh[:n], dx1[:n], sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, dx=dx[r0:r0 + n],
+                          dscale=dsc1, dshift=dsh1, dw=grads["n1"])
+        # per-sample gate handling: dW += g * G ; dg = rowsum(W * G) ; G <- 0
+        E.gate_grad_finalize(G2, w2, g2, grads["w2"], dg2)
+        E.gate_grad_finalize(Go, wo, g1, grads["wo"], dg1)
+    return dx, dmod
+
+
+class FusedBlock(torch.autograd.Function):
+    """Autograd wrapper: saves only the block input; weight gradients go to ``param.main_grad`` (fp32) when the
+    engine provides one, otherwise they are returned to autograd."""
+
+    @staticmethod
+    def forward(ctx, x, mod, meta, wn1, wqkv, wo, wn2, w1, w2):
+        ctx.meta = meta
+        ctx.save_for_backward(x, mod, wn1, wqkv, wo, wn2, w1, w2)
+        return block_forward(x, mod.float(), meta, wn1, wqkv, wo, wn2, w1, w2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, mod, wn1, wqkv, wo, wn2, w1, w2 = ctx.saved_tensors
+        params = {"n1": wn1, "to_qkv": wqkv, "wo": wo, "n2": wn2, "w1": w1, "w2": w2}
+        grads, ret = {}, {}
+        for k, p in params.items():
+            mg = getattr(p, "main_grad", None)
+            if mg is not None:
+                grads[k] = mg.view(p.shape) if mg.dim() != p.dim() else mg
+                ret[k] = None
+            else:
+                grads[k] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+                ret[k] = grads[k]
+        dy = dy.contiguous()
+        dx, dmod = block_backward(x, mod.float(), dy, ctx.meta, wn1, wqkv, wo, wn2, w1, w2, grads, dx=dy)
+        out = [ret[k].to(params[k].dtype) if ret[k] is not None else None
+               for k in ("n1", "to_qkv", "wo", "n2", "w1", "w2")]
+        return (dx, dmod.to(mod.dtype), None, *out)
+
+
+class Regroup(torch.autograd.Function):
+    """Row gather between two window layouts through a table; the backward pass is the gather with the inverse
+    table. ``peers`` lists the base addresses of every WP rank's source buffer (just the local one without WP)."""
+
+    @staticmethod
+    def forward(ctx, x, table_fwd, table_bwd, peer_fn):
+        ctx.table_bwd, ctx.peer_fn = table_bwd, peer_fn
+        out = torch.empty((table_fwd.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+        peers = peer_fn(x, "fwd") if peer_fn is not None else [x.data_ptr()]
+        E.gather_rows(table_fwd, peers, out)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy = dy.contiguous()
+        out = torch.empty((ctx.table_bwd.numel(), dy.shape[1]), dtype=dy.dtype, device=dy.device)
+        peers = ctx.peer_fn(dy, "bwd") if ctx.peer_fn is not None else [dy.data_ptr()]
+        E.gather_rows(ctx.table_bwd, peers, out)
+        return out, None, None, None

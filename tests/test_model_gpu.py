@@ -1,0 +1,53 @@
+"""The CUDA block path (hand-written forward and backward) against the PyTorch oracle on a small model."""
+import os
+
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _small_cfg(after_mod_norm=True, head_dim=64, window=(16, 16)):
+    from aeris_gb_b200.models.aeris import AerisConfig
+    return AerisConfig(img=(32, 64), window=window, in_channels=20, out_channels=8, dim=128, heads=2,
+                       head_dim=head_dim, mlp_dim=256, n_layers=2, sublayers=2, after_mod_norm=after_mod_norm,
+                       norm_eps=1e-3, chunk_windows=3)
+
+
+@pytest.mark.parametrize("after_mod_norm", [True, False])
+def test_fused_model_matches_oracle(after_mod_norm):
+    from aeris_gb_b200.models.aeris import AerisModel
+    torch.manual_seed(1)
+    cfg = _small_cfg(after_mod_norm)
+    model = AerisModel(cfg).cuda()
+    for n, p in model.named_parameters():
+        if "modulation" in n and p.dim() == 2:
+            torch.nn.init.normal_(p, std=0.05)
+    x = torch.randn(2, 32, 64, cfg.in_channels, device="cuda")
+    t = torch.tensor([0.3, 1.2], device="cuda")
+    params = [p for p in model.parameters() if p.requires_grad]
+
+    def run(force_oracle):
+        os.environ["AERIS_FORCE_ORACLE"] = "1" if force_oracle else "0"
+        for p in params:
+            p.grad = None
+        xin = x.clone().requires_grad_(True)
+        y = model(xin, t)
+        (y * torch.linspace(-1, 1, y.numel(), device="cuda").view_as(y)).sum().backward()
+        return y.detach(), xin.grad, [p.grad.clone() if p.grad is not None else None for p in params]
+
+    try:
+        y0, gx0, g0 = run(True)
+        y1, gx1, g1 = run(False)
+    finally:
+        os.environ.pop("AERIS_FORCE_ORACLE", None)
+    assert rel_err(y1, y0) < 3e-2
+    assert rel_err(gx1, gx0) < 5e-2
+    names = [n for n, p in model.named_parameters() if p.requires_grad]
+    for n, a, b in zip(names, g1, g0):
+        if b is None or b.float().norm() == 0:
+            continue
+        assert a is not None, n
+        assert rel_err(a, b) < 8e-2, (n, rel_err(a, b))
