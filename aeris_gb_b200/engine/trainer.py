@@ -1,0 +1,148 @@
+"""Single-node training engine: window-parallel (WP) x data-parallel TrigFlow training with every logical pipeline
+stage resident on each GPU (one process per GPU, NCCL for plumbing, peer-memory kernels for the halo exchange).
+
+Public API::
+
+    trainer = Trainer(model_cfg, optim_cfg, diff_cfg, device)       # after torch.distributed is initialised (or not)
+    loss = trainer.train_step(target_host, cond_host)               # pinned host tensors in, python float out
+
+What it replaces in the reference: ``ParallelEngine.exec_schedule`` with load -> fwd -> bwd -> reduce -> step
+(src/aeris/parallelism/parallel_engine.py:585-686, 889-1017, 696-887) for the case PP = 1 (all stages local), with
+the per-rank data tiles of ``scripts/data_processing/wp_create.py`` replaced by contiguous image blocks.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.utils.checkpoint as ckpt
+
+from ..diffusion import trigflow as TF
+from ..models import layout as LY
+from ..models.aeris import AerisConfig, AerisModel, StreamContext
+from .optim import FlatOptimizer, OptimConfig
+
+
+@dataclass
+class DiffusionConfig:
+    sigma_data: float = 1.0
+    sigma_min: float = 0.2
+    sigma_max: float = 500.0
+    w_lat_add: float = 0.01
+    noise_law: str = "loguniform"
+    cond_channels: int = 74
+    grad_scale_parity: bool = True   # reference sums local-mean gradients over WP ranks without dividing by WP
+
+
+def wp_grid_for(n: int) -> tuple[int, int]:
+    return {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4), 16: (4, 4)}[n]
+
+
+class Trainer:
+    def __init__(self, model_cfg: AerisConfig, optim_cfg: OptimConfig, diff_cfg: DiffusionConfig, device,
+                 seed: int = 1234, wp_group=None, dp_size: int = 1, dp_rank: int = 0, model: AerisModel | None = None):
+        self.cfg, self.ocfg, self.dcfg = model_cfg, optim_cfg, diff_cfg
+        self.device = torch.device(device)
+        self.wp_group = wp_group
+        self.wp_size = model_cfg.wp[0] * model_cfg.wp[1]
+        self.wp_rank = dist.get_rank(wp_group) if (self.wp_size > 1) else 0
+        self.dp_size, self.dp_rank = dp_size, dp_rank
+        torch.manual_seed(seed)   # identical initial weights on every rank
+        self.model = (model or AerisModel(model_cfg)).to(self.device)
+        self.opt = FlatOptimizer(self.model, optim_cfg)
+        self.grid = model_cfg.grid()
+        # noise: one stream per (wp rank, dp rank); noise level: one per dp replica, shared by its WP ranks
+        # (parallel_engine.py:119-120)
+        self.rng = torch.Generator(device=self.device)
+        self.rng.manual_seed(seed + 1000 * dp_rank + self.wp_rank)
+        self.nl_rng = torch.Generator(device=self.device)
+        self.nl_rng.manual_seed(seed + dp_rank)
+        self._ctx: dict[int, StreamContext] = {}
+        self._w_lat_tok = None
+        self._w_var = TF.variable_weights(model_cfg.out_channels, self.device)
+        self.halo = None
+        if self.wp_size > 1:
+            from ..parallel.symm import HaloExchange
+            self.halo = HaloExchange(wp_group, self.device)
+        self.timers: dict[str, float] = {}
+        self.last_norm = 0.0
+
+    # ------------------------------------------------------------------------------------------------ helpers
+    def context(self, batch: int) -> StreamContext:
+        if batch not in self._ctx:
+            peer_fn = self.halo.peer_fn if self.halo is not None else None
+            self._ctx[batch] = StreamContext(self.cfg, batch, self.wp_rank, peer_fn)
+        return self._ctx[batch]
+
+    def w_lat_tokens(self) -> torch.Tensor:
+        if self._w_lat_tok is None:
+            w = TF.latitude_weights(self.cfg.img[0], self.dcfg.w_lat_add)
+            img = w.view(1, -1, 1, 1).expand(1, self.cfg.img[0], self.cfg.img[1], 1)
+            self._w_lat_tok = LY.image_to_tokens(img, self.grid, (0, 0), self.wp_rank).to(self.device)
+        return self._w_lat_tok
+
+    def block_to_tokens(self, block: torch.Tensor) -> torch.Tensor:
+        """[B, H/wp_y, W/wp_x, C] block of this rank -> [B * tokens_per_rank, C] rows of the unshifted layout."""
+        B, hb, wb, C = block.shape
+        g = self.grid
+        x = block.view(B, g.nwy_loc, g.ws_y, g.nwx_loc, g.ws_x, C).permute(0, 1, 3, 2, 4, 5)
+        return x.reshape(B * g.tokens_per_rank, C)
+
+    def tokens_to_block(self, tok: torch.Tensor, B: int) -> torch.Tensor:
+        g = self.grid
+        C = tok.shape[-1]
+        x = tok.view(B, g.nwy_loc, g.nwx_loc, g.ws_y, g.ws_x, C).permute(0, 1, 3, 2, 4, 5)
+        return x.reshape(B, g.nwy_loc * g.ws_y, g.nwx_loc * g.ws_x, C)
+
+    # ------------------------------------------------------------------------------------------------ training
+    def loss_tokens(self, x_tok: torch.Tensor, cond_tok: torch.Tensor, t: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
+        """Sum over the local batch of the per-sample local-token-mean TrigFlow losses."""
+        B = t.shape[0]
+        rows = x_tok.shape[0] // B
+        ctx = self.context(B)
+        sd = self.dcfg.sigma_data
+        tr = t.repeat_interleave(rows)
+        model_in = TF.noise_inputs(x_tok, cond_tok, z, tr, sd)
+        pred = self.model.forward_tokens(model_in, t, ctx)
+        w_lat = self.w_lat_tokens().repeat(B, 1)
+        err = (sd * pred - TF.v_target(x_tok, z, tr)) ** 2 * self._w_var * w_lat
+        return err.sum(dim=-1).view(B, rows).mean(dim=1).sum()
+
+    def train_step(self, target_host: torch.Tensor, cond_host: torch.Tensor, read_loss: bool = True):
+        """One optimizer step on this rank's blocks of ``B`` samples. target_host: [B, H/wp_y, W/wp_x, C_out] fp32
+        (standardised residual), cond_host: [B, H/wp_y, W/wp_x, C_cond] fp32; both pinned host tensors.
+        Returns the loss averaged over the local batch (synchronises: the value is read back to the host)."""
+        dev = self.device
+        x = target_host.to(dev, non_blocking=True)
+        c = cond_host.to(dev, non_blocking=True)
+        B = x.shape[0]
+        x_tok, c_tok = self.block_to_tokens(x), self.block_to_tokens(c)
+        t = TF.sample_noise_level(B, self.dcfg.sigma_min, self.dcfg.sigma_max, self.dcfg.sigma_data,
+                                  generator=self.nl_rng, device=dev, law=self.dcfg.noise_law)
+        z = torch.randn(x_tok.shape, generator=self.rng, device=dev) * self.dcfg.sigma_data
+        loss = self.loss_tokens(x_tok, c_tok, t, z)
+        loss.backward()
+        self.reduce_and_step(B)
+        self.last_loss = loss.detach()
+        return float(self.last_loss.item()) / B if read_loss else None
+
+    def reduce_and_step(self, local_batch: int):
+        gas = local_batch
+        scale = 1.0 / (self.dp_size * gas)
+        if not self.dcfg.grad_scale_parity:
+            scale /= self.wp_size
+        if self.wp_size > 1 or self.dp_size > 1:
+            for buf in self.opt.grad_buffers():
+                dist.all_reduce(buf, group=self.wp_group)
+        nsq = self.opt.grad_norm_sq(scale) if self.ocfg.grad_clip else None
+        self.opt.step(batch_img=gas * self.dp_size, grad_scale=scale, norm_sq=nsq)
+        self._nsq = nsq
+
+    def grad_norm(self) -> float:
+        return float(self._nsq.sqrt().item()) if getattr(self, "_nsq", None) is not None else 0.0
+
+    # ------------------------------------------------------------------------------------------------ metrics
+    def flops_per_step(self, global_batch: int) -> float:
+        return self.cfg.flops_per_sample() * global_batch

@@ -22,6 +22,7 @@ from dataclasses import dataclass, field
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+import torch.utils.checkpoint
 
 from . import layout as LY
 from . import oracle as O
@@ -263,7 +264,12 @@ class OutputStage(nn.Module):
         for b in range(B):
             for r in range(0, rows, step):
                 sl = slice(b * rows + r, b * rows + min(rows, r + step))
-                outs.append(self.forward_rows(x[sl], shift[b:b + 1], scale[b:b + 1]))
+                if torch.is_grad_enabled() and x.requires_grad:
+                    # recompute in backward: the fp32 copies of a 65k x dim chunk are not kept alive
+                    outs.append(torch.utils.checkpoint.checkpoint(self.forward_rows, x[sl], shift[b:b + 1],
+                                                                  scale[b:b + 1], use_reentrant=False))
+                else:
+                    outs.append(self.forward_rows(x[sl], shift[b:b + 1], scale[b:b + 1]))
         return torch.cat(outs, dim=0)
 
 

@@ -52,5 +52,5 @@ def attn_bwd(qkv: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor, lse: torch.T
     rc = _l.lib().aeris_attn_bwd(_l.ptr(qkv), qkv.stride(0), 0, H * d, 2 * H * d, _l.ptr(o), _l.ptr(d_o),
                                  o.stride(0), _l.ptr(lse), _l.ptr(delta), _l.ptr(dqkv), dqkv.stride(0), n_win, N, H,
                                  d, _l._c_float(scale), _l.ptr(_l.status_word()), _l.stream_ptr())
-    _l.check(rc, "aeris_attn_bwd")
+    _l.check(rc, "aeris_attn_bwd", kernels=2)
     return dqkv

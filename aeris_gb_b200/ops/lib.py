@@ -70,6 +70,16 @@ def check_status(sync: bool = True) -> None:
         raise KernelError(f"device-side error {code}: {_ERR_NAMES.get(code, 'unknown')}")
 
 
-def check(rc: int, what: str) -> None:
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Number of native kernel launches issued through this module since import."""
+    return _LAUNCHES
+
+
+def check(rc: int, what: str, kernels: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += kernels
     if rc != 0:
         raise KernelError(f"{what} failed on the host side with code {rc}")
