@@ -256,21 +256,55 @@ class OutputStage(nn.Module):
 
     def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
         cfg = self.cfg
-        B = dt.shape[0]
         shift, scale = self.modulation(dt.to(cfg.data_dtype)).chunk(2, dim=1)
+        return _HeadFn.apply(x, shift, scale, self.norm.weight, self.head.weight, self)
+
+
+class _HeadFn(torch.autograd.Function):
+    """Output stage over a long token stream in 64k-row chunks. Only the (bf16) input is kept for the backward pass,
+    which recomputes each chunk in fp32 and writes the input gradient chunk by chunk into one preallocated buffer,
+    so no full-size fp32 copy of the stream ever exists."""
+    STEP = 1 << 16
+
+    @staticmethod
+    def forward(ctx, x, shift, scale, norm_w, head_w, stage):
+        B = shift.shape[0]
         rows = x.shape[0] // B
-        outs = []
-        step = 1 << 16
+        out = torch.empty((x.shape[0], head_w.shape[0]), dtype=head_w.dtype, device=x.device)
+        with torch.no_grad():
+            for b in range(B):
+                for r in range(0, rows, _HeadFn.STEP):
+                    sl = slice(b * rows + r, b * rows + min(rows, r + _HeadFn.STEP))
+                    out[sl] = stage.forward_rows(x[sl], shift[b:b + 1], scale[b:b + 1])
+        ctx.stage = stage
+        ctx.save_for_backward(x, shift, scale, norm_w, head_w)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, shift, scale, norm_w, head_w = ctx.saved_tensors
+        stage = ctx.stage
+        B = shift.shape[0]
+        rows = x.shape[0] // B
+        dx = torch.empty_like(x)
+        dshift, dscale = torch.zeros_like(shift), torch.zeros_like(scale)
+        dnw, dhw = torch.zeros_like(norm_w), torch.zeros_like(head_w)
         for b in range(B):
-            for r in range(0, rows, step):
-                sl = slice(b * rows + r, b * rows + min(rows, r + step))
-                if torch.is_grad_enabled() and x.requires_grad:
-                    # recompute in backward: the fp32 copies of a 65k x dim chunk are not kept alive
-                    outs.append(torch.utils.checkpoint.checkpoint(self.forward_rows, x[sl], shift[b:b + 1],
-                                                                  scale[b:b + 1], use_reentrant=False))
-                else:
-                    outs.append(self.forward_rows(x[sl], shift[b:b + 1], scale[b:b + 1]))
-        return torch.cat(outs, dim=0)
+            for r in range(0, rows, _HeadFn.STEP):
+                sl = slice(b * rows + r, b * rows + min(rows, r + _HeadFn.STEP))
+                with torch.enable_grad():
+                    xc = x[sl].detach().requires_grad_(True)
+                    sh = shift[b:b + 1].detach().requires_grad_(True)
+                    sc = scale[b:b + 1].detach().requires_grad_(True)
+                    y = stage.forward_rows(xc, sh, sc)
+                    gx, gsh, gsc, gnw, ghw = torch.autograd.grad(y, (xc, sh, sc, stage.norm.weight, stage.head.weight),
+                                                                 dout[sl])
+                dx[sl] = gx
+                dshift[b:b + 1] += gsh
+                dscale[b:b + 1] += gsc
+                dnw += gnw
+                dhw += ghw
+        return dx, dshift, dscale, dnw, dhw, None
 
 
 # ---------------------------------------------------------------------------------------------------- full model

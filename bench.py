@@ -19,6 +19,8 @@ import threading
 import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+# the flagship run fills most of the 180 GB; growable segments keep the caching allocator from fragmenting it
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 
 def reference_arm(args):
@@ -99,6 +101,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", default="full", choices=["full", "quarter", "tiny"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="override the number of Swin layers (development only)")
+    ap.add_argument("--chunk-windows", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -121,6 +125,10 @@ def main():
         group = dist.group.WORLD
 
     cfg = flagship_config(world, args.scale)
+    if args.layers:
+        cfg.n_layers = args.layers
+    if args.chunk_windows:
+        cfg.chunk_windows = args.chunk_windows
     W = max(args.warmup, 3)
     K = args.steps
     B = world                                   # global batch N, every sample split over the N WP ranks
