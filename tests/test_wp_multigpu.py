@@ -1,0 +1,21 @@
+"""Window-parallel parity on 2 and 4 GPUs: the peer-memory halo gather must reproduce the single-GPU result."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_wp_parity(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    worker = os.path.join(os.path.dirname(__file__), "wp_worker.py")
+    port = 29500 + n
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), worker],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
