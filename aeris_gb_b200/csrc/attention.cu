@@ -807,3 +807,33 @@ extern "C" int aeris_attn_bwd(const void* qkv, int ldq, int q_col0, int k_col0, 
   return head_dim == 64 ? launch_attn_bwd<1>(t128, t64, t64, d128, t64, t128, t128, d64, p, stream)
                         : launch_attn_bwd<2>(t128, t64, t64, d128, t64, t128, t128, d64, p, stream);
 }
+
+// ------------------------------------------------------------------------------------------ allocation-free variant
+// Same computation as aeris_attn_bwd, for hosts that must not allocate device memory at call time (declared and
+// described in noalloc.h). The `delta` scratch (one float per (window, head, token)) lives in this file-scope device
+// array instead of a caller-provided buffer. The array name is only a host-side handle: its device address is
+// looked up once per device with cudaGetSymbolAddress and that address is what the kernels receive.
+#include "noalloc.h"
+
+static __device__ __align__(256) float g_attn_delta_scratch[AERIS_NOALLOC_MAX_SCRATCH_FLOATS];
+static float* g_attn_delta_ptr[AERIS_NOALLOC_MAX_DEVICES] = {};
+
+extern "C" int aeris_attn_bwd_noalloc(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0, const void* o,
+                                      const void* d_o, int ldo, const float* lse, void* dqkv, int ldg, int n_win,
+                                      int N, int H, int head_dim, float scale, int* status, void* stream_) {
+  if (n_win <= 0 || N <= 0 || H <= 0) return AERIS_NOALLOC_ERR_BAD_SHAPE;
+  const long long need = static_cast<long long>(n_win) * H * N;
+  if (need > AERIS_NOALLOC_MAX_SCRATCH_FLOATS) return AERIS_NOALLOC_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= AERIS_NOALLOC_MAX_DEVICES)
+    return AERIS_NOALLOC_ERR_DEVICE;
+  if (g_attn_delta_ptr[dev] == nullptr) {
+    // one-time set-up for this device (which is current): resolve the device address of the scratch array
+    float* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_attn_delta_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return AERIS_NOALLOC_ERR_SYMBOL;
+    g_attn_delta_ptr[dev] = ptr;
+  }
+  return aeris_attn_bwd(qkv, ldq, q_col0, k_col0, v_col0, o, d_o, ldo, lse, g_attn_delta_ptr[dev], dqkv, ldg, n_win,
+                        N, H, head_dim, scale, status, stream_);
+}
