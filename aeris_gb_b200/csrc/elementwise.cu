@@ -69,12 +69,13 @@ __device__ __forceinline__ void block_sum(float (&v)[NRED], float* red, int pari
 // (modulate -> norm); mode 1: h = (RMSNorm(x)*w)*(1+scale)+shift (norm -> modulate). scale/shift may be null
 // (plain RMSNorm). With `gidx`, source row r comes from peers.p[gidx[r] >> 28] at row (gidx[r] & 0x0fffffff), and
 // the gathered row is also written to x_out.
+constexpr int FWD_RPI = 4;  // rows per iteration of one CTA: one block-wide reduction serves four rows
 __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ gidx,
                                    PeerPtrs peers, __nv_bfloat16* __restrict__ x_out,
                                    const float* __restrict__ scale, const float* __restrict__ shift,
                                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h, int rows,
                                    int D, int mode, float eps, int rows_per_cta) {
-  __shared__ float red[2 * 1 * 32];
+  __shared__ float red[2 * FWD_RPI * 32];
   const int c0 = threadIdx.x * 8;
   const bool active = c0 < D;
   float sc[8], sh[8], wv[8];
@@ -88,39 +89,48 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
   const int r0 = blockIdx.x * rows_per_cta;
   const int r1 = min(rows, r0 + rows_per_cta);
   int parity = 0;
-  for (int r = r0; r < r1; ++r, parity ^= 1) {
-    float v[8];
+  for (int r = r0; r < r1; r += FWD_RPI, parity ^= 1) {
+    float y[FWD_RPI][8];
+    float ss[FWD_RPI];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = 0.f;
-    if (active) {
-      const __nv_bfloat16* src;
-      if (gidx) {
-        const uint32_t code = gidx[r];
-        src = peers.p[code >> 28] + static_cast<size_t>(code & 0x0fffffffu) * D + c0;
-      } else {
-        src = x + static_cast<size_t>(r) * D + c0;
+    for (int k = 0; k < FWD_RPI; ++k) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      const int rr = r + k;
+      if (active && rr < r1) {
+        const __nv_bfloat16* src;
+        if (gidx) {
+          const uint32_t code = gidx[rr];
+          src = peers.p[code >> 28] + static_cast<size_t>(code & 0x0fffffffu) * D + c0;
+        } else {
+          src = x + static_cast<size_t>(rr) * D + c0;
+        }
+        load8(src, v);
+        if (x_out) store8(x_out + static_cast<size_t>(rr) * D + c0, v);
       }
-      load8(src, v);
-      if (x_out) store8(x_out + static_cast<size_t>(r) * D + c0, v);
-    }
-    float y[8];
-    float ss[1] = {0.f};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      y[i] = (mode == 0) ? fmaf(v[i], sc[i], v[i]) + sh[i] : v[i];
-      ss[0] += y[i] * y[i];
-    }
-    if (!active) ss[0] = 0.f;
-    block_sum<1>(ss, red, parity);
-    const float rinv = rsqrtf(ss[0] / D + eps);
-    if (active) {
-      float o[8];
+      ss[k] = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float n = y[i] * rinv * wv[i];
-        o[i] = (mode == 0) ? n : fmaf(n, sc[i], n) + sh[i];
+        y[k][i] = (mode == 0) ? fmaf(v[i], sc[i], v[i]) + sh[i] : v[i];
+        ss[k] += y[k][i] * y[k][i];
       }
-      store8(h + static_cast<size_t>(r) * D + c0, o);
+      if (!active || rr >= r1) ss[k] = 0.f;
+    }
+    block_sum<FWD_RPI>(ss, red, parity);
+#pragma unroll
+    for (int k = 0; k < FWD_RPI; ++k) {
+      const int rr = r + k;
+      if (active && rr < r1) {
+        const float rinv = rsqrtf(ss[k] / D + eps);
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float n = y[k][i] * rinv * wv[i];
+          o[i] = (mode == 0) ? n : fmaf(n, sc[i], n) + sh[i];
+        }
+        store8(h + static_cast<size_t>(rr) * D + c0, o);
+      }
     }
   }
 }
