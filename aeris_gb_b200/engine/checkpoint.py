@@ -1,0 +1,116 @@
+"""Checkpoint IO in the reference's on-disk format.
+
+Training writes one file per *logical* pipeline stage, ``checkpoint_PP{stage}.pth`` (plus ``it_{it}_checkpoint_PP{stage}
+.pth`` every 1000 iterations), each a dict with ``cur_nimg``, ``model_state_dict`` (device-dtype copy),
+``main_model_state_dict`` (fp32 master), ``optimizer_state_dict`` and ``ema_state_dict``
+(src/aeris/parallelism/parallel_engine.py:1119-1160). Files are loaded with ``weights_only=True``. Because files are
+per logical stage they do not depend on how many physical pipeline ranks wrote them.
+
+Inference reads the per-stage files into one monolithic model (``input_stage.* / layers.{i}.* / output_stage.*``),
+always from ``ema_state_dict`` (src/aeris_wp_inference/model.py:479-495).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+
+def _fname(directory, stage: int, it: int | None = None) -> str:
+    name = f"checkpoint_PP{stage}.pth" if it is None else f"it_{it}_checkpoint_PP{stage}.pth"
+    return os.path.join(directory, name)
+
+
+def save_stage_checkpoint(directory: str, module, opt, it: int | None = None) -> list[str]:
+    """``module``: a PipelineStage; ``opt``: FlatOptimizer built on it. Writes one file per logical stage it holds."""
+    os.makedirs(directory, exist_ok=True)
+    model_sd = module.logical_state_dicts()
+    master = module.logical_state_dicts({k: v for k, v in opt.master_state_dict().items()})
+    ema = module.logical_state_dicts({k: v for k, v in opt.ema_state_dict().items()}) if opt.cfg.use_ema else {}
+    osd = opt.state_dict()
+    exp_avg = module.logical_state_dicts(osd["exp_avg"])
+    exp_avg_sq = module.logical_state_dicts(osd["exp_avg_sq"])
+    written = []
+    for stage, sd in model_sd.items():
+        full_master = {k: v.detach().float().cpu().clone() for k, v in sd.items()}     # buffers and frozen params too
+        full_master.update({k: v.detach().cpu().clone() for k, v in master.get(stage, {}).items()})
+        ckpt = {
+            "cur_nimg": int(opt.cur_nimg),
+            "model_state_dict": {k: v.detach().cpu().clone() for k, v in sd.items()},
+            "main_model_state_dict": full_master,
+            "optimizer_state_dict": {"step": int(opt.step_count),
+                                     "exp_avg": {k: v.cpu() for k, v in exp_avg.get(stage, {}).items()},
+                                     "exp_avg_sq": {k: v.cpu() for k, v in exp_avg_sq.get(stage, {}).items()}},
+        }
+        if opt.cfg.use_ema:
+            full_ema = dict(full_master)
+            full_ema.update({k: v.detach().cpu().clone() for k, v in ema.get(stage, {}).items()})
+            ckpt["ema_state_dict"] = full_ema
+        path = _fname(directory, stage, it)
+        tmp = path + ".tmp"
+        torch.save(ckpt, tmp)
+        os.replace(tmp, path)       # a crash mid-write never leaves a truncated checkpoint under the final name
+        written.append(path)
+    return written
+
+
+def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
+    """Loads every logical stage of ``module``; returns False (and leaves everything untouched) if any file is
+    missing or unreadable, as the reference's training path does (:1143-1148)."""
+    if not directory:
+        return False
+    loaded = {}
+    for stage in module.stage_ids:
+        try:
+            loaded[stage] = torch.load(_fname(directory, stage), map_location="cpu", weights_only=True)
+        except Exception:
+            return False
+    model_sd, master, ema, m, v = {}, {}, {}, {}, {}
+    for stage, ck in loaded.items():
+        for k, t in ck["model_state_dict"].items():
+            model_sd[module.key_for(stage, k)] = t
+        for k, t in ck["main_model_state_dict"].items():
+            master[module.key_for(stage, k)] = t
+        for k, t in ck.get("ema_state_dict", {}).items():
+            ema[module.key_for(stage, k)] = t
+        for k, t in ck["optimizer_state_dict"]["exp_avg"].items():
+            m[module.key_for(stage, k)] = t
+        for k, t in ck["optimizer_state_dict"]["exp_avg_sq"].items():
+            v[module.key_for(stage, k)] = t
+    first = next(iter(loaded.values()))
+    # parameters are views of the optimizer's flat buffers, so loading the masters refreshes the model copies too;
+    # buffers and frozen parameters come from the model state dict
+    own = module.state_dict()
+    for k, t in model_sd.items():
+        if k in own and k not in master:
+            own[k].copy_(t)
+    opt.load_state_dict({"step": first["optimizer_state_dict"]["step"], "cur_nimg": first["cur_nimg"],
+                         "exp_avg": m, "exp_avg_sq": v}, master=master, ema=ema or None)
+    return True
+
+
+def convert_inference_checkpoint(path: str, n_logical: int, model, map_location="cpu", use_ema: bool = True,
+                                 strict: bool = True) -> dict:
+    """Per-stage files -> one state dict for :class:`AerisModel`, then ``model.load_state_dict``. Takes
+    ``ema_state_dict`` (or ``model_state_dict``). Keys the monolithic model does not have are skipped (the reference
+    drops ``latent_embed*`` and ``*.1.norm*`` the same way, model.py:483,488)."""
+    which = "ema_state_dict" if use_ema else "model_state_dict"
+    own = model.state_dict()
+    new = {}
+    for stage in range(n_logical):
+        ck = torch.load(_fname(path, stage), map_location=map_location, weights_only=True)
+        sd = ck[which] if which in ck else ck["model_state_dict"]
+        for k, t in sd.items():
+            if stage == 0:
+                key = f"input_stage.{k}"
+            elif stage == n_logical - 1:
+                key = f"output_stage.{k}"
+            else:
+                key = f"layers.{stage - 1}.{k}"
+            if key in own:
+                new[key] = t.to(own[key].dtype)
+    missing = [k for k in own if k not in new]
+    if strict:
+        assert not missing, f"checkpoint does not cover the model: missing {missing[:5]}..."
+    model.load_state_dict(new, strict=False)
+    return new

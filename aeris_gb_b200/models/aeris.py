@@ -82,8 +82,10 @@ class AerisConfig:
 class StreamContext:
     """Per-forward information the stage modules need about the token stream."""
 
-    def __init__(self, cfg: AerisConfig, batch: int, rank: int = 0, peer_fn=None):
+    def __init__(self, cfg: AerisConfig, batch: int, rank: int = 0, peer_fn=None, wp_group=None, sp_group=None):
         self.cfg = cfg
+        self.wp_group = wp_group      # torch.distributed group of the WP peers (CPU re-partition, result gathers)
+        self.sp_group = sp_group      # Ulysses sequence-parallel group, None when SP = 1
         self.grid = cfg.grid()
         self.batch = batch
         self.rank = rank
@@ -95,6 +97,29 @@ class StreamContext:
         if key not in self._tables:
             self._tables[key] = LY.gather_table(self.grid, src_shift, dst_shift, self.rank, self.batch).to(device)
         return self._tables[key]
+
+    def cpu_regroup(self, x: torch.Tensor, table_fwd: torch.Tensor, table_bwd: torch.Tensor) -> torch.Tensor:
+        """Multi-rank re-partition without peer memory (CPU / gloo runs): all-gather the WP ranks' rows, then index."""
+        return _AllGatherRegroup.apply(x, table_fwd, table_bwd, self.wp_group)
+
+
+class _AllGatherRegroup(torch.autograd.Function):
+    @staticmethod
+    def _run(x, table, group):
+        import torch.distributed as dist
+        world = dist.get_world_size(group)
+        bufs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(bufs, x.contiguous(), group=group)
+        return LY.apply_gather_reference(table, bufs)
+
+    @staticmethod
+    def forward(ctx, x, table_fwd, table_bwd, group):
+        ctx.table_bwd, ctx.group = table_bwd, group
+        return _AllGatherRegroup._run(x, table_fwd, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _AllGatherRegroup._run(g.contiguous(), ctx.table_bwd, ctx.group), None, None, None
 
 
 def use_fused(t: torch.Tensor) -> bool:

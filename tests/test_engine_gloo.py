@@ -1,0 +1,149 @@
+"""The pipeline engine on CPU ranks (gloo): PP / WP / DP / overlapped schedule / distributed optimizer all have to
+reproduce the single-process result; checkpoints written per logical stage reload into any pipeline split."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from aeris_gb_b200.engine.optim import OptimConfig
+from aeris_gb_b200.engine.pipeline import EngineConfig, ParallelEngine
+from aeris_gb_b200.engine.trainer import DiffusionConfig
+from aeris_gb_b200.models.aeris import AerisConfig
+from aeris_gb_b200.parallel.topology import ProcessGrid
+
+IMG, CH, CC = (16, 32), 6, 4
+
+
+def _cfg(wp=(1, 1)):
+    return AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=32, heads=2, head_dim=16,
+                       mlp_dim=64, n_layers=4, sublayers=1, model_dtype=torch.float32, wp=wp, norm_eps=1e-5)
+
+
+def _field(seed, C):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(1, IMG[0], IMG[1], C, generator=g)
+
+
+def _block(img, eng):
+    hb, wb = IMG[0] // eng.grid.WP_Y, IMG[1] // eng.grid.WP_X
+    return img[:, eng.c.wp_y * hb:(eng.c.wp_y + 1) * hb, eng.c.wp_x * wb:(eng.c.wp_x + 1) * wb].contiguous()
+
+
+def _sample_index(eng):
+    it, mb = divmod(eng.loads, eng.GAS)
+    return (it * eng.GAS + mb) * eng.grid.DP + eng.c.dp
+
+
+def _data_fn(eng):
+    i = _sample_index(eng)
+    return _block(_field(1000 + i, CC), eng), _block(_field(2000 + i, CH), eng)
+
+
+def _noise_fn(eng):
+    return _block(_field(3000 + _sample_index(eng), CH), eng)
+
+
+def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_dir, resume):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    grid = ProcessGrid(world, PP=PP, WP_Y=WP[0], WP_X=WP[1])
+    ecfg = EngineConfig(gas=gas, overlap_p2p=overlap, dist_optimizer=distopt, checkpoint_dir=ckpt_dir,
+                        checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5)
+    torch.manual_seed(0)
+    eng = ParallelEngine(_cfg(WP), OptimConfig(lr=0.5, eps=1.0, lr_rampup_img=0, grad_clip_max_norm=0.5, weight_decay=0.0),
+                         DiffusionConfig(grad_scale_parity=False, cond_channels=CC), ecfg, grid, rank, "cpu",
+                         data_fn=_data_fn, groups={} if world == 1 else None)
+    # identical initial weights regardless of the split: every logical stage is seeded by its own index
+    for st, sd in eng.module.logical_state_dicts().items():
+        g = torch.Generator().manual_seed(100 + st)
+        for k, v in sd.items():
+            if v.dtype.is_floating_point and "inv_freq" not in k:
+                v.copy_(torch.randn(v.shape, generator=g) * 0.1)
+    eng.opt = type(eng.opt)(eng.module, eng.ocfg, *([eng.groups.get("weight"), True] if distopt else []))
+    eng.noise_fn = _noise_fn
+    eng.t_fn = lambda e: torch.tensor([0.2 + 0.13 * (_sample_index(e) % 9)])
+    eng.keep_grads = True
+    if resume:
+        assert eng.load_checkpoint()
+        eng.loads = eng.opt.step_count * gas
+    losses = []
+    for _ in range(iters):
+        eng.exec_schedule()
+        losses.append(eng.tot_loss)
+    if ckpt_dir and not resume:
+        eng.save_checkpoint()
+    if eng.c.dp == 0 and eng.c.wp_y == 0 and eng.c.wp_x == 0:
+        torch.save({"sd": {st: {k: v.clone() for k, v in sd.items()} for st, sd in eng.module.logical_state_dicts().items()},
+                    "grads": eng.module.logical_state_dicts(eng.last_grads) if not distopt else {},
+                    "loss": losses, "norm": eng.total_norm}, os.path.join(out_dir, f"pp{eng.c.pp}.pt"))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _launch(world, **kw):
+    out = tempfile.mkdtemp()
+    port = 29600 + (os.getpid() + hash(tuple(sorted((k, str(v)) for k, v in kw.items())))) % 300
+    args = (world, port, kw["PP"], kw["WP"], kw["gas"], kw.get("overlap", False), kw.get("distopt", False),
+            kw["iters"], out, kw.get("ckpt_dir"), kw.get("resume", False))
+    if world == 1:
+        _run(0, *args)
+    else:
+        mp.spawn(_run, args=args, nprocs=world, join=True)
+    merged, loss, norm = {}, None, None
+    grads = {}
+    for f in sorted(os.listdir(out)):
+        d = torch.load(os.path.join(out, f), weights_only=True)
+        merged.update(d["sd"])
+        grads.update(d["grads"])
+        if d["loss"] and any(l != 0.0 for l in d["loss"]):
+            loss = d["loss"]
+        norm = d["norm"]
+    _launch.last_grads = grads
+    return merged, loss, norm
+
+
+def _assert_same(a, b, tol=2e-5):
+    assert a.keys() == b.keys()
+    for st in a:
+        for k in a[st]:
+            assert torch.allclose(a[st][k], b[st][k], atol=tol, rtol=1e-4), (st, k, (a[st][k] - b[st][k]).abs().max())
+
+
+@pytest.fixture(scope="module")
+def single():
+    return _launch(1, PP=1, WP=(1, 1), gas=4, iters=2)
+
+
+def test_pp3_matches_single_process(single):
+    sd, loss, norm = _launch(3, PP=3, WP=(1, 1), gas=4, iters=2)
+    _assert_same(sd, single[0])
+    assert loss == pytest.approx(single[1], rel=1e-4)
+    assert norm == pytest.approx(single[2], rel=1e-4)
+
+
+def test_pp2_overlapped_wp2_matches_single_process(single):
+    sd, loss, _ = _launch(4, PP=2, WP=(1, 2), gas=4, iters=2, overlap=True)
+    _assert_same(sd, single[0])
+    assert loss == pytest.approx(single[1], rel=1e-4)
+
+
+def test_dp2_distributed_optimizer_matches_single_process(single):
+    sd, _, _ = _launch(2, PP=1, WP=(1, 1), gas=2, iters=2, distopt=True)
+    _assert_same(sd, single[0])
+
+
+def test_checkpoint_roundtrip_across_pipeline_splits(single):
+    ck = tempfile.mkdtemp()
+    _launch(1, PP=1, WP=(1, 1), gas=4, iters=1, ckpt_dir=ck)
+    assert sorted(os.listdir(ck)) == [f"checkpoint_PP{i}.pth" for i in range(6)]
+    d = torch.load(os.path.join(ck, "checkpoint_PP1.pth"), weights_only=True)
+    assert set(d) == {"cur_nimg", "model_state_dict", "main_model_state_dict", "optimizer_state_dict", "ema_state_dict"}
+    assert "modulelist.0.1.to_qkv.weight" in d["model_state_dict"] and d["cur_nimg"] == 4
+    # resume the second iteration on a 2-stage pipeline: must land on the single-process 2-iteration weights
+    sd, _, _ = _launch(2, PP=2, WP=(1, 1), gas=4, iters=1, ckpt_dir=ck, resume=True)
+    _assert_same(sd, single[0])
