@@ -21,6 +21,21 @@ def _fname(directory, stage: int, it: int | None = None) -> str:
     return os.path.join(directory, name)
 
 
+def _integrity(ckpt: dict) -> dict:
+    """Per-tensor float64 sums of every state-dict section: an extra key that the reference's loaders ignore and that
+    lets :func:`load_stage_checkpoint` reject a file whose payload was damaged (torch.load does not verify it)."""
+    out = {}
+    sections = {n: ckpt.get(n, {}) for n in ("model_state_dict", "main_model_state_dict", "ema_state_dict")}
+    osd = ckpt.get("optimizer_state_dict", {})
+    sections["optimizer/exp_avg"] = osd.get("exp_avg", {})
+    sections["optimizer/exp_avg_sq"] = osd.get("exp_avg_sq", {})
+    for section, sd in sections.items():
+        for k, t in sd.items():
+            if torch.is_tensor(t) and t.dtype.is_floating_point:
+                out[f"{section}/{k}"] = float(torch.nan_to_num(t.double()).sum())
+    return out
+
+
 def save_stage_checkpoint(directory: str, module, opt, it: int | None = None) -> list[str]:
     """``module``: a PipelineStage; ``opt``: FlatOptimizer built on it. Writes one file per logical stage it holds."""
     os.makedirs(directory, exist_ok=True)
@@ -46,6 +61,7 @@ def save_stage_checkpoint(directory: str, module, opt, it: int | None = None) ->
             full_ema = dict(full_master)
             full_ema.update({k: v.detach().cpu().clone() for k, v in ema.get(stage, {}).items()})
             ckpt["ema_state_dict"] = full_ema
+        ckpt["integrity"] = _integrity(ckpt)
         path = _fname(directory, stage, it)
         tmp = path + ".tmp"
         torch.save(ckpt, tmp)
@@ -62,7 +78,13 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     loaded = {}
     for stage in module.stage_ids:
         try:
-            loaded[stage] = torch.load(_fname(directory, stage), map_location="cpu", weights_only=True)
+            ck = torch.load(_fname(directory, stage), map_location="cpu", weights_only=True)
+            if "integrity" in ck:
+                now = _integrity(ck)
+                for k, v in ck["integrity"].items():
+                    if not (abs(now.get(k, float("nan")) - v) <= 1e-9 * max(1.0, abs(v))):
+                        raise ValueError(f"checkpoint payload damaged: {k}")
+            loaded[stage] = ck
         except Exception:
             return False
     model_sd, master, ema, m, v = {}, {}, {}, {}, {}
@@ -81,8 +103,9 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     # parameters are views of the optimizer's flat buffers, so loading the masters refreshes the model copies too;
     # buffers and frozen parameters come from the model state dict
     own = module.state_dict()
+    managed = set(opt.master_state_dict().keys())
     for k, t in model_sd.items():
-        if k in own and k not in master:
+        if k in own and k not in managed:
             own[k].copy_(t)
     opt.load_state_dict({"step": first["optimizer_state_dict"]["step"], "cur_nimg": first["cur_nimg"],
                          "exp_avg": m, "exp_avg_sq": v}, master=master, ema=ema or None)
