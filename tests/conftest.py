@@ -24,3 +24,10 @@ def _status_clean(request):
 def rel_err(a, b):
     a, b = a.float(), b.float()
     return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+def free_port() -> int:
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]

@@ -87,7 +87,8 @@ def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_
 
 def _launch(world, **kw):
     out = tempfile.mkdtemp()
-    port = 29600 + (os.getpid() + hash(tuple(sorted((k, str(v)) for k, v in kw.items())))) % 300
+    from conftest import free_port
+    port = free_port()
     args = (world, port, kw["PP"], kw["WP"], kw["gas"], kw.get("overlap", False), kw.get("distopt", False),
             kw["iters"], out, kw.get("ckpt_dir"), kw.get("resume", False))
     if world == 1:

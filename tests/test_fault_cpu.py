@@ -34,7 +34,8 @@ def _worker(rank, world, port, out):
 
 def test_heartbeat_detects_a_silent_rank_between_steps():
     out = tempfile.mkdtemp()
-    mp.spawn(_worker, args=(3, 29871 + os.getpid() % 50, out), nprocs=3, join=True)
+    from conftest import free_port
+    mp.spawn(_worker, args=(3, free_port(), out), nprocs=3, join=True)
     r0 = open(os.path.join(out, "r0.txt")).read()
     r2 = open(os.path.join(out, "r2.txt")).read()
     assert "ranks [1]" in r0 and "ranks [1]" in r2
