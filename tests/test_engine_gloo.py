@@ -143,7 +143,8 @@ def test_checkpoint_roundtrip_across_pipeline_splits(single):
     _launch(1, PP=1, WP=(1, 1), gas=4, iters=1, ckpt_dir=ck)
     assert sorted(os.listdir(ck)) == [f"checkpoint_PP{i}.pth" for i in range(6)]
     d = torch.load(os.path.join(ck, "checkpoint_PP1.pth"), weights_only=True)
-    assert set(d) == {"cur_nimg", "model_state_dict", "main_model_state_dict", "optimizer_state_dict", "ema_state_dict"}
+    assert set(d) == {"cur_nimg", "model_state_dict", "main_model_state_dict", "optimizer_state_dict", "ema_state_dict",
+                      "integrity"}     # the five reference keys plus the payload check
     assert "modulelist.0.1.to_qkv.weight" in d["model_state_dict"] and d["cur_nimg"] == 4
     # resume the second iteration on a 2-stage pipeline: must land on the single-process 2-iteration weights
     sd, _, _ = _launch(2, PP=2, WP=(1, 1), gas=4, iters=1, ckpt_dir=ck, resume=True)
