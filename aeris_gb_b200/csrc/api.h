@@ -38,6 +38,16 @@ int aeris_adamw(float* master, float* grad, float* m, float* v, void* wbf16, flo
                 long long n, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
                 float grad_scale, float max_norm, float ema_beta, void* stream);
 
+int aeris_signal_barrier(const void* const* flag_ptrs, int rank, int world, unsigned epoch, int* status,
+                         double timeout_s, void* stream);
+int aeris_wait_flag(const void* flag, unsigned expected, int* status, double timeout_s, void* stream);
+int aeris_grad_reduce_scatter(const void* const* grad_ptrs, const void* mc_grad, int world, long long lo, long long n,
+                              float scale, float* out, double* sumsq, void* stream);
+int aeris_shard_adamw_allgather(float* master, const float* grad, float* m, float* v, float* ema,
+                                const void* const* param_ptrs, void* mc_params, int world, long long lo, long long n,
+                                const double* norm_sq, float lr, float beta1, float beta2, float eps,
+                                float weight_decay, int step, float max_norm, float ema_beta, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,7 +42,8 @@ def wp_grid_for(n: int) -> tuple[int, int]:
 
 class Trainer:
     def __init__(self, model_cfg: AerisConfig, optim_cfg: OptimConfig, diff_cfg: DiffusionConfig, device,
-                 seed: int = 1234, wp_group=None, dp_size: int = 1, dp_rank: int = 0, model: AerisModel | None = None):
+                 seed: int = 1234, wp_group=None, dp_size: int = 1, dp_rank: int = 0, model: AerisModel | None = None,
+                 fused_dp: bool | None = None, use_multicast: bool = True):
         self.cfg, self.ocfg, self.dcfg = model_cfg, optim_cfg, diff_cfg
         self.device = torch.device(device)
         self.wp_group = wp_group
@@ -51,7 +52,13 @@ class Trainer:
         self.dp_size, self.dp_rank = dp_size, dp_rank
         torch.manual_seed(seed)   # identical initial weights on every rank
         self.model = (model or AerisModel(model_cfg)).to(self.device)
-        self.opt = FlatOptimizer(self.model, optim_cfg)
+        # weight-group collectives: this library's peer-memory kernels (default on GPUs with > 1 rank) or NCCL
+        self.fused_dp = (self.wp_size > 1 and self.device.type == "cuda") if fused_dp is None else fused_dp
+        if self.fused_dp:
+            from .fused_dp import FusedShardedOptimizer
+            self.opt = FusedShardedOptimizer(self.model, optim_cfg, wp_group, self.device, use_multicast)
+        else:
+            self.opt = FlatOptimizer(self.model, optim_cfg)
         self.grid = model_cfg.grid()
         # noise: one stream per (wp rank, dp rank); noise level: one per dp replica, shared by its WP ranks
         # (parallel_engine.py:119-120)
@@ -133,6 +140,9 @@ class Trainer:
         scale = 1.0 / (self.dp_size * gas)
         if not self.dcfg.grad_scale_parity:
             scale /= self.wp_size
+        if self.fused_dp:
+            self._nsq = self.opt.reduce_and_step(gas * self.dp_size, scale)
+            return
         if self.wp_size > 1 or self.dp_size > 1:
             for buf in self.opt.grad_buffers():
                 dist.all_reduce(buf, group=self.wp_group)

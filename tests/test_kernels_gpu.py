@@ -166,3 +166,24 @@ def test_adamw_matches_torch():
     g = torch.randn(n, device=DEV)
     E.sumsq(g, nsq)
     assert abs(nsq.item() - g.double().pow(2).sum().item()) / nsq.item() < 1e-5
+
+
+def test_bounded_wait_times_out_and_leaves_the_context_usable():
+    """A device-side wait on a flag that nothing sets must give up after its limit and report it to the host."""
+    import ctypes
+    import time
+    from aeris_gb_b200.ops import lib as L
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    t0 = time.perf_counter()
+    rc = L.lib().aeris_wait_flag(L.ptr(flag), ctypes.c_uint(1), L.ptr(L.status_word()), ctypes.c_double(0.5),
+                                 L.stream_ptr())
+    assert rc == 0
+    with pytest.raises(L.KernelError, match="peer signal"):
+        L.check_status()
+    assert 0.4 < time.perf_counter() - t0 < 5.0
+    # the status word was cleared and the context still works
+    a = torch.ones(1024, device=DEV)
+    assert float((a * 2).sum()) == 2048.0
+    flag.fill_(1)
+    L.lib().aeris_wait_flag(L.ptr(flag), ctypes.c_uint(1), L.ptr(L.status_word()), ctypes.c_double(0.5), L.stream_ptr())
+    L.check_status()

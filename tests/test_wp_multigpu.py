@@ -19,3 +19,15 @@ def test_wp_parity(n):
                         "--master-addr", "127.0.0.1", "--master-port", str(port), worker],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("multicast", [0, 1])
+def test_fused_gradient_reduce_adamw_allgather(multicast):
+    n = 2
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    worker = os.path.join(os.path.dirname(__file__), "fused_dp_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29520 + multicast), worker, str(multicast)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
