@@ -375,7 +375,6 @@ class PipelineStageView:
         cur = st.entry_shift()
         for i in st.layer_ids:
             nxt = st.cfg.layer_shift(i)
-            x = st._regroup(x, cur, nxt, ctx)
+            x = st.layers[str(i)](x, dt, ctx, regroup=(cur, nxt))
             cur = nxt
-            x = st.layers[str(i)](x, dt, ctx)
         return x

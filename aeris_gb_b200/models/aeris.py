@@ -98,6 +98,20 @@ class StreamContext:
             self._tables[key] = LY.gather_table(self.grid, src_shift, dst_shift, self.rank, self.batch).to(device)
         return self._tables[key]
 
+    def regroup_unfused(self, x: torch.Tensor, src, dst) -> torch.Tensor:
+        """Stand-alone re-partition between two window layouts (oracle path, and the final return to the plain
+        layout before the output stage)."""
+        if src == dst:
+            return x
+        fwd, bwd = self.table(src, dst, x.device), self.table(dst, src, x.device)
+        if use_fused(x):
+            from . import fused
+            return fused.Regroup.apply(x, fwd, bwd, self.peer_fn)
+        if self.grid.n_ranks == 1:
+            _, row = LY.decode_table(fwd)
+            return x[row.to(x.device)]
+        return self.cpu_regroup(x, fwd, bwd)
+
     def cpu_regroup(self, x: torch.Tensor, table_fwd: torch.Tensor, table_bwd: torch.Tensor) -> torch.Tensor:
         """Multi-rank re-partition without peer memory (CPU / gloo runs): all-gather the WP ranks' rows, then index."""
         return _AllGatherRegroup.apply(x, table_fwd, table_bwd, self.wp_group)
@@ -235,10 +249,15 @@ class SwinLayer(nn.Module):
             ]) for _ in range(cfg.sublayers)
         ])
 
-    def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext, regroup=None) -> torch.Tensor:
+        """``regroup = (src_shift, dst_shift)``: the stream arrives in the ``src`` window layout and this layer works
+        in ``dst``. On the CUDA path the re-partition (with its halo exchange under WP) is fused into the first
+        block's modulate+norm kernel; the oracle path applies it as a separate gather."""
         cfg = self.cfg
         eps = cfg.eps(x.dtype)
-        for n1, attn, n2, ff, mod in self.modulelist:
+        if regroup is not None and regroup[0] == regroup[1]:
+            regroup = None
+        for j, (n1, attn, n2, ff, mod) in enumerate(self.modulelist):
             m = mod(dt.to(mod.modulation[-1].weight.dtype))
             if use_fused(x):
                 from . import fused
@@ -246,9 +265,15 @@ class SwinLayer(nn.Module):
                 meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.L, cfg.heads, cfg.head_dim,
                                        E.MODE_MOD_THEN_NORM if cfg.after_mod_norm else E.MODE_NORM_THEN_MOD,
                                        eps, cfg.chunk_windows)
+                rg = None
+                if j == 0 and regroup is not None:
+                    rg = (ctx.table(regroup[0], regroup[1], x.device), ctx.table(regroup[1], regroup[0], x.device),
+                          ctx.peer_fn)
                 x = fused.FusedBlock.apply(x, m, meta, n1.weight, attn.to_qkv.weight, attn.wo.weight, n2.weight,
-                                           ff.w1.weight, ff.w2.weight)
+                                           ff.w1.weight, ff.w2.weight, rg)
             else:
+                if j == 0 and regroup is not None:
+                    x = ctx.regroup_unfused(x, regroup[0], regroup[1])
                 p = {"n1": n1.weight, "to_qkv": attn.to_qkv.weight, "wo": attn.wo.weight, "n2": n2.weight,
                      "w1": ff.w1.weight, "w2": ff.w2.weight}
                 x = O.block_forward(x, m, p, n_win_per_sample=ctx.grid.windows_per_rank, L=ctx.grid.L,
@@ -343,27 +368,14 @@ class AerisModel(nn.Module):
         self.layers = nn.ModuleList([SwinLayer(cfg) for _ in range(cfg.n_layers)]).to(cfg.model_dtype)
         self.output_stage = OutputStage(cfg)
 
-    def regroup(self, x: torch.Tensor, src, dst, ctx: StreamContext) -> torch.Tensor:
-        if src == dst:
-            return x
-        fwd = ctx.table(src, dst, x.device)
-        bwd = ctx.table(dst, src, x.device)
-        if use_fused(x):
-            from . import fused
-            return fused.Regroup.apply(x, fwd, bwd, ctx.peer_fn)
-        assert ctx.grid.n_ranks == 1, "the CPU oracle runs single-rank (multi-rank layouts are tested separately)"
-        _, row = LY.decode_table(fwd)
-        return x[row.to(x.device)]
-
     def forward_tokens(self, x_tok: torch.Tensor, t: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
         x, dt = self.input_stage(x_tok, t, ctx)
         cur = (0, 0)
         for i, layer in enumerate(self.layers):
             nxt = self.cfg.layer_shift(i)
-            x = self.regroup(x, cur, nxt, ctx)
+            x = layer(x, dt, ctx, regroup=(cur, nxt))
             cur = nxt
-            x = layer(x, dt, ctx)
-        x = self.regroup(x, cur, (0, 0), ctx)
+        x = ctx.regroup_unfused(x, cur, (0, 0))
         return self.output_stage(x, dt, ctx)
 
     def forward(self, x_img: torch.Tensor, t: torch.Tensor) -> torch.Tensor:

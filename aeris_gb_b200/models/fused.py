@@ -68,8 +68,12 @@ def _chunks(meta: BlockMeta):
 
 
 def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv, wo, wn2, w1, w2,
-                  out: torch.Tensor | None = None) -> torch.Tensor:
-    """x: [B * n_win * L, D] bf16 window-major; mod: [B, 6D] fp32 (shift1, scale1, gate1, shift2, scale2, gate2)."""
+                  out: torch.Tensor | None = None, gather=None) -> torch.Tensor:
+    """x: [B * n_win * L, D] bf16 window-major; mod: [B, 6D] fp32 (shift1, scale1, gate1, shift2, scale2, gate2).
+
+    ``gather = (table, peer_ptrs, src)``: ``x`` is then an EMPTY buffer in this block's window layout; the first
+    modulate+norm kernel of every chunk pulls its rows through the table from ``src`` on this or a peer GPU (the
+    re-partition / halo exchange of a shifted layer) and writes them into ``x`` on the way."""
     T, D = x.shape
     B = mod.shape[0]
     F = w2.shape[1]
@@ -92,7 +96,12 @@ def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv
             r0 = b * rows_per_sample + w0 * meta.L
             n = nw * meta.L
             xc = x[r0:r0 + n]
-            E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h[:n])
+            if gather is not None:
+                table, peers, _src = gather
+                E.modnorm_fwd(None, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h[:n],
+                              gather_idx=table[r0:r0 + n], peer_ptrs=peers, x_out=xc, rows=n)
+            else:
+                E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h[:n])
             G.gemm(h[:n], wqkv, out=qkv[:n])
             A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n],
                        lse=lse[:n * meta.heads].view(nw, meta.heads, meta.L))
@@ -183,10 +192,22 @@ class FusedBlock(torch.autograd.Function):
     engine provides one, otherwise they are returned to autograd."""
 
     @staticmethod
-    def forward(ctx, x, mod, meta, wn1, wqkv, wo, wn2, w1, w2):
+    def forward(ctx, x, mod, meta, wn1, wqkv, wo, wn2, w1, w2, regroup=None):
+        """``regroup = (table_fwd, table_bwd, peer_fn)`` fuses the preceding window re-partition into this block: the
+        incoming stream ``x`` is in the previous layout (published to the WP peers when ``peer_fn`` is given) and the
+        first modulate+norm kernel gathers this block's rows from it."""
         ctx.meta = meta
+        ctx.regroup = regroup
+        if regroup is not None:
+            table_fwd, _, peer_fn = regroup
+            peers = peer_fn(x, "fwd") if peer_fn is not None else [x.data_ptr()]
+            xg = torch.empty((table_fwd.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+            y = block_forward(xg, mod.float(), meta, wn1, wqkv, wo, wn2, w1, w2, gather=(table_fwd, peers, x))
+            x = xg
+        else:
+            y = block_forward(x, mod.float(), meta, wn1, wqkv, wo, wn2, w1, w2)
         ctx.save_for_backward(x, mod, wn1, wqkv, wo, wn2, w1, w2)
-        return block_forward(x, mod.float(), meta, wn1, wqkv, wo, wn2, w1, w2)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -203,9 +224,15 @@ class FusedBlock(torch.autograd.Function):
                 ret[k] = grads[k]
         dy = dy.contiguous()
         dx, dmod = block_backward(x, mod.float(), dy, ctx.meta, wn1, wqkv, wo, wn2, w1, w2, grads, dx=dy)
+        if ctx.regroup is not None:
+            _, table_bwd, peer_fn = ctx.regroup
+            peers = peer_fn(dx, "bwd") if peer_fn is not None else [dx.data_ptr()]
+            back = torch.empty((table_bwd.numel(), dx.shape[1]), dtype=dx.dtype, device=dx.device)
+            E.gather_rows(table_bwd, peers, back)
+            dx = back
         out = [ret[k].to(params[k].dtype) if ret[k] is not None else None
                for k in ("n1", "to_qkv", "wo", "n2", "w1", "w2")]
-        return (dx, dmod.to(mod.dtype), None, *out)
+        return (dx, dmod.to(mod.dtype), None, *out, None)
 
 
 class Regroup(torch.autograd.Function):

@@ -63,16 +63,7 @@ class PipelineStage(nn.Module):
         return (0, 0) if self.has_output or not self.layer_ids else self.cfg.layer_shift(self.layer_ids[-1])
 
     def _regroup(self, x, src, dst, ctx: StreamContext):
-        if src == dst:
-            return x
-        fwd, bwd = ctx.table(src, dst, x.device), ctx.table(dst, src, x.device)
-        if use_fused(x):
-            from . import fused
-            return fused.Regroup.apply(x, fwd, bwd, ctx.peer_fn)
-        if ctx.grid.n_ranks == 1:
-            _, row = LY.decode_table(fwd)
-            return x[row.to(x.device)]
-        return ctx.cpu_regroup(x, fwd, bwd)
+        return ctx.regroup_unfused(x, src, dst)
 
     def forward(self, x: torch.Tensor, dt: torch.Tensor | None, t: torch.Tensor | None, ctx: StreamContext):
         """First stage: ``x`` = model input tokens [T, C_in] and ``t`` the noise levels; other stages: ``x`` = stream
@@ -84,9 +75,8 @@ class PipelineStage(nn.Module):
             cur = (0, 0)
         for i in self.layer_ids:
             nxt = self.cfg.layer_shift(i)
-            x = self._regroup(x, cur, nxt, ctx)
+            x = self.layers[str(i)](x, dt, ctx, regroup=(cur, nxt))
             cur = nxt
-            x = self.layers[str(i)](x, dt, ctx)
         if self.has_output:
             x = self._regroup(x, cur, (0, 0), ctx)
             x = self.output_stage(x, dt, ctx)
