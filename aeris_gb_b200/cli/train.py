@@ -1,0 +1,150 @@
+"""Training entry point.
+
+    python -m aeris_gb_b200.cli.train experiment=b200_1p3b_wp8 data.synthetic=true trainer.benchmark_steps=20
+    torchrun --nproc-per-node 8 -m aeris_gb_b200.cli.train experiment=b200_1p3b_wp8
+
+Same flow as the reference's Hydra main (src/aeris/train.py:66-358): bootstrap, seeds, dataset, channel wiring, engine,
+optimizer policy, warm-up probe, checkpoint load, data loader, main loop with TFLOP/s per GPU, periodic checkpoints.
+Overrides are ``key=value`` (dotted) like Hydra's. With ``model.PP = 1`` and ``model.SP = 1`` the single-node fused
+engine (:class:`Trainer`) runs the step; otherwise the pipeline engine (:class:`ParallelEngine`).
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+from ..data.samplers import InfiniteSampler
+from ..data.synthetic import SyntheticERA5
+from ..engine.checkpoint import load_stage_checkpoint, save_stage_checkpoint
+from ..engine.optim import FlatOptimizer
+from ..engine.pipeline import EngineConfig, ParallelEngine
+from ..engine.trainer import Trainer
+from ..parallel.topology import ProcessGrid
+from ..utils import config as C
+from ..utils.dist_setup import setup, teardown
+from ..utils.fault import StepWatchdog, check_finite
+from ..utils.io import log0
+from ..utils.timers import tflops_per_gpu, wandb_payload
+
+
+def build_dataset(cfg, mcfg, wp_rank, channels):
+    if cfg.data.get("synthetic", False) or not cfg.data.get("root"):
+        return SyntheticERA5(img=mcfg.img, cond_channels=channels["condition"], target_channels=channels["label"],
+                             wp=mcfg.wp, wp_rank=wp_rank, seed=int(cfg.seed))
+    from ..data.era5 import ERA5NRMDataset
+    ds = ERA5NRMDataset(cfg.data.dataset.root, cfg.data.root, interval=int(cfg.model.interval),
+                        channels=channels["dataset"])
+    ds.open_file(wp_rank[0], wp_rank[1], load_x=True, load_t=True, benchmark=bool(cfg.model.get("benchmark", False)))
+    return _ChannelsLast(ds)
+
+
+class _ChannelsLast(torch.utils.data.Dataset):
+    """ERA5 items are [C, H, W]; the engines take [H, W, C] blocks."""
+
+    def __init__(self, ds):
+        self.ds = ds
+
+    def __len__(self):
+        return len(self.ds)
+
+    def __getitem__(self, i):
+        x, t = self.ds[i]
+        return x.permute(1, 2, 0).contiguous(), t.permute(1, 2, 0).contiguous()
+
+
+def main(argv=None):
+    argv = list(sys.argv[1:] if argv is None else argv)
+    cfg = C.compose("train", argv)
+    rank, world, device = setup()
+    torch.manual_seed(int(cfg.seed) + rank)
+    mcfg, ocfg, dcfg = C.model_config(cfg), C.optim_config(cfg), C.diffusion_config(cfg)
+    if str(cfg.model.get("dtype", "bfloat16")) == "float32" or device.type == "cpu":
+        mcfg.model_dtype = torch.float32
+    channels = C.channel_counts(cfg)
+    PP, SP = int(cfg.model.get("PP", 1)), int(cfg.model.get("SP", 1))
+    gas = int(cfg.data.gas)
+    grid = ProcessGrid(world, PP=PP, SP=SP, WP_Y=mcfg.wp[0], WP_X=mcfg.wp[1])
+    log0(grid.describe())
+    c = grid.coords(rank)
+    ckpt_dir = cfg.model.get("checkpoint_dir")
+    if rank == 0 and ckpt_dir:
+        C.save_run_config(cfg, ckpt_dir)
+    ds = build_dataset(cfg, mcfg, (c.wp_y, c.wp_x), channels)
+    sampler = InfiniteSampler(ds, rank=c.dp, num_replicas=grid.DP, seed=int(cfg.seed))
+    loader = iter(torch.utils.data.DataLoader(ds, sampler=sampler, batch_size=1,
+                                              num_workers=0 if isinstance(ds, SyntheticERA5) else int(cfg.data.data_workers),
+                                              pin_memory=device.type == "cuda"))
+    steps = int(cfg.trainer.get("benchmark_steps", -1))
+    total_steps = steps if steps > 0 else max(1, int(cfg.trainer.total_kimg * 1000) // (gas * grid.DP))
+    watchdog = StepWatchdog()
+    wandb = None
+    if os.environ.get("WANDB_MODE", "disabled") != "disabled" and rank == 0:
+        try:
+            import wandb as _w
+            wandb = _w
+            wandb.init(project="aeris", config=cfg.to_dict())
+        except Exception:
+            wandb = None
+
+    if PP == 1 and SP == 1:
+        groups = grid.build_groups(rank, kinds=("wp",)) if world > 1 else {}
+        trainer = Trainer(mcfg, ocfg, dcfg, device, seed=int(cfg.seed), wp_group=groups.get("wp"),
+                          dp_size=grid.DP, dp_rank=c.dp)
+        if cfg.model.get("load") and ckpt_dir and isinstance(trainer.opt, FlatOptimizer):
+            if load_stage_checkpoint(ckpt_dir, trainer.model, trainer.opt, device):
+                log0(f"loaded a checkpoint from {ckpt_dir} at {trainer.opt.cur_nimg} images")
+        start = trainer.opt.cur_nimg // (gas * grid.DP)
+        for it in range(start, total_steps):
+            batch = [next(loader) for _ in range(gas)]
+            cond = torch.cat([b[0] for b in batch]).pin_memory() if device.type == "cuda" else torch.cat([b[0] for b in batch])
+            tgt = torch.cat([b[1] for b in batch]).pin_memory() if device.type == "cuda" else torch.cat([b[1] for b in batch])
+            t0 = time.perf_counter()
+            loss = trainer.train_step(tgt, cond)
+            dt = time.perf_counter() - t0
+            check_finite("loss", loss)
+            tf = tflops_per_gpu(mcfg.flops_per_sample(), gas * grid.DP, dt, world)
+            slow = watchdog.observe(dt)
+            log0(f"it {it} loss {loss:.5f} |g| {trainer.grad_norm():.4f} {dt:.3f} s/it {tf:.1f} TFLOP/s/GPU"
+                 + (" SLOW STEP" if slow else ""))
+            if wandb:
+                wandb.log(wandb_payload(it, trainer.opt.cur_nimg, tf, dt, loss, trainer.grad_norm(), trainer.opt.last_lr))
+            if ckpt_dir and not cfg.model.get("benchmark") and (it + 1) % 100 == 0 and rank == 0 \
+                    and isinstance(trainer.opt, FlatOptimizer):
+                save_stage_checkpoint(ckpt_dir, trainer.model, trainer.opt,
+                                      it=(it + 1) if (it + 1) % 1000 == 0 else None)
+    else:
+        ecfg = EngineConfig(gas=gas, overlap_p2p=bool(cfg.model.get("overlap_p2p_comms", False)),
+                            dist_optimizer=bool(cfg.model.get("dist_optimizer", False)),
+                            rs_grads=bool(cfg.model.get("rs_grads", True)), checkpoint_dir=ckpt_dir,
+                            benchmark=bool(cfg.model.get("benchmark", False)), seed=int(cfg.seed),
+                            init_policy={k: cfg.model.get(k) for k in
+                                         ("init_scale_test14", "init_scale_test15", "time_emb_init", "head_init_std",
+                                          "token_emb_init_std", "modulation_0_init", "modulation_2_init")
+                                         if cfg.model.get(k) is not None})
+
+        def data_fn(_eng):
+            cnd, tg = next(loader)
+            return cnd, tg
+        eng = ParallelEngine(mcfg, ocfg, dcfg, ecfg, grid, rank, device, data_fn=data_fn)
+        eng.warmup()
+        if cfg.model.get("load"):
+            eng.load_checkpoint()
+        for it in range(eng.cur_nimg // (gas * grid.DP), total_steps):
+            t0 = time.perf_counter()
+            timers = eng.exec_schedule()
+            dt = time.perf_counter() - t0
+            tf = tflops_per_gpu(mcfg.flops_per_sample(), gas * grid.DP, dt, world)
+            if eng.is_last_stage() and c.dp == 0 and c.wp_y == 0 and c.wp_x == 0 and c.sp == 0:
+                print(f"it {it} loss {eng.tot_loss:.5f} |g| {eng.total_norm:.4f} {dt:.3f} s/it {tf:.1f} TFLOP/s/GPU",
+                      flush=True)
+            if cfg.trainer.get("report_timings") and rank in grid.stage_heads():
+                print(c.pp, "times:", {k: round(v, 4) for k, v in timers.items()}, flush=True)
+    teardown()
+
+
+if __name__ == "__main__":
+    main()

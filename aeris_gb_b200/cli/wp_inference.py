@@ -1,0 +1,156 @@
+"""WP-only autoregressive ensemble inference.
+
+    torchrun --nproc-per-node 8 -m aeris_gb_b200.cli.wp_inference --checkpoint DIR --WP-Y 2 --WP-X 4 --members 4
+    torchrun --nproc-per-node 8 -m aeris_gb_b200.cli.wp_inference --checkpoint DIR --member-parallel --members 8
+
+Reference: src/aeris_wp_inference/inference.py (argparse CLI :24-41, rollout :43-198, mesh [DP, SP=WP] :215-231,
+checkpoint conversion :281, strided initial conditions :302-314). Two layouts: every member window-parallel over all
+GPUs (the reference's), or one member per GPU (``--member-parallel``: no halo traffic at all, members are independent
+until the metrics). The state stays on the device for the whole rollout. Without ``--data`` synthetic N(0,1) initial
+states and forcings are used, and with ``--random-init`` random weights (benchmarking without a checkpoint).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..data.sharding import gather_blocks, shard_block
+from ..diffusion.rollout import Forecaster, SamplerConfig
+from ..diffusion import trigflow as TF
+from ..engine.checkpoint import convert_inference_checkpoint
+from ..eval.metrics import EnsembleMetrics
+from ..models import layout as LY
+from ..models.aeris import AerisModel, StreamContext
+from ..parallel.symm import HaloExchange
+from ..utils import config as C
+from ..utils.dist_setup import setup, teardown
+from ..utils.io import print0
+
+
+def parse(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--checkpoint", default=None)
+    ap.add_argument("--experiment", default="b200_wp_inference")
+    ap.add_argument("--WP-Y", type=int, default=1)
+    ap.add_argument("--WP-X", type=int, default=1)
+    ap.add_argument("--member-parallel", action="store_true")
+    ap.add_argument("--members", type=int, default=1)
+    ap.add_argument("--rollout-steps", type=int, default=None)
+    ap.add_argument("--sampler-steps", type=int, default=None)
+    ap.add_argument("--stride-ic", type=int, default=1)
+    ap.add_argument("--data", default=None, help="monolithic test file [T, 73, 721, 1440]")
+    ap.add_argument("--data-root", default=None)
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--random-init", action="store_true")
+    ap.add_argument("--no-ema", action="store_true")
+    ap.add_argument("--euler", action="store_true")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--debug", action="store_true")
+    ap.add_argument("overrides", nargs="*")
+    return ap.parse_args(argv)
+
+
+def main(argv=None):
+    a = parse(argv)
+    rank, world, device = setup()
+    if a.checkpoint and os.path.exists(os.path.join(a.checkpoint, ".hydra", "config.yaml")):
+        cfg = C.load_run_config(a.checkpoint)
+    else:
+        cfg = C.compose("train", [f"experiment={a.experiment}"] + list(a.overrides))
+    wp = (1, 1) if a.member_parallel else (a.WP_Y, a.WP_X)
+    cfg.model.WP_Y, cfg.model.WP_X = wp
+    mcfg = C.model_config(cfg)
+    if device.type == "cpu":
+        mcfg.model_dtype = torch.float32
+    n_wp = wp[0] * wp[1]
+    assert world % n_wp == 0
+    dp = world // n_wp
+    dp_rank, wp_rank = rank // n_wp, rank % n_wp
+    wp_group = None
+    if n_wp > 1:
+        for d in range(dp):
+            g = dist.new_group(list(range(d * n_wp, (d + 1) * n_wp)))
+            if d == dp_rank:
+                wp_group = g
+    torch.manual_seed(a.seed)
+    model = AerisModel(mcfg).to(device).eval()
+    if a.checkpoint and not a.random_init:
+        convert_inference_checkpoint(a.checkpoint, mcfg.n_layers + 2, model, use_ema=not a.no_ema, strict=False)
+    halo = HaloExchange(wp_group, device) if (n_wp > 1 and device.type == "cuda") else None
+    grid = mcfg.grid()
+    H, W = mcfg.img
+    hb, wb = H // wp[0], W // wp[1]
+    C_out = mcfg.out_channels
+    C_f = mcfg.in_channels - 2 * C_out
+    steps = a.rollout_steps or int(cfg.model.get("rollout_steps", 4))
+    sampler = SamplerConfig(n_steps=a.sampler_steps or int(cfg.model.get("sampler_steps", 20)),
+                            sigma_min=cfg.model.sigma_min, sigma_max=cfg.model.sigma_max,
+                            sigma_data=cfg.model.sigma_data, heun=not a.euler)
+    # members handled by this rank: all of them when window-parallel, a strided subset when member-parallel
+    my_members = list(range(dp_rank, a.members, dp)) if a.member_parallel else list(range(a.members))
+    M = len(my_members)
+    ctx = StreamContext(mcfg, max(M, 1), wp_rank, halo.peer_fn if halo else None, wp_group=wp_group)
+
+    def denoise(model_in, t):
+        B = model_in.shape[0]
+        tok = model_in.reshape(B * hb * wb, -1)
+        g = grid
+        tok = model_in.view(B, g.nwy_loc, g.ws_y, g.nwx_loc, g.ws_x, -1).permute(0, 1, 3, 2, 4, 5).reshape(B * g.tokens_per_rank, -1)
+        out = model.forward_tokens(tok, t, ctx)
+        out = out.view(B, g.nwy_loc, g.nwx_loc, g.ws_y, g.ws_x, -1).permute(0, 1, 3, 2, 4, 5)
+        return out.reshape(B, hb, wb, -1).float()
+
+    stats = {k: torch.zeros(C_out, device=device) if "mean" in k else torch.ones(C_out, device=device)
+             for k in ("x_mean", "x_std", "t_mean", "t_std")}
+    gen = torch.Generator(device=device).manual_seed(a.seed * 1000 + rank)
+    fc = Forecaster(denoise, stats, sampler, C_out)
+    w_lat = TF.latitude_weights(H, float(cfg.model.get("w_lat_add", 0.0))).to(device)
+    w_lat_blk = w_lat.view(wp[0], hb)[wp_rank // wp[1]]
+    metrics = EnsembleMetrics(steps, C_out, H * W, device, group=wp_group)
+    g0 = torch.Generator().manual_seed(a.seed)
+    state_full = torch.randn(H, W, C_out, generator=g0)
+    truth_full = [torch.randn(H, W, C_out, generator=g0) for _ in range(steps)] if a.debug else None
+    state = shard_block(state_full.unsqueeze(0), wp, (wp_rank // wp[1], wp_rank % wp[1])).to(device).repeat(max(M, 1), 1, 1, 1)
+    forcing = torch.randn(max(M, 1), hb, wb, C_f, generator=gen, device=device) if C_f > 0 else None
+    times = []
+
+    def on_step(k, x):
+        if device.type == "cuda":
+            torch.cuda.synchronize()
+        times.append(time.perf_counter())
+        if a.member_parallel and world > 1:
+            allm = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(allm, x)
+            mem = torch.cat(allm).permute(0, 3, 1, 2)
+        else:
+            mem = x.permute(0, 3, 1, 2)
+        label = (truth_full[k] if truth_full is not None else state_full)
+        label = shard_block(label.unsqueeze(0), wp, (wp_rank // wp[1], wp_rank % wp[1]))[0].to(device).permute(2, 0, 1)
+        metrics.update(k, mem, label, w_lat_blk)
+
+    t_start = time.perf_counter()
+    times.append(t_start)
+    if M > 0:
+        fc.rollout(state, (lambda k: forcing), steps, generator=gen, on_step=on_step)
+    metrics.end_initial_condition()
+    agg, scores = metrics.finalize()
+    per_step = float(np.mean(np.diff(times))) if len(times) > 1 else float("nan")
+    if a.out and rank == 0:
+        os.makedirs(a.out, exist_ok=True)
+        np.save(os.path.join(a.out, "rollout_err_aggregate.npy"), agg)
+        np.save(os.path.join(a.out, "rollout_err.npy"), scores)
+    print0(json.dumps({"entry": "wp_inference", "world": world, "wp": list(wp), "member_parallel": a.member_parallel,
+                       "members": a.members, "rollout_steps": steps, "sampler_steps": sampler.n_steps,
+                       "model_evals_per_step": fc.model_evals_per_forecast_step(), "s_per_forecast_step": per_step,
+                       "rmse_t2m_first_step": float(scores[0, 0, 0])}))
+    teardown()
+
+
+if __name__ == "__main__":
+    main()

@@ -9,7 +9,7 @@ from torch.utils.data import Dataset
 
 class SyntheticERA5(Dataset):
     def __init__(self, img=(720, 1440), cond_channels=74, target_channels=70, wp=(1, 1), wp_rank=(0, 0),
-                 length: int = 1 << 30, seed: int = 0, pool: int = 4, channels_last: bool = True):
+                 length: int = 4096, seed: int = 0, pool: int = 4, channels_last: bool = True):
         self.hb, self.wb = img[0] // wp[0], img[1] // wp[1]
         self.cc, self.ct, self.length, self.seed, self.pool = cond_channels, target_channels, length, seed, pool
         self.rank_id = wp_rank[0] * wp[1] + wp_rank[1]

@@ -21,6 +21,38 @@ def _fname(directory, stage: int, it: int | None = None) -> str:
     return os.path.join(directory, name)
 
 
+def _n_logical(module) -> int:
+    return module.cfg.n_layers + 2
+
+
+def _stage_ids(module) -> list[int]:
+    return list(getattr(module, "stage_ids", range(_n_logical(module))))
+
+
+def _key_for(module, stage: int, key: str) -> str:
+    if stage == 0:
+        return f"input_stage.{key}"
+    if stage == _n_logical(module) - 1:
+        return f"output_stage.{key}"
+    return f"layers.{stage - 1}.{key}"
+
+
+def _logical(module, sd: dict) -> dict[int, dict]:
+    """Splits a state dict with ``input_stage.* / layers.{i}.* / output_stage.*`` keys (PipelineStage and AerisModel
+    both use them) into one dict per logical pipeline stage with the reference's per-stage key names."""
+    out: dict[int, dict] = {}
+    last = _n_logical(module) - 1
+    for k, v in sd.items():
+        if k.startswith("input_stage."):
+            out.setdefault(0, {})[k[len("input_stage."):]] = v
+        elif k.startswith("output_stage."):
+            out.setdefault(last, {})[k[len("output_stage."):]] = v
+        elif k.startswith("layers."):
+            _, idx, rest = k.split(".", 2)
+            out.setdefault(int(idx) + 1, {})[rest] = v
+    return out
+
+
 def _integrity(ckpt: dict) -> dict:
     """Per-tensor float64 sums of every state-dict section: an extra key that the reference's loaders ignore and that
     lets :func:`load_stage_checkpoint` reject a file whose payload was damaged (torch.load does not verify it)."""
@@ -37,14 +69,15 @@ def _integrity(ckpt: dict) -> dict:
 
 
 def save_stage_checkpoint(directory: str, module, opt, it: int | None = None) -> list[str]:
-    """``module``: a PipelineStage; ``opt``: FlatOptimizer built on it. Writes one file per logical stage it holds."""
+    """``module``: a PipelineStage or a whole AerisModel; ``opt``: FlatOptimizer built on it. Writes one file per
+    logical stage the module holds."""
     os.makedirs(directory, exist_ok=True)
-    model_sd = module.logical_state_dicts()
-    master = module.logical_state_dicts({k: v for k, v in opt.master_state_dict().items()})
-    ema = module.logical_state_dicts({k: v for k, v in opt.ema_state_dict().items()}) if opt.cfg.use_ema else {}
+    model_sd = _logical(module, module.state_dict())
+    master = _logical(module, dict(opt.master_state_dict()))
+    ema = _logical(module, dict(opt.ema_state_dict())) if opt.cfg.use_ema else {}
     osd = opt.state_dict()
-    exp_avg = module.logical_state_dicts(osd["exp_avg"])
-    exp_avg_sq = module.logical_state_dicts(osd["exp_avg_sq"])
+    exp_avg = _logical(module, osd["exp_avg"])
+    exp_avg_sq = _logical(module, osd["exp_avg_sq"])
     written = []
     for stage, sd in model_sd.items():
         full_master = {k: v.detach().float().cpu().clone() for k, v in sd.items()}     # buffers and frozen params too
@@ -76,7 +109,7 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     if not directory:
         return False
     loaded = {}
-    for stage in module.stage_ids:
+    for stage in _stage_ids(module):
         try:
             ck = torch.load(_fname(directory, stage), map_location="cpu", weights_only=True)
             if "integrity" in ck:
@@ -90,15 +123,15 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     model_sd, master, ema, m, v = {}, {}, {}, {}, {}
     for stage, ck in loaded.items():
         for k, t in ck["model_state_dict"].items():
-            model_sd[module.key_for(stage, k)] = t
+            model_sd[_key_for(module, stage, k)] = t
         for k, t in ck["main_model_state_dict"].items():
-            master[module.key_for(stage, k)] = t
+            master[_key_for(module, stage, k)] = t
         for k, t in ck.get("ema_state_dict", {}).items():
-            ema[module.key_for(stage, k)] = t
+            ema[_key_for(module, stage, k)] = t
         for k, t in ck["optimizer_state_dict"]["exp_avg"].items():
-            m[module.key_for(stage, k)] = t
+            m[_key_for(module, stage, k)] = t
         for k, t in ck["optimizer_state_dict"]["exp_avg_sq"].items():
-            v[module.key_for(stage, k)] = t
+            v[_key_for(module, stage, k)] = t
     first = next(iter(loaded.values()))
     # parameters are views of the optimizer's flat buffers, so loading the masters refreshes the model copies too;
     # buffers and frozen parameters come from the model state dict
