@@ -23,7 +23,9 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
 
-enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GATE_RESID = 2, EPI_ACC_F32 = 3, EPI_STORE_F32 = 4 };
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GATE_RESID = 2, EPI_ACC_F32 = 3, EPI_STORE_F32 = 4,
+              EPI_SWIGLU_BOTH = 5,   // EPI_SWIGLU that also stores the raw [gate | up] product to aux [M, 2F]
+              EPI_SWIGLU_BWD = 6 };  // acc = d(act); reads u = [gate | up] from resid [M, 2F], writes d(u) to C [M, 2F]
 
 struct GemmParams {
   int M, N, K;
@@ -39,6 +41,7 @@ struct GemmParams {
   int b_tile_stride;           // rows of B advanced per n-tile (BN, or BN/2 for SwiGLU)
   int b_half_off;              // row offset of the second half-box of B (BN/2, or F for SwiGLU)
   int k_splits;
+  int swiglu_f;                // F for the SwiGLU epilogues
   int* status;
 };
 
@@ -202,9 +205,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       const bool kempty = (split * kb_per_split) >= kb_total;  // split with no k-blocks: accumulator undefined
 
-      if (p.epi == EPI_SWIGLU) {
+      if (p.epi == EPI_SWIGLU_BWD) {
+        // d(gate) = d(act) * up * dsilu(gate), d(up) = d(act) * silu(gate); u is read and d(u) written in place
+        const __nv_bfloat16* usrc = p.resid + static_cast<size_t>(row) * p.ldr + tn * BN;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c, v);
+          tmem_wait_ld();
+          if (row_ok) {
+            uint32_t og[16], ou[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 g4 = *reinterpret_cast<const uint4*>(usrc + c + 8 * i);
+              const uint4 u4 = *reinterpret_cast<const uint4*>(usrc + p.swiglu_f + c + 8 * i);
+              const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 g2 = unpack_bf16x2(gw[j]), u2 = unpack_bf16x2(uw[j]);
+                const float d0 = __uint_as_float(v[8 * i + 2 * j]), d1 = __uint_as_float(v[8 * i + 2 * j + 1]);
+                const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+                const float si0 = g2.x * s0, si1 = g2.y * s1;
+                og[4 * i + j] = pack_bf16x2(d0 * u2.x * (s0 + si0 * (1.f - s0)), d1 * u2.y * (s1 + si1 * (1.f - s1)));
+                ou[4 * i + j] = pack_bf16x2(d0 * si0, d1 * si1);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(og[4 * i], og[4 * i + 1], og[4 * i + 2], og[4 * i + 3]);
+              *reinterpret_cast<uint4*>(dst + p.swiglu_f + c + 8 * i) =
+                  make_uint4(ou[4 * i], ou[4 * i + 1], ou[4 * i + 2], ou[4 * i + 3]);
+            }
+          }
+        }
+      } else if (p.epi == EPI_SWIGLU || p.epi == EPI_SWIGLU_BOTH) {
         constexpr int H = BN / 2;
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * H;
+        __nv_bfloat16* raw = (p.epi == EPI_SWIGLU_BOTH) ? p.aux + static_cast<size_t>(row) * p.ld_aux + tn * H : nullptr;
 #pragma unroll 1
         for (int c = 0; c < H; c += 32) {
           uint32_t g[32], u[32];
@@ -212,6 +250,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tmem_ld32(taddr + H + c, u);
           tmem_wait_ld();
           if (row_ok) {
+            if (raw) {
+              uint32_t rg[16], ru[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                rg[i] = pack_bf16x2(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
+                ru[i] = pack_bf16x2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                *reinterpret_cast<uint4*>(raw + c + 8 * i) = make_uint4(rg[4 * i], rg[4 * i + 1], rg[4 * i + 2], rg[4 * i + 3]);
+                *reinterpret_cast<uint4*>(raw + p.swiglu_f + c + 8 * i) =
+                    make_uint4(ru[4 * i], ru[4 * i + 1], ru[4 * i + 2], ru[4 * i + 3]);
+              }
+            }
             uint32_t o[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -416,7 +468,8 @@ extern "C" int aeris_gemm_bf16(const void* A, const void* B, void* C, int M, int
   if (M <= 0 || N <= 0 || K <= 0) return -1;
   if (bn != 128 && bn != 256) bn = (N % 256 == 0) ? 256 : 128;
   if (N % bn != 0) return -2;
-  if (epi == EPI_SWIGLU && b_mn) return -3;
+  const bool swiglu_fwd = (epi == EPI_SWIGLU || epi == EPI_SWIGLU_BOTH);
+  if (swiglu_fwd && b_mn) return -3;
   if (k_splits < 1) k_splits = 1;
   if (k_splits > 1 && epi != EPI_ACC_F32) return -4;
   GemmParams p{};
@@ -424,8 +477,8 @@ extern "C" int aeris_gemm_bf16(const void* A, const void* B, void* C, int M, int
   p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.ldr = ldr;
   p.gate = gate; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : M;
   p.aux = reinterpret_cast<__nv_bfloat16*>(aux); p.ld_aux = ld_aux;
-  p.k_splits = k_splits; p.status = status;
-  if (epi == EPI_SWIGLU) {
+  p.k_splits = k_splits; p.status = status; p.swiglu_f = swiglu_f;
+  if (swiglu_fwd) {
     // N counts gate+up columns (2F); a tile holds bn/2 gate columns and the matching bn/2 up columns.
     p.b_tile_stride = bn / 2;
     p.b_half_off = swiglu_f;
@@ -439,7 +492,7 @@ extern "C" int aeris_gemm_bf16(const void* A, const void* B, void* C, int M, int
   else       r = make_tmap_2d_bf16(&ta, A, M, K, lda, 64, BK);
   if (r) return r;
   if (!b_mn) {
-    const uint64_t brows = (epi == EPI_SWIGLU) ? static_cast<uint64_t>(2) * swiglu_f : static_cast<uint64_t>(N);
+    const uint64_t brows = swiglu_fwd ? static_cast<uint64_t>(2) * swiglu_f : static_cast<uint64_t>(N);
     r = make_tmap_2d_bf16(&tb, B, K, brows, ldb, BK, bn / 2);
   } else {
     r = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);

@@ -131,7 +131,6 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
     lse = ws.get("lse", (cmax * meta.heads,), f32, dev)
     h2 = ws.get("h2", (cmax, D), bf, dev)
     u = ws.get("u", (cmax, 2 * F), bf, dev)
-    dact = ws.get("dact", (cmax, F), bf, dev)
     dh = ws.get("dh", (cmax, D), bf, dev)
     dx1 = ws.get("dx1", (cmax, D), bf, dev)
     d_o = ws.get("d_o", (cmax, HD), bf, dev)
@@ -162,12 +161,11 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
             A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n], lse=lse_c)
             G.gemm(o[:n], wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
             E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=h2[:n])
-            G.gemm(h2[:n], w1, out=u[:n])
-            E.swiglu_fwd(u[:n], out=act[:n])
+            G.gemm(h2[:n], w1, out=act[:n], epi=G.EPI_SWIGLU_BOTH, aux=u[:n])         # act and the raw [gate | up]
             # ---- MLP half: y = x1 + g2 * (act @ w2^T)
-            G.gemm(dyc, w2g, b_t=True, out=dact[:n])                                   # dact = (dy * g2) @ w2
             G.gemm(dyc, act[:n], a_t=True, b_t=True, out=G2, epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
-            E.swiglu_bwd(u[:n], dact[:n], du=u[:n])                                    # du overwrites u
+            # dact = (dy * g2) @ w2 never reaches memory: the epilogue turns it into du, overwriting u
+            G.gemm(dyc, w2g, b_t=True, out=u[:n], epi=G.EPI_SWIGLU_BWD, resid=u[:n])
             G.gemm(u[:n], w1, b_t=True, out=dh[:n])                                    # dh2 = du @ w1
             G.gemm(u[:n], h2[:n], a_t=True, b_t=True, out=grads["w1"], epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
             E.modnorm_bwd(x1[:n], dh[:n], dyc, sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, dx=dx1[:n],

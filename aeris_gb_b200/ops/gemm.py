@@ -5,7 +5,7 @@ import torch
 
 from . import lib as _l
 
-EPI_STORE, EPI_SWIGLU, EPI_GATE_RESID, EPI_ACC_F32, EPI_STORE_F32 = range(5)
+EPI_STORE, EPI_SWIGLU, EPI_GATE_RESID, EPI_ACC_F32, EPI_STORE_F32, EPI_SWIGLU_BOTH, EPI_SWIGLU_BWD = range(7)
 
 
 def _ld(t: torch.Tensor) -> int:
@@ -23,7 +23,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
 
     epi: EPI_STORE bf16 out; EPI_SWIGLU ``silu(acc[:, :F]) * acc[:, F:]`` (b = [2F, K]) -> ``[M, F]``;
     EPI_GATE_RESID ``resid + gate * acc`` (gate fp32 ``[M // rows_per_gate, N]``; ``aux`` optionally receives the
-    raw product); EPI_ACC_F32 ``out += acc`` in fp32 (split-K allowed); EPI_STORE_F32 fp32 out.
+    raw product); EPI_ACC_F32 ``out += acc`` in fp32 (split-K allowed); EPI_STORE_F32 fp32 out;
+    EPI_SWIGLU_BOTH = EPI_SWIGLU that also writes the raw ``[gate | up]`` product to ``aux [M, 2F]``;
+    EPI_SWIGLU_BWD: the product is d(act) ``[M, F]``, ``resid`` holds ``u = [gate | up]`` and ``out`` receives d(u).
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     if a_t:
@@ -37,14 +39,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     assert K == Kb, (a.shape, b.shape, a_t, b_t)
     swiglu_f = 0
     n_out = N
-    if epi == EPI_SWIGLU:
+    if epi in (EPI_SWIGLU, EPI_SWIGLU_BOTH):
         assert N % 2 == 0 and not b_t
         swiglu_f = N // 2
         n_out = swiglu_f
+        assert epi == EPI_SWIGLU or (aux is not None and aux.shape == (M, N))
+    if epi == EPI_SWIGLU_BWD:
+        # acc = d(act) [M, F]; resid = u [M, 2F]; out = d(u) [M, 2F] (may alias resid)
+        assert resid is not None and out is not None and resid.shape == (M, 2 * N) and out.shape == (M, 2 * N)
+        swiglu_f = N
     if out is None:
         dt = torch.float32 if epi in (EPI_ACC_F32, EPI_STORE_F32) else torch.bfloat16
         out = (torch.zeros if epi == EPI_ACC_F32 else torch.empty)((M, n_out), dtype=dt, device=a.device)
-    assert out.shape == (M, n_out)
+    assert out.shape == (M, n_out) or epi == EPI_SWIGLU_BWD
     if bn == 0:
         bn = 256 if N % 256 == 0 else 128
     rc = _l.lib().aeris_gemm_bf16(

@@ -44,6 +44,16 @@ def test_gemm_epilogues(M, N, K):
     F = N // 2
     sref = torch.nn.functional.silu(ref[:, :F]) * ref[:, F:]
     assert rel_err(G.gemm(a, b, epi=G.EPI_SWIGLU), sref) < TOL
+    raw = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    act = G.gemm(a, b, epi=G.EPI_SWIGLU_BOTH, aux=raw)
+    assert rel_err(act, sref) < TOL and rel_err(raw, ref) < TOL
+    # fused SwiGLU backward: product = d(act) [M, F], u given, d(u) out (in place)
+    u = torch.randn(M, 2 * N, device=DEV).bfloat16()
+    ur = u.float().requires_grad_(True)
+    (torch.nn.functional.silu(ur[:, :N]) * ur[:, N:]).backward(ref)
+    du = u.clone()
+    G.gemm(a, b, out=du, epi=G.EPI_SWIGLU_BWD, resid=du)
+    assert rel_err(du, ur.grad) < TOL
     x = torch.randn(M, N, device=DEV).bfloat16()
     g = torch.randn(1, N, device=DEV)
     aux = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
