@@ -38,39 +38,51 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 // -------------------------------------------------------------------------------------------------------- forward
-// grid = (q_tiles, H, n_win). One CTA owns a 128-row Q tile and streams the window's K/V in 128-row tiles.
-// TMEM: S [128 x 128] fp32, O_part[2] [128 x d] fp32 (fresh P V product per tile; the running output lives in
-// registers so that no TMEM read-modify-write is needed for the online-softmax rescale).
+// grid = (q_tiles, H, n_win). One CTA owns a 128-row Q tile and streams the window's K/V in 64-row tiles through a
+// three-stage TMA ring. S = Q K^T is double buffered in TMEM, so the tensor core computes the scores of tile j+1 while
+// the four softmax warps (one thread per query row) work on tile j; each tile's 64 scores are read from TMEM once
+// and stay in registers for the exact row maximum, the exponentials and the bf16 probabilities that go back to shared
+// memory (double buffered) as the A operand of P V. The P V product of every tile lands in one of two TMEM buffers
+// and is folded into the register-resident running output with the online-softmax rescale.
+constexpr int KVT = 64;
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int DCH>
 __global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
   constexpr int HD = 64 * DCH;
   constexpr int Q_BYTES = DCH * 16384;
-  constexpr int KV_BYTES = 2 * DCH * 16384;  // K tile + V tile
-  constexpr int P_BYTES = 32768;
+  constexpr int KV_BYTES = 2 * DCH * 8192;  // K tile + V tile (64 rows each)
+  constexpr int NST = 3;
+  constexpr int P_BYTES = 16384;            // [128 x 64] bf16
   constexpr int TMEM_COLS = (DCH == 1) ? 256 : 512;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Q_BYTES;
-  uint8_t* sP = sKV + 2 * KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint8_t* sP = sKV + NST * KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * P_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_full = bars + 6;
-  uint64_t* o_full = bars + 7;    // [2]
-  uint64_t* o_free = bars + 9;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* kv_full = bars + 1;    // [3]
+  uint64_t* kv_empty = bars + 4;   // [3]
+  uint64_t* s_full = bars + 7;     // [2]
+  uint64_t* p_full = bars + 9;     // [2]
+  uint64_t* o_full = bars + 11;    // [2]
+  uint64_t* o_free = bars + 13;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, head = blockIdx.y, win = blockIdx.z;
   const int N = p.N;
-  const int nfull = N / TILE, rem = N - nfull * TILE;
+  const int nfull = N / KVT, rem = N - nfull * KVT;
   const int nkv = nfull + (rem ? 1 : 0);
-  const int n_last = rem ? ((rem + 15) & ~15) : TILE;  // MMA N of the last K/V tile
+  const int n_last = rem ? ((rem + 15) & ~15) : KVT;  // MMA N of the last K/V tile
 
   if (threadIdx.x == 0) {
     int ab = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -86,12 +98,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
     mbar_init(q_full, 1);
+    for (int i = 0; i < NST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
-      mbar_init(&o_full[i], 1);  mbar_init(&o_free[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4);
+      mbar_init(&o_full[i], 1); mbar_init(&o_free[i], 4);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -99,8 +110,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base;
-  const uint32_t tO0 = tmem_base + 128;
+  const uint32_t tS0 = tmem_base;          // S[2] : 2 x 64 columns
+  const uint32_t tO0 = tmem_base + 128;    // O_part[2] : 2 x HD columns
 
   if (warp == 0) {
     if (elect_one_sync()) {
@@ -108,50 +119,60 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < DCH; ++c)
         tma_load_3d(sQ + c * 16384, &tm_q, q_full, p.q_col0 + head * HD + c * 64, qt * TILE, win);
+      int st = 0;
+      uint32_t ph = 0;
       for (int j = 0; j < nkv; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
-        uint8_t* sK = sKV + s * KV_BYTES;
-        uint8_t* sV = sK + DCH * 16384;
-        mbar_expect_tx(&kv_full[s], KV_BYTES);
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
+        uint8_t* sK = sKV + st * KV_BYTES;
+        uint8_t* sV = sK + DCH * 8192;
+        mbar_expect_tx(&kv_full[st], KV_BYTES);
 #pragma unroll
         for (int c = 0; c < DCH; ++c) {
-          tma_load_3d(sK + c * 16384, &tm_k, &kv_full[s], p.k_col0 + head * HD + c * 64, j * TILE, win);
-          tma_load_3d(sV + c * 16384, &tm_v, &kv_full[s], p.v_col0 + head * HD + c * 64, j * TILE, win);
+          tma_load_3d(sK + c * 8192, &tm_k, &kv_full[st], p.k_col0 + head * HD + c * 64, j * KVT, win);
+          tma_load_3d(sV + c * 8192, &tm_v, &kv_full[st], p.v_col0 + head * HD + c * 64, j * KVT, win);
         }
+        if (++st == NST) { st = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (elect_one_sync()) {
       bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_ATTN);
-      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
-      for (int j = 0; j < nkv && ok; ++j) {
-        const int s = j & 1;
-        const int ncur = (j == nkv - 1) ? n_last : TILE;
-        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aKV = smem_u32(sKV);
+      // S[j & 1] = Q K_j^T  (A = Q K-major, B = K K-major, reduction over d)
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j % NST;
+        if (!mbar_wait(&kv_full[st], (j / NST) & 1, p.status, ERR_TIMEOUT_ATTN)) return false;
         tc_fence_after();
-        const uint32_t aK = smem_u32(sKV + s * KV_BYTES), aV = aK + DCH * 16384;
-        // S = Q K^T  (A = Q K-major, B = K K-major, reduction over d)
+        const int ncur = (j == nkv - 1) ? n_last : KVT;
+        const uint32_t aK = aKV + st * KV_BYTES;
         const uint32_t idesc_qk = make_idesc_bf16(TILE, ncur, 0, 0);
 #pragma unroll
         for (int kk = 0; kk < 4 * DCH; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(tS, make_smem_desc(aQ + off, 0, 1024), make_smem_desc(aK + off, 0, 1024), idesc_qk, kk > 0);
+          const uint32_t qoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t koff = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(tS0 + (j & 1) * 64, make_smem_desc(aQ + qoff, 0, 1024), make_smem_desc(aK + koff, 0, 1024),
+                  idesc_qk, kk > 0);
         }
-        tc_commit(s_full);
-        // O_part = P V  (A = P K-major over kv, B = V MN-major: d contiguous, kv rows strided)
-        if (!mbar_wait(p_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
-        if (!mbar_wait(&o_free[j & 1], ((j >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_commit(&s_full[j & 1]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      if (ok && nkv > 1) ok = issue_qk(1);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int b = j & 1, st = j % NST;
+        const int ncur = (j == nkv - 1) ? n_last : KVT;
+        if (!mbar_wait(&p_full[b], (j >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        if (!mbar_wait(&o_free[b], ((j >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
         tc_fence_after();
+        // O_part[b] = P_j V_j  (A = P K-major over kv, B = V MN-major: d contiguous, kv rows strided)
+        const uint32_t aV = aKV + st * KV_BYTES + DCH * 8192;
         const uint32_t idesc_pv = make_idesc_bf16(TILE, HD, 0, 1);
-        const uint32_t tO = tO0 + (j & 1) * HD;
-        for (int kk = 0; kk < ncur / 16; ++kk) {
-          const uint32_t poff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(tO, make_smem_desc(aP + poff, 0, 1024), make_smem_desc(aV + kk * 2048, 16384, 1024), idesc_pv,
-                  kk > 0);
-        }
-        tc_commit(&o_full[j & 1]);
-        tc_commit(&kv_empty[s]);
+        for (int kk = 0; kk < ncur / 16; ++kk)
+          umma_ss(tO0 + b * HD, make_smem_desc(aP + b * P_BYTES + kk * 32, 0, 1024),
+                  make_smem_desc(aV + kk * 2048, 8192, 1024), idesc_pv, kk > 0);
+        tc_commit(&o_full[b]);
+        tc_commit(&kv_empty[st]);
+        if (j + 2 < nkv) ok = issue_qk(j + 2);   // S[b] is free: the softmax warps signalled p_full[b] after reading it
       }
     }
   } else {
@@ -160,101 +181,114 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int grow = qt * TILE + row;         // row inside the window
     const bool warp_valid = (qt * TILE + q * 32) < N;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const float sl2 = p.scale_log2;
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
     float acc[HD];
 #pragma unroll
     for (int i = 0; i < HD; ++i) acc[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < nkv && ok; ++j) {
+      const int b = j & 1;
       const bool last = (j == nkv - 1);
-      const int ncur = last ? n_last : TILE;
-      const int valid = (last && rem) ? rem : TILE;
-      if (!mbar_wait(s_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      if (!mbar_wait(&s_full[b], (j >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
       tc_fence_after();
       float alpha = 1.f;
+      uint8_t* sPb = sP + b * P_BYTES;
       if (warp_valid) {
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < ncur; c += 32) {
-          if (ncur - c >= 32) {
-            uint32_t v[32];
-            tmem_ld32(tS + lane_addr + c, v);
-            tmem_wait_ld();
+        if (!last || rem == 0) {
+          // full 64-column tile: one TMEM read, scores stay in registers
+          uint32_t v0[32], v1[32];
+          tmem_ld32(tS0 + b * 64 + lane_addr, v0);
+          tmem_ld32(tS0 + b * 64 + lane_addr + 32, v1);
+          tmem_wait_ld();
+          float mx = max3(__uint_as_float(v0[0]), __uint_as_float(v0[1]), __uint_as_float(v1[0]));
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
-          } else {
+          for (int i = 1; i < 16; ++i) {
+            mx = max3(mx, __uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
+            mx = max3(mx, __uint_as_float(v1[2 * i - 1]), __uint_as_float(v1[2 * i]));
+          }
+          mx = fmaxf(mx, __uint_as_float(v1[31]));
+          const float m_new = fmaxf(m, mx * sl2);
+          alpha = fast_exp2(m - m_new);  // first tile: exp2(-inf) = 0
+          float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(v0[8 * g + 2 * i]), sl2, -m_new));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(v0[8 * g + 2 * i + 1]), sl2, -m_new));
+              rs0 += p0; rs1 += p1;
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+            *reinterpret_cast<uint4*>(sPb + swz128(row, g)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(v1[8 * g + 2 * i]), sl2, -m_new));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(v1[8 * g + 2 * i + 1]), sl2, -m_new));
+              rs0 += p0; rs1 += p1;
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+            *reinterpret_cast<uint4*>(sPb + swz128(row, 4 + g)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+          l = l * alpha + (rs0 + rs1);
+          m = m_new;
+        } else {
+          // last, partial tile: n_last (multiple of 16) columns computed, `rem` of them valid
+          float mx = -INFINITY;
+#pragma unroll 1
+          for (int c = 0; c < n_last; c += 16) {
             uint32_t v[16];
-            tmem_ld16(tS + lane_addr + c, v);
+            tmem_ld16(tS0 + b * 64 + lane_addr + c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-              if (c + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+              if (c + i < rem) mx = fmaxf(mx, __uint_as_float(v[i]));
           }
-        }
-        const float m_new = fmaxf(m, mx * p.scale_log2);
-        alpha = fast_exp2(m - m_new);  // first tile: exp2(-inf) = 0
-        float rs = 0.f;
+          const float m_new = fmaxf(m, mx * sl2);
+          alpha = fast_exp2(m - m_new);
+          float rs = 0.f;
 #pragma unroll 1
-        for (int c = 0; c < ncur; c += 32) {
-          uint32_t pk[16];
-          if (ncur - c >= 32) {
-            uint32_t v[32];
-            tmem_ld32(tS + lane_addr + c, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -m_new));
-              float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_new));
-              if (c + 2 * i >= valid) p0 = 0.f;
-              if (c + 2 * i + 1 >= valid) p1 = 0.f;
-              rs += p0 + p1;
-              pk[i] = pack_bf16x2(p0, p1);
-            }
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = c + g * 8;
-              uint8_t* dst = sP + (col >> 6) * 16384 + swz128(row, (col & 63) >> 3);
-              *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
-            }
-          } else {
-            uint32_t v[16];
-            tmem_ld16(tS + lane_addr + c, v);
+          for (int c = 0; c < n_last; c += 16) {
+            uint32_t v[16], pk[8];
+            tmem_ld16(tS0 + b * 64 + lane_addr + c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -m_new));
-              float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_new));
-              if (c + 2 * i >= valid) p0 = 0.f;
-              if (c + 2 * i + 1 >= valid) p1 = 0.f;
+              float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), sl2, -m_new));
+              float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sl2, -m_new));
+              if (c + 2 * i >= rem) p0 = 0.f;
+              if (c + 2 * i + 1 >= rem) p1 = 0.f;
               rs += p0 + p1;
               pk[i] = pack_bf16x2(p0, p1);
             }
 #pragma unroll
-            for (int g = 0; g < 2; ++g) {
-              const int col = c + g * 8;
-              uint8_t* dst = sP + (col >> 6) * 16384 + swz128(row, (col & 63) >> 3);
-              *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
-            }
+            for (int g = 0; g < 2; ++g)
+              *reinterpret_cast<uint4*>(sPb + swz128(row, (c >> 3) + g)) =
+                  make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
           }
+          l = l * alpha + rs;
+          m = m_new;
         }
-        l = l * alpha + rs;
-        m = m_new;
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[b]);
       // fold in the previous tile's P V product
       if (j > 0) {
-        const int b = (j - 1) & 1;
-        if (!mbar_wait(&o_full[b], ((j - 1) >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        const int pb = (j - 1) & 1;
+        if (!mbar_wait(&o_full[pb], ((j - 1) >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
         tc_fence_after();
         if (warp_valid) {
 #pragma unroll
           for (int c = 0; c < HD; c += 32) {
             uint32_t v[32];
-            tmem_ld32(tO0 + b * HD + lane_addr + c, v);
+            tmem_ld32(tO0 + pb * HD + lane_addr + c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(acc[c + i], alpha_prev, __uint_as_float(v[i]));
@@ -262,19 +296,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&o_free[b]);
+        if (lane == 0) mbar_arrive(&o_free[pb]);
       }
       alpha_prev = alpha;
     }
     if (ok) {
-      const int b = (nkv - 1) & 1;
-      if (mbar_wait(&o_full[b], ((nkv - 1) >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) {
+      const int pb = (nkv - 1) & 1;
+      if (mbar_wait(&o_full[pb], ((nkv - 1) >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) {
         tc_fence_after();
         if (warp_valid) {
 #pragma unroll
           for (int c = 0; c < HD; c += 32) {
             uint32_t v[32];
-            tmem_ld32(tO0 + b * HD + lane_addr + c, v);
+            tmem_ld32(tO0 + pb * HD + lane_addr + c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(acc[c + i], alpha_prev, __uint_as_float(v[i]));
@@ -307,7 +341,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 template <int DCH>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const AttnFwdParams& p, cudaStream_t stream) {
-  constexpr int SMEM = DCH * 16384 + 2 * 2 * DCH * 16384 + 32768 + 128;
+  constexpr int SMEM = DCH * 16384 + 3 * 2 * DCH * 8192 + 2 * 16384 + 256;
   static bool configured = false;
   auto kern = attn_fwd_kernel<DCH>;
   if (!configured) {
@@ -779,8 +813,8 @@ extern "C" int aeris_attn_fwd(const void* q, int ldq, int q_col0, const void* k,
   CUtensorMap tq, tk, tv;
   int r;
   if ((r = make_tmap_3d_bf16(&tq, q, ldq, N, n_win, ldq, static_cast<uint64_t>(N) * ldq, 64, TILE))) return r;
-  if ((r = make_tmap_3d_bf16(&tk, k, ldk, N, n_win, ldk, static_cast<uint64_t>(N) * ldk, 64, TILE))) return r;
-  if ((r = make_tmap_3d_bf16(&tv, v, ldv, N, n_win, ldv, static_cast<uint64_t>(N) * ldv, 64, TILE))) return r;
+  if ((r = make_tmap_3d_bf16(&tk, k, ldk, N, n_win, ldk, static_cast<uint64_t>(N) * ldk, 64, KVT))) return r;
+  if ((r = make_tmap_3d_bf16(&tv, v, ldv, N, n_win, ldv, static_cast<uint64_t>(N) * ldv, 64, KVT))) return r;
   return head_dim == 64 ? launch_attn_fwd<1>(tq, tk, tv, p, stream) : launch_attn_fwd<2>(tq, tk, tv, p, stream);
 }
 
