@@ -375,6 +375,15 @@ struct AttnBwdParams {
 };
 constexpr int BT = 64;  // streamed tile rows in the backward kernels
 
+// Both backward kernels stream 64-row tiles but run the tensor core and the math warps at a granularity of 32 score
+// columns ("halves"), double buffered in TMEM: while the math warps turn half g into dS (and P), the tensor core is
+// already computing the scores of half g+1, and the accumulating products of half g are issued as soon as its
+// operands are in shared memory. Half g uses buffer g & 1; only the last streamed tile can have a single half.
+__device__ __forceinline__ int half_cols(int g, int n_tiles, int n_last) {
+  const int j = g >> 1, h = g & 1;
+  return (j == n_tiles - 1) ? min(32, n_last - 32 * h) : 32;
+}
+
 template <int DCH>
 __global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 2 : 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -384,20 +393,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   constexpr int QB = DCH * 16384;       // Q tile, dO tile (128 rows)
   constexpr int KB = DCH * 8192;        // K tile, V tile (64 rows)
   constexpr int STAGE = 2 * KB;
+  constexpr int NST = 3;
   constexpr int TMEM_COLS = 256;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + QB;
   uint8_t* sKV = sdO + QB;
-  uint8_t* sdS = sKV + 2 * STAGE;  // [128 x 64] bf16
+  uint8_t* sdS = sKV + NST * STAGE;  // [128 x 64] bf16
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 16384);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 3;
-  uint64_t* sp_full = bars + 5;
-  uint64_t* ds_full = bars + 6;
-  uint64_t* dq_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* kv_full = bars + 1;    // [3]
+  uint64_t* kv_empty = bars + 4;   // [3]
+  uint64_t* sp_full = bars + 7;    // [2]
+  uint64_t* ds_full = bars + 9;    // [2]
+  uint64_t* dq_full = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -406,6 +416,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int nfull = N / BT, rem = N - nfull * BT;
   const int nkv = nfull + (rem ? 1 : 0);
   const int n_last = rem ? ((rem + 15) & ~15) : BT;
+  const int G = 2 * (nkv - 1) + (n_last > 32 ? 2 : 1);   // number of halves
 
   if (threadIdx.x == 0) {
     int ab = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -417,8 +428,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (threadIdx.x == 0) {
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    mbar_init(sp_full, 1); mbar_init(ds_full, 4); mbar_init(dq_full, 1);
+    for (int i = 0; i < NST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sp_full[i], 1); mbar_init(&ds_full[i], 4); }
+    mbar_init(dq_full, 1);
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -426,7 +438,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tdQ = tmem_base + 128;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tdQ = tmem_base + 128;   // S[2] and dP[2]: 32 columns each
 
   if (warp == 0) {
     if (elect_one_sync()) {
@@ -436,51 +448,66 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tma_load_3d(sQ + c * 16384, &tm_q, q_full, p.q_col0 + head * HD + c * 64, qt * TILE, win);
         tma_load_3d(sdO + c * 16384, &tm_do, q_full, head * HD + c * 64, qt * TILE, win);
       }
+      int st = 0;
+      uint32_t ph = 0;
       for (int j = 0; j < nkv; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
-        uint8_t* sK = sKV + s * STAGE;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
+        uint8_t* sK = sKV + st * STAGE;
         uint8_t* sV = sK + KB;
-        mbar_expect_tx(&kv_full[s], STAGE);
+        mbar_expect_tx(&kv_full[st], STAGE);
 #pragma unroll
         for (int c = 0; c < DCH; ++c) {
-          tma_load_3d(sK + c * 8192, &tm_k, &kv_full[s], p.k_col0 + head * HD + c * 64, j * BT, win);
-          tma_load_3d(sV + c * 8192, &tm_v, &kv_full[s], p.v_col0 + head * HD + c * 64, j * BT, win);
+          tma_load_3d(sK + c * 8192, &tm_k, &kv_full[st], p.k_col0 + head * HD + c * 64, j * BT, win);
+          tma_load_3d(sV + c * 8192, &tm_v, &kv_full[st], p.v_col0 + head * HD + c * 64, j * BT, win);
         }
+        if (++st == NST) { st = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (elect_one_sync()) {
       bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_ATTN);
-      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), adS = smem_u32(sdS);
-      for (int j = 0; j < nkv && ok; ++j) {
-        const int s = j & 1;
-        const int ncur = (j == nkv - 1) ? n_last : BT;
-        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), adS = smem_u32(sdS), aKV = smem_u32(sKV);
+      // S[h] = Q K[32h..]^T and dP[h] = dO V[32h..]^T for half g
+      auto issue_sp = [&](int g) -> bool {
+        const int j = g >> 1, h = g & 1, st = j % NST;
+        if (h == 0 && !mbar_wait(&kv_full[st], (j / NST) & 1, p.status, ERR_TIMEOUT_ATTN)) return false;
         tc_fence_after();
-        const uint32_t aK = smem_u32(sKV + s * STAGE), aV = aK + KB;
-        const uint32_t idesc_s = make_idesc_bf16(TILE, ncur, 0, 0);
+        const int nc = half_cols(g, nkv, n_last);
+        const uint32_t aK = aKV + st * STAGE + h * 4096, aV = aK + KB;
+        const uint32_t idesc_s = make_idesc_bf16(TILE, nc, 0, 0);
 #pragma unroll
         for (int kk = 0; kk < 4 * DCH; ++kk) {
           const uint32_t qoff = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t koff = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(tS, make_smem_desc(aQ + qoff, 0, 1024), make_smem_desc(aK + koff, 0, 1024), idesc_s, kk > 0);
+          umma_ss(tS + h * 32, make_smem_desc(aQ + qoff, 0, 1024), make_smem_desc(aK + koff, 0, 1024), idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 4 * DCH; ++kk) {
           const uint32_t qoff = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t koff = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(tdP, make_smem_desc(adO + qoff, 0, 1024), make_smem_desc(aV + koff, 0, 1024), idesc_s, kk > 0);
+          umma_ss(tdP + h * 32, make_smem_desc(adO + qoff, 0, 1024), make_smem_desc(aV + koff, 0, 1024), idesc_s, kk > 0);
         }
-        tc_commit(sp_full);
-        if (!mbar_wait(ds_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_commit(&sp_full[h]);
+        return true;
+      };
+      if (ok) ok = issue_sp(0);
+      if (ok && G > 1) ok = issue_sp(1);
+      for (int g = 0; g < G && ok; ++g) {
+        const int j = g >> 1, h = g & 1, st = j % NST;
+        const int nc = half_cols(g, nkv, n_last);
+        if (!mbar_wait(&ds_full[h], (g >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
         tc_fence_after();
-        // dQ += dS K : A = dS (K-major over kv), B = K MN-major (d contiguous, kv rows strided)
+        // dQ += dS[:, half] K[half rows] : A = dS (K-major over kv), B = K MN-major (d contiguous, kv rows strided)
+        const uint32_t aK = aKV + st * STAGE;
         const uint32_t idesc_dq = make_idesc_bf16(TILE, HD, 0, 1);
-        for (int kk = 0; kk < ncur / 16; ++kk)
-          umma_ss(tdQ, make_smem_desc(adS + kk * 32, 0, 1024), make_smem_desc(aK + kk * 2048, 8192, 1024), idesc_dq,
-                  (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(&kv_empty[s]);
+        for (int kk = 0; kk < nc / 16; ++kk) {
+          const int k16 = 2 * h + kk;   // 16-column group inside the 64-column tile
+          umma_ss(tdQ, make_smem_desc(adS + k16 * 32, 0, 1024), make_smem_desc(aK + k16 * 2048, 8192, 1024), idesc_dq,
+                  (g > 0 || kk > 0) ? 1u : 0u);
+        }
+        const bool tile_done = (h == 1) || (g == G - 1);
+        if (tile_done) tc_commit(&kv_empty[st]);
+        if (g + 2 < G) ok = issue_sp(g + 2);
       }
       if (ok) tc_commit(dq_full);
     }
@@ -510,38 +537,62 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       p.delta[sidx] = delta;
     }
+    const float sl2 = p.scale_log2, sc = p.scale;
     bool ok = true;
-    for (int j = 0; j < nkv && ok; ++j) {
+    for (int g = 0; g < G && ok; ++g) {
+      const int j = g >> 1, h = g & 1;
       const bool last = (j == nkv - 1);
-      const int ncur = last ? n_last : BT;
-      const int valid = (last && rem) ? rem : BT;
-      if (!mbar_wait(sp_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      const int nc = half_cols(g, nkv, n_last);
+      const int valid = (last && rem) ? rem - 32 * h : 32;     // valid columns inside this half
+      if (!mbar_wait(&sp_full[h], (g >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < ncur; c += 16) {
-        uint32_t sv[16], dv[16], pk[8];
-        tmem_ld16(tS + lane_addr + c, sv);
-        tmem_ld16(tdP + lane_addr + c, dv);
+      if (nc == 32 && valid >= 32) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(tS + h * 32 + lane_addr, sv);
+        tmem_ld32(tdP + h * 32 + lane_addr, dv);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -lse));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -lse));
-          float d0 = p0 * (__uint_as_float(dv[2 * i]) - delta) * p.scale;
-          float d1 = p1 * (__uint_as_float(dv[2 * i + 1]) - delta) * p.scale;
-          if (c + 2 * i >= valid || !row_ok) d0 = 0.f;
-          if (c + 2 * i + 1 >= valid || !row_ok) d1 = 0.f;
-          pk[i] = pack_bf16x2(d0, d1);
-        }
+        for (int gq = 0; gq < 4; ++gq) {
+          uint32_t pk[4];
 #pragma unroll
-        for (int g = 0; g < 2; ++g)
-          *reinterpret_cast<uint4*>(sdS + swz128(row, (c >> 3) + g)) =
-              make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+          for (int i = 0; i < 4; ++i) {
+            const int e = 8 * gq + 2 * i;
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), sl2, -lse));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), sl2, -lse));
+            float d0 = p0 * (__uint_as_float(dv[e]) - delta) * sc;
+            float d1 = p1 * (__uint_as_float(dv[e + 1]) - delta) * sc;
+            if (!row_ok) { d0 = 0.f; d1 = 0.f; }
+            pk[i] = pack_bf16x2(d0, d1);
+          }
+          *reinterpret_cast<uint4*>(sdS + swz128(row, 4 * h + gq)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < nc; c += 16) {
+          uint32_t sv[16], dv[16], pk[8];
+          tmem_ld16(tS + h * 32 + lane_addr + c, sv);
+          tmem_ld16(tdP + h * 32 + lane_addr + c, dv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * i]), sl2, -lse));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), sl2, -lse));
+            float d0 = p0 * (__uint_as_float(dv[2 * i]) - delta) * sc;
+            float d1 = p1 * (__uint_as_float(dv[2 * i + 1]) - delta) * sc;
+            if (c + 2 * i >= valid || !row_ok) d0 = 0.f;
+            if (c + 2 * i + 1 >= valid || !row_ok) d1 = 0.f;
+            pk[i] = pack_bf16x2(d0, d1);
+          }
+#pragma unroll
+          for (int gq = 0; gq < 2; ++gq)
+            *reinterpret_cast<uint4*>(sdS + swz128(row, 4 * h + (c >> 3) + gq)) =
+                make_uint4(pk[4 * gq], pk[4 * gq + 1], pk[4 * gq + 2], pk[4 * gq + 3]);
+        }
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
+      if (lane == 0) mbar_arrive(&ds_full[h]);
     }
     if (ok && mbar_wait(dq_full, 0, p.status, ERR_TIMEOUT_ATTN)) {
       tc_fence_after();
@@ -553,12 +604,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_wait_ld();
         if (row_ok) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4*>(dst + c + g * 8) = make_uint4(
-                pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
-                pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
-                pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
-                pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+          for (int gq = 0; gq < 4; ++gq)
+            *reinterpret_cast<uint4*>(dst + c + gq * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(v[8 * gq]), __uint_as_float(v[8 * gq + 1])),
+                pack_bf16x2(__uint_as_float(v[8 * gq + 2]), __uint_as_float(v[8 * gq + 3])),
+                pack_bf16x2(__uint_as_float(v[8 * gq + 4]), __uint_as_float(v[8 * gq + 5])),
+                pack_bf16x2(__uint_as_float(v[8 * gq + 6]), __uint_as_float(v[8 * gq + 7])));
         }
       }
     }
@@ -573,29 +624,31 @@ template <int DCH>
 __global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 2 : 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                    const AttnBwdParams p) {
+                    const AttnBwdParams p, const int stat_floats) {
   constexpr int HD = 64 * DCH;
   constexpr int KB = DCH * 16384;  // K tile, V tile (128 rows)
   constexpr int QB = DCH * 8192;   // Q tile, dO tile (64 rows)
   constexpr int STAGE = 2 * QB;
+  constexpr int NST = 2;
   constexpr int TMEM_COLS = (DCH == 1) ? 256 : 512;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = sK + KB;
   uint8_t* sQD = sV + KB;
-  uint8_t* sPT = sQD + 2 * STAGE;  // [128 x 64] bf16
-  uint8_t* sdST = sPT + 16384;     // [128 x 64] bf16
-  float* s_stat = reinterpret_cast<float*>(sdST + 16384);  // [2 parities][lse 64 | delta 64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_stat + 256);
+  uint8_t* sPT = sQD + NST * STAGE;  // [128 x 64] bf16
+  uint8_t* sdST = sPT + 16384;       // [128 x 64] bf16
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdST + 16384);
   uint64_t* k_full = bars;
-  uint64_t* qd_full = bars + 1;
-  uint64_t* qd_empty = bars + 3;
-  uint64_t* sp_full = bars + 5;
-  uint64_t* pd_full = bars + 6;
-  uint64_t* acc_full = bars + 7;
-  uint64_t* stat_bar = bars + 8;  // lse/delta of the current Q tile staged in shared memory (128 arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* qd_full = bars + 1;    // [2]
+  uint64_t* qd_empty = bars + 3;   // [2]
+  uint64_t* sp_full = bars + 5;    // [2]
+  uint64_t* pd_full = bars + 7;    // [2]
+  uint64_t* acc_full = bars + 9;
+  uint64_t* stat_bar = bars + 10;  // lse/delta of the whole window staged in shared memory (128 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+  float* s_lse = reinterpret_cast<float*>(bars + 16);   // [stat_floats] then delta [stat_floats]
+  float* s_delta = s_lse + stat_floats;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt = blockIdx.x, head = blockIdx.y, win = blockIdx.z;
@@ -603,6 +656,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int nfull = N / BT, rem = N - nfull * BT;
   const int nq = nfull + (rem ? 1 : 0);
   const int n_last = rem ? ((rem + 15) & ~15) : BT;
+  const int G = 2 * (nq - 1) + (n_last > 32 ? 2 : 1);
 
   if (threadIdx.x == 0) {
     int ab = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -614,8 +668,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (threadIdx.x == 0) {
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
     mbar_init(k_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&qd_full[i], 1); mbar_init(&qd_empty[i], 1); }
-    mbar_init(sp_full, 1); mbar_init(pd_full, 4); mbar_init(acc_full, 1); mbar_init(stat_bar, 128);
+    for (int i = 0; i < NST; ++i) { mbar_init(&qd_full[i], 1); mbar_init(&qd_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sp_full[i], 1); mbar_init(&pd_full[i], 4); }
+    mbar_init(acc_full, 1); mbar_init(stat_bar, 128);
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -633,54 +688,68 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tma_load_3d(sK + c * 16384, &tm_k, k_full, p.k_col0 + head * HD + c * 64, kt * TILE, win);
         tma_load_3d(sV + c * 16384, &tm_v, k_full, p.v_col0 + head * HD + c * 64, kt * TILE, win);
       }
+      int st = 0;
+      uint32_t ph = 0;
       for (int i = 0; i < nq; ++i) {
-        const int s = i & 1;
-        if (!mbar_wait(&qd_empty[s], ((i >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
-        uint8_t* sQ = sQD + s * STAGE;
+        if (!mbar_wait(&qd_empty[st], ph ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
+        uint8_t* sQ = sQD + st * STAGE;
         uint8_t* sdO = sQ + QB;
-        mbar_expect_tx(&qd_full[s], STAGE);
+        mbar_expect_tx(&qd_full[st], STAGE);
 #pragma unroll
         for (int c = 0; c < DCH; ++c) {
-          tma_load_3d(sQ + c * 8192, &tm_q, &qd_full[s], p.q_col0 + head * HD + c * 64, i * BT, win);
-          tma_load_3d(sdO + c * 8192, &tm_do, &qd_full[s], head * HD + c * 64, i * BT, win);
+          tma_load_3d(sQ + c * 8192, &tm_q, &qd_full[st], p.q_col0 + head * HD + c * 64, i * BT, win);
+          tma_load_3d(sdO + c * 8192, &tm_do, &qd_full[st], head * HD + c * 64, i * BT, win);
         }
+        if (++st == NST) { st = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (elect_one_sync()) {
       bool ok = mbar_wait(k_full, 0, p.status, ERR_TIMEOUT_ATTN);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), adST = smem_u32(sdST);
-      for (int i = 0; i < nq && ok; ++i) {
-        const int s = i & 1;
-        const int ncur = (i == nq - 1) ? n_last : BT;
-        if (!mbar_wait(&qd_full[s], (i >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      const uint32_t aQD = smem_u32(sQD);
+      auto issue_sp = [&](int g) -> bool {
+        const int i = g >> 1, h = g & 1, st = i % NST;
+        if (h == 0 && !mbar_wait(&qd_full[st], (i / NST) & 1, p.status, ERR_TIMEOUT_ATTN)) return false;
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQD + s * STAGE), adO = aQ + QB;
-        const uint32_t idesc_s = make_idesc_bf16(TILE, ncur, 0, 0);
+        const int nc = half_cols(g, nq, n_last);
+        const uint32_t aQ = aQD + st * STAGE + h * 4096, adO = aQ + QB;
+        const uint32_t idesc_s = make_idesc_bf16(TILE, nc, 0, 0);
 #pragma unroll
         for (int kk = 0; kk < 4 * DCH; ++kk) {
           const uint32_t koff = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t qoff = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(tS, make_smem_desc(aK + koff, 0, 1024), make_smem_desc(aQ + qoff, 0, 1024), idesc_s, kk > 0);
+          umma_ss(tS + h * 32, make_smem_desc(aK + koff, 0, 1024), make_smem_desc(aQ + qoff, 0, 1024), idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 4 * DCH; ++kk) {
           const uint32_t koff = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t qoff = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(tdP, make_smem_desc(aV + koff, 0, 1024), make_smem_desc(adO + qoff, 0, 1024), idesc_s, kk > 0);
+          umma_ss(tdP + h * 32, make_smem_desc(aV + koff, 0, 1024), make_smem_desc(adO + qoff, 0, 1024), idesc_s, kk > 0);
         }
-        tc_commit(sp_full);
-        if (!mbar_wait(pd_full, i & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_commit(&sp_full[h]);
+        return true;
+      };
+      if (ok) ok = issue_sp(0);
+      if (ok && G > 1) ok = issue_sp(1);
+      for (int g = 0; g < G && ok; ++g) {
+        const int i = g >> 1, h = g & 1, st = i % NST;
+        const int nc = half_cols(g, nq, n_last);
+        if (!mbar_wait(&pd_full[h], (g >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t aQ = aQD + st * STAGE, adO = aQ + QB;
         const uint32_t idesc_acc = make_idesc_bf16(TILE, HD, 0, 1);
-        for (int kk = 0; kk < ncur / 16; ++kk) {
-          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-          umma_ss(tdV, make_smem_desc(aPT + kk * 32, 0, 1024), make_smem_desc(adO + kk * 2048, 8192, 1024),
+        for (int kk = 0; kk < nc / 16; ++kk) {
+          const int k16 = 2 * h + kk;
+          const uint32_t acc = (g > 0 || kk > 0) ? 1u : 0u;
+          umma_ss(tdV, make_smem_desc(aPT + k16 * 32, 0, 1024), make_smem_desc(adO + k16 * 2048, 8192, 1024),
                   idesc_acc, acc);
-          umma_ss(tdK, make_smem_desc(adST + kk * 32, 0, 1024), make_smem_desc(aQ + kk * 2048, 8192, 1024),
+          umma_ss(tdK, make_smem_desc(adST + k16 * 32, 0, 1024), make_smem_desc(aQ + k16 * 2048, 8192, 1024),
                   idesc_acc, acc);
         }
-        tc_commit(&qd_empty[s]);
+        const bool tile_done = (h == 1) || (g == G - 1);
+        if (tile_done) tc_commit(&qd_empty[st]);
+        if (g + 2 < G) ok = issue_sp(g + 2);
       }
       if (ok) tc_commit(acc_full);
     }
@@ -692,53 +761,59 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const int t128 = threadIdx.x - 64;  // 0..127 among the four math warps
     const size_t sbase = (static_cast<size_t>(win) * p.H + head) * N;
-    bool ok = true;
-    for (int i = 0; i < nq && ok; ++i) {
+    // stage lse and delta of every query row of this (window, head) once
+    for (int i = t128; i < stat_floats; i += 128) {
+      s_lse[i] = (i < N) ? p.lse[sbase + i] : 0.f;
+      s_delta[i] = (i < N) ? p.delta[sbase + i] : 0.f;
+    }
+    mbar_arrive(stat_bar);
+    bool ok = mbar_wait(stat_bar, 0, p.status, ERR_TIMEOUT_ATTN);
+    const float sl2 = p.scale_log2, sc = p.scale;
+    for (int g = 0; g < G && ok; ++g) {
+      const int i = g >> 1, h = g & 1;
       const bool last = (i == nq - 1);
-      const int ncur = last ? n_last : BT;
-      const int valid = (last && rem) ? rem : BT;
-      float* st = s_stat + (i & 1) * 128;
-      {
-        const int col = t128 & 63;
-        const int gq = i * BT + col;
-        float v = 0.f;
-        if (gq < N) v = (t128 < 64) ? p.lse[sbase + gq] : p.delta[sbase + gq];
-        st[t128] = v;
-      }
-      mbar_arrive(stat_bar);
-      if (!mbar_wait(stat_bar, i & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
-      if (!mbar_wait(sp_full, i & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      const int nc = half_cols(g, nq, n_last);
+      const int valid = (last && rem) ? rem - 32 * h : 32;
+      const float* ls = s_lse + i * BT + 32 * h;
+      const float* de = s_delta + i * BT + 32 * h;
+      if (!mbar_wait(&sp_full[h], (g >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < ncur; c += 16) {
+      for (int c = 0; c < nc; c += 16) {
         uint32_t sv[16], dv[16], pp[8], dd[8];
-        tmem_ld16(tS + lane_addr + c, sv);
-        tmem_ld16(tdP + lane_addr + c, dv);
+        tmem_ld16(tS + h * 32 + lane_addr + c, sv);
+        tmem_ld16(tdP + h * 32 + lane_addr + c, dv);
+        float lq[16], dq[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float4 a = *reinterpret_cast<const float4*>(ls + c + 4 * k);
+          const float4 b = *reinterpret_cast<const float4*>(de + c + 4 * k);
+          lq[4 * k] = a.x; lq[4 * k + 1] = a.y; lq[4 * k + 2] = a.z; lq[4 * k + 3] = a.w;
+          dq[4 * k] = b.x; dq[4 * k + 1] = b.y; dq[4 * k + 2] = b.z; dq[4 * k + 3] = b.w;
+        }
         tmem_wait_ld();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const float l0 = st[c + 2 * k], l1 = st[c + 2 * k + 1];
-          const float e0 = st[64 + c + 2 * k], e1 = st[64 + c + 2 * k + 1];
-          float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * k]), p.scale_log2, -l0));
-          float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * k + 1]), p.scale_log2, -l1));
+          float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * k]), sl2, -lq[2 * k]));
+          float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * k + 1]), sl2, -lq[2 * k + 1]));
           if (c + 2 * k >= valid || !row_ok) p0 = 0.f;
           if (c + 2 * k + 1 >= valid || !row_ok) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(dv[2 * k]) - e0) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dv[2 * k + 1]) - e1) * p.scale;
+          const float d0 = p0 * (__uint_as_float(dv[2 * k]) - dq[2 * k]) * sc;
+          const float d1 = p1 * (__uint_as_float(dv[2 * k + 1]) - dq[2 * k + 1]) * sc;
           pp[k] = pack_bf16x2(p0, p1);
           dd[k] = pack_bf16x2(d0, d1);
         }
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const uint32_t off = swz128(row, (c >> 3) + g);
-          *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pp[4 * g], pp[4 * g + 1], pp[4 * g + 2], pp[4 * g + 3]);
-          *reinterpret_cast<uint4*>(sdST + off) = make_uint4(dd[4 * g], dd[4 * g + 1], dd[4 * g + 2], dd[4 * g + 3]);
+        for (int gq = 0; gq < 2; ++gq) {
+          const uint32_t off = swz128(row, 4 * h + (c >> 3) + gq);
+          *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pp[4 * gq], pp[4 * gq + 1], pp[4 * gq + 2], pp[4 * gq + 3]);
+          *reinterpret_cast<uint4*>(sdST + off) = make_uint4(dd[4 * gq], dd[4 * gq + 1], dd[4 * gq + 2], dd[4 * gq + 3]);
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pd_full);
+      if (lane == 0) mbar_arrive(&pd_full[h]);
     }
     if (ok && mbar_wait(acc_full, 0, p.status, ERR_TIMEOUT_ATTN)) {
       tc_fence_after();
@@ -756,12 +831,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           tmem_wait_ld();
           if (row_ok) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g)
-              *reinterpret_cast<uint4*>(dst + c + g * 8) = make_uint4(
-                  pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
-                  pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
-                  pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
-                  pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+            for (int gq = 0; gq < 4; ++gq)
+              *reinterpret_cast<uint4*>(dst + c + gq * 8) = make_uint4(
+                  pack_bf16x2(__uint_as_float(v[8 * gq]), __uint_as_float(v[8 * gq + 1])),
+                  pack_bf16x2(__uint_as_float(v[8 * gq + 2]), __uint_as_float(v[8 * gq + 3])),
+                  pack_bf16x2(__uint_as_float(v[8 * gq + 4]), __uint_as_float(v[8 * gq + 5])),
+                  pack_bf16x2(__uint_as_float(v[8 * gq + 6]), __uint_as_float(v[8 * gq + 7])));
           }
         }
       }
@@ -778,20 +853,26 @@ static int launch_attn_bwd(const CUtensorMap& tq128, const CUtensorMap& tk64, co
                            const CUtensorMap& tdo128, const CUtensorMap& tq64, const CUtensorMap& tk128,
                            const CUtensorMap& tv128, const CUtensorMap& tdo64, const AttnBwdParams& p,
                            cudaStream_t stream) {
-  constexpr int SMEM_DQ = 2 * DCH * 16384 + 2 * 2 * DCH * 8192 + 16384 + 128;
-  constexpr int SMEM_DKV = 2 * DCH * 16384 + 2 * 2 * DCH * 8192 + 2 * 16384 + 1024 + 128;
-  static bool configured = false;
+  const int stat_floats = ((p.N + BT - 1) / BT) * BT;      // lse and delta of one window, padded to whole tiles
+  const int SMEM_DQ = 2 * DCH * 16384 + 3 * 2 * DCH * 8192 + 16384 + 128;
+  const int SMEM_DKV = 2 * DCH * 16384 + 2 * 2 * DCH * 8192 + 2 * 16384 + 128 + 2 * stat_floats * 4;
+  if (SMEM_DKV > 227 * 1024) return -23;
   auto k1 = attn_bwd_dq_kernel<DCH>;
   auto k2 = attn_bwd_dkv_kernel<DCH>;
-  if (!configured) {
+  static int configured_dkv = 0;
+  static bool configured_dq = false;
+  if (!configured_dq) {
     if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ) != cudaSuccess) return -20;
+    configured_dq = true;
+  }
+  if (configured_dkv < SMEM_DKV) {
     if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DKV) != cudaSuccess) return -20;
-    configured = true;
+    configured_dkv = SMEM_DKV;
   }
   dim3 grid((p.N + TILE - 1) / TILE, p.H, p.n_win);
   k1<<<grid, ATT_THREADS, SMEM_DQ, stream>>>(tq128, tk64, tv64, tdo128, p);
   if (cudaGetLastError() != cudaSuccess) return -21;
-  k2<<<grid, ATT_THREADS, SMEM_DKV, stream>>>(tq64, tk128, tv128, tdo64, p);
+  k2<<<grid, ATT_THREADS, SMEM_DKV, stream>>>(tq64, tk128, tv128, tdo64, p, stat_floats);
   return cudaGetLastError() == cudaSuccess ? 0 : -22;
 }
 
