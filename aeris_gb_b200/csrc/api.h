@@ -12,6 +12,11 @@ int aeris_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
                     int rows_per_gate, void* aux, int ld_aux, int swiglu_f, int k_splits, int bn, int* status,
                     void* stream);
 
+int aeris_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                         int a_mn, int b_mn, int epi, const void* resid, int ldr, const float* gate,
+                         int rows_per_gate, void* aux, int ld_aux, int swiglu_f, int k_splits, int* status,
+                         void* stream);
+
 int aeris_attn_fwd(const void* q, int ldq, int q_col0, const void* k, int ldk, int k_col0, const void* v, int ldv,
                    int v_col0, void* o, int ldo, float* lse, int n_win, int N, int H, int head_dim, float scale,
                    int* status, void* stream);

@@ -92,6 +92,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;  // someone else gave up
   }
 }
+// Non-suspending poll (mbarrier.test_wait) with the same time limit: the waiting thread never yields its issue slot,
+// which suits single elected threads that wait on barriers signalled from another CTA of the cluster.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity, int* status, int code) {
+  const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 512; ++i)
+      if (mbar_test_wait(bar, parity)) return true;
+    if (globaltimer_ns() - t0 > AERIS_WAIT_TIMEOUT_NS) {
+      if (status) atomicCAS(status, 0, code);
+      return false;
+    }
+    if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
+  }
+}
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

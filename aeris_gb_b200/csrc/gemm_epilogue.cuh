@@ -1,0 +1,198 @@
+// Shared by the one-CTA and the two-CTA GEMM kernels: parameters and the TMEM -> registers -> global epilogue.
+#pragma once
+#include "common.cuh"
+
+namespace aeris {
+
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GATE_RESID = 2, EPI_ACC_F32 = 3, EPI_STORE_F32 = 4,
+              EPI_SWIGLU_BOTH = 5,   // EPI_SWIGLU that also stores the raw [gate | up] product to aux [M, 2F]
+              EPI_SWIGLU_BWD = 6 };  // acc = d(act); reads u = [gate | up] from resid [M, 2F], writes d(u) to C [M, 2F]
+
+struct GemmParams {
+  int M, N, K;
+  int epi;
+  void* C;
+  int ldc;
+  const __nv_bfloat16* resid;  // EPI_GATE_RESID: out = resid + gate[col] * acc
+  int ldr;
+  const float* gate;           // [M / rows_per_gate][N]
+  int rows_per_gate;
+  __nv_bfloat16* aux;          // optional raw copy of acc (bf16) in EPI_GATE_RESID
+  int ld_aux;
+  int b_tile_stride;           // rows of B advanced per n-tile (BN, or BN/2 for SwiGLU)
+  int b_half_off;              // row offset of the second half-box of B (BN/2, or F for SwiGLU)
+  int k_splits;
+  int swiglu_f;                // F for the SwiGLU epilogues
+  int* status;
+};
+
+
+// One thread = one accumulator row (TMEM lane) of a BN-column tile whose first accumulator column is `taddr`.
+// `row` is the global output row, `tn` the tile's index along N, `kempty` marks a split-K slice without work.
+template <int BN>
+__device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t taddr, int row, bool row_ok, int tn,
+                                                  bool kempty) {
+
+  if (p.epi == EPI_SWIGLU_BWD) {
+    // d(gate) = d(act) * up * dsilu(gate), d(up) = d(act) * silu(gate); u is read and d(u) written in place
+    const __nv_bfloat16* usrc = p.resid + static_cast<size_t>(row) * p.ldr + tn * BN;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * BN;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c, v);
+      tmem_wait_ld();
+      if (row_ok) {
+        uint32_t og[16], ou[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 g4 = *reinterpret_cast<const uint4*>(usrc + c + 8 * i);
+          const uint4 u4 = *reinterpret_cast<const uint4*>(usrc + p.swiglu_f + c + 8 * i);
+          const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 g2 = unpack_bf16x2(gw[j]), u2 = unpack_bf16x2(uw[j]);
+            const float d0 = __uint_as_float(v[8 * i + 2 * j]), d1 = __uint_as_float(v[8 * i + 2 * j + 1]);
+            const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+            const float si0 = g2.x * s0, si1 = g2.y * s1;
+            og[4 * i + j] = pack_bf16x2(d0 * u2.x * (s0 + si0 * (1.f - s0)), d1 * u2.y * (s1 + si1 * (1.f - s1)));
+            ou[4 * i + j] = pack_bf16x2(d0 * si0, d1 * si1);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(og[4 * i], og[4 * i + 1], og[4 * i + 2], og[4 * i + 3]);
+          *reinterpret_cast<uint4*>(dst + p.swiglu_f + c + 8 * i) =
+              make_uint4(ou[4 * i], ou[4 * i + 1], ou[4 * i + 2], ou[4 * i + 3]);
+        }
+      }
+    }
+  } else if (p.epi == EPI_SWIGLU || p.epi == EPI_SWIGLU_BOTH) {
+    constexpr int H = BN / 2;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * H;
+    __nv_bfloat16* raw = (p.epi == EPI_SWIGLU_BOTH) ? p.aux + static_cast<size_t>(row) * p.ld_aux + tn * H : nullptr;
+#pragma unroll 1
+    for (int c = 0; c < H; c += 32) {
+      uint32_t g[32], u[32];
+      tmem_ld32(taddr + c, g);
+      tmem_ld32(taddr + H + c, u);
+      tmem_wait_ld();
+      if (row_ok) {
+        if (raw) {
+          uint32_t rg[16], ru[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            rg[i] = pack_bf16x2(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
+            ru[i] = pack_bf16x2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            *reinterpret_cast<uint4*>(raw + c + 8 * i) = make_uint4(rg[4 * i], rg[4 * i + 1], rg[4 * i + 2], rg[4 * i + 3]);
+            *reinterpret_cast<uint4*>(raw + p.swiglu_f + c + 8 * i) =
+                make_uint4(ru[4 * i], ru[4 * i + 1], ru[4 * i + 2], ru[4 * i + 3]);
+          }
+        }
+        uint32_t o[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+          const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+          const float s0 = g0 / (1.f + __expf(-g0)), s1 = g1 / (1.f + __expf(-g1));
+          o[i] = pack_bf16x2(s0 * u0, s1 * u1);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+      }
+    }
+  } else if (p.epi == EPI_ACC_F32 || p.epi == EPI_STORE_F32) {
+    float* out = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * BN;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c, v);
+      tmem_wait_ld();
+      if (row_ok && !kempty) {
+        if (p.epi == EPI_STORE_F32) {
+          float4* dst = reinterpret_cast<float4*>(out + c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+        } else if (p.k_splits > 1) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + c + 4 * i),
+                         "f"(__uint_as_float(v[4 * i])), "f"(__uint_as_float(v[4 * i + 1])),
+                         "f"(__uint_as_float(v[4 * i + 2])), "f"(__uint_as_float(v[4 * i + 3]))
+                         : "memory");
+          }
+        } else {
+          float4* dst = reinterpret_cast<float4*>(out + c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float4 o = dst[i];
+            o.x += __uint_as_float(v[4 * i]);
+            o.y += __uint_as_float(v[4 * i + 1]);
+            o.z += __uint_as_float(v[4 * i + 2]);
+            o.w += __uint_as_float(v[4 * i + 3]);
+            dst[i] = o;
+          }
+        }
+      }
+    }
+  } else {
+    // EPI_STORE / EPI_GATE_RESID : bf16 output
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * BN;
+    const __nv_bfloat16* res =
+        p.resid ? p.resid + static_cast<size_t>(row) * p.ldr + tn * BN : nullptr;
+    const float* gate = nullptr;
+    if (p.epi == EPI_GATE_RESID && row_ok)
+      gate = p.gate + static_cast<size_t>(row / p.rows_per_gate) * p.N + tn * BN;
+    __nv_bfloat16* aux = p.aux ? p.aux + static_cast<size_t>(row) * p.ld_aux + tn * BN : nullptr;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c, v);
+      tmem_wait_ld();
+      if (row_ok) {
+        uint32_t o[16];
+        if (p.epi == EPI_GATE_RESID) {
+          if (aux) {
+            uint32_t a[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              a[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            uint4* adst = reinterpret_cast<uint4*>(aux + c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) adst[i] = make_uint4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
+          }
+          const uint4* rsrc = reinterpret_cast<const uint4*>(res + c);
+          const float4* gsrc = reinterpret_cast<const float4*>(gate + c);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 r4 = rsrc[i];
+            const uint32_t rr[4] = {r4.x, r4.y, r4.z, r4.w};
+            const float4 ga = gsrc[2 * i], gb = gsrc[2 * i + 1];
+            const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 r2 = unpack_bf16x2(rr[j]);
+              const float a0 = __uint_as_float(v[8 * i + 2 * j]), a1 = __uint_as_float(v[8 * i + 2 * j + 1]);
+              o[4 * i + j] = pack_bf16x2(fmaf(gg[2 * j], a0, r2.x), fmaf(gg[2 * j + 1], a1, r2.y));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+      }
+    }
+  }
+}
+
+}  // namespace aeris

@@ -1,9 +1,15 @@
 """Python front end of the tcgen05 GEMM (``csrc/gemm.cu``)."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import lib as _l
+
+# The two-CTA (cta_group::2, 256 x 256 tile per SM pair) kernel is used for every product whose N is a multiple of 256
+# unless AERIS_GEMM_2CTA=0.
+TWO_CTA_DEFAULT = os.environ.get("AERIS_GEMM_2CTA", "1") != "0"
 
 EPI_STORE, EPI_SWIGLU, EPI_GATE_RESID, EPI_ACC_F32, EPI_STORE_F32, EPI_SWIGLU_BOTH, EPI_SWIGLU_BWD = range(7)
 
@@ -15,7 +21,8 @@ def _ld(t: torch.Tensor) -> int:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False, out: torch.Tensor | None = None,
          epi: int = EPI_STORE, resid: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-         rows_per_gate: int = 0, aux: torch.Tensor | None = None, k_splits: int = 1, bn: int = 0) -> torch.Tensor:
+         rows_per_gate: int = 0, aux: torch.Tensor | None = None, k_splits: int = 1, bn: int = 0,
+         two_cta: bool | None = None) -> torch.Tensor:
     """``out (op)= A @ B^T`` on the tensor cores.
 
     ``a`` is ``[M, K]`` (or, with ``a_t``, the stored tensor is ``[K, M]`` and is used transposed); ``b`` is
@@ -52,6 +59,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         dt = torch.float32 if epi in (EPI_ACC_F32, EPI_STORE_F32) else torch.bfloat16
         out = (torch.zeros if epi == EPI_ACC_F32 else torch.empty)((M, n_out), dtype=dt, device=a.device)
     assert out.shape == (M, n_out) or epi == EPI_SWIGLU_BWD
+    if two_cta is None:
+        two_cta = TWO_CTA_DEFAULT and bn == 0
+    if two_cta and N % 256 == 0:
+        rc = _l.lib().aeris_gemm_bf16_2cta(
+            _l.ptr(a), _l.ptr(b), _l.ptr(out), M, N, K, _ld(a), _ld(b), _ld(out), int(a_t), int(b_t), epi,
+            _l.ptr(resid), _ld(resid) if resid is not None else 0, _l.ptr(gate), rows_per_gate,
+            _l.ptr(aux), _ld(aux) if aux is not None else 0, swiglu_f, k_splits, _l.ptr(_l.status_word()),
+            _l.stream_ptr())
+        _l.check(rc, "aeris_gemm_bf16_2cta")
+        return out
     if bn == 0:
         bn = 256 if N % 256 == 0 else 128
     rc = _l.lib().aeris_gemm_bf16(

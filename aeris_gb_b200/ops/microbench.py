@@ -58,6 +58,7 @@ def main():
     ap.add_argument("--rows", type=int, default=129600)
     ap.add_argument("--dim", type=int, default=1536)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--one-cta", action="store_true", help="force the one-CTA GEMM kernel")
     a = ap.parse_args()
     dev = "cuda"
     tf_peak, bw_peak, src = _peaks()
@@ -71,7 +72,8 @@ def main():
         if a.epi == G.EPI_GATE_RESID:
             kw["resid"] = torch.randn(a.m, a.n, device=dev).bfloat16()
             kw["gate"] = torch.randn(1, a.n, device=dev)
-        ms = _time(lambda: G.gemm(A_, B_, a_t=a.a_t, b_t=a.b_t, epi=a.epi, k_splits=a.k_splits, **kw), a.iters)
+        ms = _time(lambda: G.gemm(A_, B_, a_t=a.a_t, b_t=a.b_t, epi=a.epi, k_splits=a.k_splits,
+                                  two_cta=not a.one_cta, **kw), a.iters)
         fl = 2.0 * a.m * a.n * a.k
         out.update(shape=[a.m, a.n, a.k], a_t=a.a_t, b_t=a.b_t, epi=a.epi, ms=ms, tflops=fl / ms / 1e9,
                    frac_of_peak=fl / ms / 1e9 / tf_peak, peak_source=src)
