@@ -56,8 +56,9 @@ class ParallelEngine:
         self.c = grid.coords(rank)
         self.groups = groups if groups is not None else grid.build_groups(rank)
         self.PP, self.GAS = grid.PP, ecfg.gas
-        assert (model_cfg.wp[0], model_cfg.wp[1]) == (grid.WP_Y, grid.WP_X)
+        assert (model_cfg.wp[0], model_cfg.wp[1], model_cfg.sp) == (grid.WP_Y, grid.WP_X, grid.SP)
         self.wp_rank = self.c.wp_y * grid.WP_X + self.c.wp_x
+        self.replica_rank = self.wp_rank * grid.SP + self.c.sp     # rank inside the WP x SP group holding one sample
         n_logical = model_cfg.n_layers + 2
         self.stage_ids = split_stages(n_logical, self.PP)[self.c.pp]
         torch.manual_seed(ecfg.seed + 17 * self.c.pp)
@@ -88,16 +89,16 @@ class ParallelEngine:
         self.keep_grads = False        # tests: keep a copy of the reduced, scaled gradients of the last step
         self.loads = 0
         halo = None
-        if grid.WP_Y * grid.WP_X > 1 and self.device.type == "cuda":
+        if grid.WP_Y * grid.WP_X * grid.SP > 1 and self.device.type == "cuda":
             from ..parallel.symm import HaloExchange
-            halo = HaloExchange(self.groups["wp"], self.device)
-        self.ctx = StreamContext(model_cfg, 1, self.wp_rank, halo.peer_fn if halo else None,
-                                 wp_group=self.groups.get("wp"), sp_group=self.groups.get("sp"))
-        self.tokens = self.ctx.grid.tokens_per_rank // grid.SP
+            halo = HaloExchange(self.groups["replica"], self.device)
+        self.ctx = StreamContext(model_cfg, 1, self.replica_rank, halo.peer_fn if halo else None,
+                                 wp_group=self.groups.get("replica"), sp_group=self.groups.get("sp"))
+        self.tokens = self.ctx.grid.tokens_per_rank
         self._w_var = TF.variable_weights(model_cfg.out_channels, self.device)
         w = TF.latitude_weights(model_cfg.img[0], diff_cfg.w_lat_add)
         img = w.view(1, -1, 1, 1).expand(1, model_cfg.img[0], model_cfg.img[1], 1)
-        self._w_lat = self._sp_slice(LY.image_to_tokens(img, self.ctx.grid, (0, 0), self.wp_rank)).to(self.device)
+        self._w_lat = LY.image_to_tokens(img, self.ctx.grid, (0, 0), self.replica_rank).to(self.device)
         self.loss_acc = torch.zeros((), device=self.device)
         self.tot_loss, self.total_norm, self.stage_norm = 0.0, 0.0, 0.0
         self.cur_it = 0
@@ -135,7 +136,7 @@ class ParallelEngine:
             dist.broadcast(p.data, src=src, group=g)
 
     def _sp_slice(self, tok: torch.Tensor) -> torch.Tensor:
-        """This SP rank's contiguous slice of every window's tokens. tok: [windows * L, C]."""
+        """This SP rank's contiguous slice of every window's tokens. tok: [windows * L, C] (whole windows)."""
         SP = self.grid.SP
         if SP == 1:
             return tok
@@ -153,7 +154,7 @@ class ParallelEngine:
         def to_tok(blk):
             B, hb, wb, C = blk.shape
             x = blk.to(self.device).view(B, g.nwy_loc, g.ws_y, g.nwx_loc, g.ws_x, C).permute(0, 1, 3, 2, 4, 5)
-            return self._sp_slice(x.reshape(B * g.tokens_per_rank, C).float())
+            return self._sp_slice(x.reshape(B * g.windows_per_rank * g.L, C).float())
         x = to_tok(tgt_blk)
         if self.t_fn is not None:
             t = self.t_fn(self).to(self.device)

@@ -48,6 +48,7 @@ class AerisConfig:
     model_dtype: torch.dtype = torch.bfloat16
     data_dtype: torch.dtype = torch.float32
     wp: tuple[int, int] = (1, 1)
+    sp: int = 1                     # Ulysses sequence-parallel degree
     chunk_windows: int = 64
     shift_layers: str = "odd"       # which layers use the half-window shift: "odd" | "none"
 
@@ -56,7 +57,7 @@ class AerisConfig:
         return self.n_layers * self.sublayers
 
     def grid(self) -> LY.Grid:
-        return LY.Grid(self.img[0], self.img[1], self.window[0], self.window[1], self.wp[0], self.wp[1])
+        return LY.Grid(self.img[0], self.img[1], self.window[0], self.window[1], self.wp[0], self.wp[1], self.sp)
 
     def eps(self, dtype: torch.dtype) -> float:
         return self.norm_eps if self.norm_eps is not None else float(torch.finfo(dtype).eps)
@@ -276,9 +277,14 @@ class SwinLayer(nn.Module):
                     x = ctx.regroup_unfused(x, regroup[0], regroup[1])
                 p = {"n1": n1.weight, "to_qkv": attn.to_qkv.weight, "wo": attn.wo.weight, "n2": n2.weight,
                      "w1": ff.w1.weight, "w2": ff.w2.weight}
-                x = O.block_forward(x, m, p, n_win_per_sample=ctx.grid.windows_per_rank, L=ctx.grid.L,
+                attn = None
+                if ctx.sp_group is not None and ctx.grid.sp > 1:
+                    from ..parallel.sequence import sp_window_attention
+                    attn = lambda qkv, nw, nl, H, d: sp_window_attention(qkv, nw, nl, H, d, ctx.sp_group,
+                                                                           O.window_attention)
+                x = O.block_forward(x, m, p, n_win_per_sample=ctx.grid.windows_per_rank, L=ctx.grid.n_local,
                                     heads=cfg.heads, head_dim=cfg.head_dim, after_mod_norm=cfg.after_mod_norm,
-                                    eps=eps)
+                                    eps=eps, attention=attn)
         return x
 
 

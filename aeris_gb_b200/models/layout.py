@@ -33,11 +33,13 @@ class Grid:
     ws_x: int
     wp_y: int = 1
     wp_x: int = 1
+    sp: int = 1       # Ulysses sequence parallelism: every window's token sequence is cut into `sp` contiguous slices
 
     def __post_init__(self):
         assert self.H % self.ws_y == 0 and self.W % self.ws_x == 0, "image must be a multiple of the window"
         assert (self.H // self.ws_y) % self.wp_y == 0 and (self.W // self.ws_x) % self.wp_x == 0, \
             "window grid must divide evenly over the WP grid"
+        assert (self.ws_y * self.ws_x) % self.sp == 0, "window tokens must divide evenly over the SP ranks"
 
     @property
     def nwy(self) -> int:
@@ -53,7 +55,13 @@ class Grid:
 
     @property
     def n_ranks(self) -> int:
-        return self.wp_y * self.wp_x
+        """Ranks that together hold one sample: WP grid x SP; rank = wp_rank * sp + sp_rank."""
+        return self.wp_y * self.wp_x * self.sp
+
+    @property
+    def n_local(self) -> int:
+        """Tokens of one window held by one rank."""
+        return self.L // self.sp
 
     @property
     def nwy_loc(self) -> int:
@@ -70,10 +78,11 @@ class Grid:
     @property
     def tokens_per_rank(self) -> int:
         """Tokens of ONE sample held by one rank."""
-        return self.windows_per_rank * self.L
+        return self.windows_per_rank * self.n_local
 
     def rank_coords(self, rank: int) -> tuple[int, int]:
-        return rank // self.wp_x, rank % self.wp_x
+        wp_rank = rank // self.sp
+        return wp_rank // self.wp_x, wp_rank % self.wp_x
 
     def half_shift(self) -> tuple[int, int]:
         return self.ws_y // 2, self.ws_x // 2
@@ -90,8 +99,10 @@ def pixel_owner(grid: Grid, shift: tuple[int, int]) -> tuple[np.ndarray, np.ndar
     wx, ix = x // grid.ws_x, x % grid.ws_x
     ry, lwy = wy // grid.nwy_loc, wy % grid.nwy_loc
     rx, lwx = wx // grid.nwx_loc, wx % grid.nwx_loc
-    rank = ry[:, None] * grid.wp_x + rx[None, :]
-    row = ((lwy[:, None] * grid.nwx_loc + lwx[None, :]) * grid.L + iy[:, None] * grid.ws_x + ix[None, :])
+    seq = iy[:, None] * grid.ws_x + ix[None, :]            # position in the window's token sequence
+    sp_rank, tok = seq // grid.n_local, seq % grid.n_local
+    rank = (ry[:, None] * grid.wp_x + rx[None, :]) * grid.sp + sp_rank
+    row = (lwy[:, None] * grid.nwx_loc + lwx[None, :]) * grid.n_local + tok
     return rank.astype(np.int64), row.astype(np.int64)
 
 

@@ -81,11 +81,12 @@ def swiglu(u: torch.Tensor) -> torch.Tensor:
 
 
 def block_forward(x: torch.Tensor, mod: torch.Tensor, p: dict, *, n_win_per_sample: int, L: int, heads: int,
-                  head_dim: int, after_mod_norm: bool, eps: float) -> torch.Tensor:
+                  head_dim: int, after_mod_norm: bool, eps: float, attention=None) -> torch.Tensor:
     """One transformer block on a window-major token stream (parallel_swin.py:454-472).
 
     x: [B * n_win_per_sample * L, D]; mod: [B, 6 D] = (shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp,
-    gate_mlp); p: weights ``n1, to_qkv, wo, n2, w1, w2``.
+    gate_mlp); p: weights ``n1, to_qkv, wo, n2, w1, w2``. ``L`` is the number of tokens of a window held locally
+    (the whole window unless sequence parallel); ``attention`` overrides the attention call (Ulysses SP).
     """
     B = mod.shape[0]
     T, D = x.shape
@@ -99,7 +100,7 @@ def block_forward(x: torch.Tensor, mod: torch.Tensor, p: dict, *, n_win_per_samp
 
     h = pre(xs, sh1, sc1, p["n1"]).reshape(T, D)
     qkv = F.linear(h, p["to_qkv"])
-    o = window_attention(qkv, B * n_win_per_sample, L, heads, head_dim)
+    o = (attention or window_attention)(qkv, B * n_win_per_sample, L, heads, head_dim)
     a = F.linear(o, p["wo"]).view(B, T // B, D)
     xs = xs + g1.unsqueeze(1) * a
     h2 = pre(xs, sh2, sc2, p["n2"]).reshape(T, D)

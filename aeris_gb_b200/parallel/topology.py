@@ -63,6 +63,11 @@ class ProcessGrid:
         c = self.coords(rank)
         return self.grid[c.dp, :, :, c.pp, c.sp].flatten().tolist()
 
+    def replica_ranks(self, rank: int) -> list[int]:
+        """WP x SP ranks that together hold one sample at one pipeline stage (row-major over (wp_y, wp_x, sp))."""
+        c = self.coords(rank)
+        return self.grid[c.dp, :, :, c.pp, :].flatten().tolist()
+
     def dp_ranks(self, rank: int) -> list[int]:
         c = self.coords(rank)
         return self.grid[:, c.wp_y, c.wp_x, c.pp, c.sp].flatten().tolist()
@@ -77,7 +82,7 @@ class ProcessGrid:
 
     def all_group_lists(self, kind: str) -> list[list[int]]:
         fn = {"sp": self.sp_ranks, "pp": self.pp_ranks, "wp": self.wp_ranks, "dp": self.dp_ranks,
-              "weight": self.weight_ranks}[kind]
+              "weight": self.weight_ranks, "replica": self.replica_ranks}[kind]
         seen, out = set(), []
         for r in range(self.used):
             g = tuple(fn(r))
@@ -87,7 +92,8 @@ class ProcessGrid:
         return out
 
     # ---- torch.distributed groups -----------------------------------------------------------------------------
-    def build_groups(self, rank: int, kinds=("sp", "pp", "wp", "dp", "weight"), backend: str | None = None) -> dict:
+    def build_groups(self, rank: int, kinds=("sp", "pp", "wp", "dp", "weight", "replica"),
+                     backend: str | None = None) -> dict:
         """Creates every group of the requested kinds on every rank (``new_group`` is collective over the world) and
         returns this rank's group of each kind. Groups of size 1 are returned as ``None``."""
         import torch.distributed as dist

@@ -17,9 +17,9 @@ from aeris_gb_b200.parallel.topology import ProcessGrid
 IMG, CH, CC = (16, 32), 6, 4
 
 
-def _cfg(wp=(1, 1)):
+def _cfg(wp=(1, 1), sp=1):
     return AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=32, heads=2, head_dim=16,
-                       mlp_dim=64, n_layers=4, sublayers=1, model_dtype=torch.float32, wp=wp, norm_eps=1e-5)
+                       mlp_dim=64, n_layers=4, sublayers=1, model_dtype=torch.float32, wp=wp, sp=sp, norm_eps=1e-5)
 
 
 def _field(seed, C):
@@ -46,15 +46,15 @@ def _noise_fn(eng):
     return _block(_field(3000 + _sample_index(eng), CH), eng)
 
 
-def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_dir, resume):
+def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_dir, resume, SP=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     if world > 1:
         dist.init_process_group("gloo", rank=rank, world_size=world)
-    grid = ProcessGrid(world, PP=PP, WP_Y=WP[0], WP_X=WP[1])
+    grid = ProcessGrid(world, PP=PP, WP_Y=WP[0], WP_X=WP[1], SP=SP)
     ecfg = EngineConfig(gas=gas, overlap_p2p=overlap, dist_optimizer=distopt, checkpoint_dir=ckpt_dir,
                         checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5)
     torch.manual_seed(0)
-    eng = ParallelEngine(_cfg(WP), OptimConfig(lr=0.5, eps=1.0, lr_rampup_img=0, grad_clip_max_norm=0.5, weight_decay=0.0),
+    eng = ParallelEngine(_cfg(WP, SP), OptimConfig(lr=0.5, eps=1.0, lr_rampup_img=0, grad_clip_max_norm=0.5, weight_decay=0.0),
                          DiffusionConfig(grad_scale_parity=False, cond_channels=CC), ecfg, grid, rank, "cpu",
                          data_fn=_data_fn, groups={} if world == 1 else None)
     # identical initial weights regardless of the split: every logical stage is seeded by its own index
@@ -76,7 +76,7 @@ def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_
         losses.append(eng.tot_loss)
     if ckpt_dir and not resume:
         eng.save_checkpoint()
-    if eng.c.dp == 0 and eng.c.wp_y == 0 and eng.c.wp_x == 0:
+    if eng.c.dp == 0 and eng.c.wp_y == 0 and eng.c.wp_x == 0 and eng.c.sp == 0:
         torch.save({"sd": {st: {k: v.clone() for k, v in sd.items()} for st, sd in eng.module.logical_state_dicts().items()},
                     "grads": eng.module.logical_state_dicts(eng.last_grads) if not distopt else {},
                     "loss": losses, "norm": eng.total_norm}, os.path.join(out_dir, f"pp{eng.c.pp}.pt"))
@@ -90,7 +90,7 @@ def _launch(world, **kw):
     from conftest import free_port
     port = free_port()
     args = (world, port, kw["PP"], kw["WP"], kw["gas"], kw.get("overlap", False), kw.get("distopt", False),
-            kw["iters"], out, kw.get("ckpt_dir"), kw.get("resume", False))
+            kw["iters"], out, kw.get("ckpt_dir"), kw.get("resume", False), kw.get("SP", 1))
     if world == 1:
         _run(0, *args)
     else:
@@ -129,6 +129,12 @@ def test_pp3_matches_single_process(single):
 
 def test_pp2_overlapped_wp2_matches_single_process(single):
     sd, loss, _ = _launch(4, PP=2, WP=(1, 2), gas=4, iters=2, overlap=True)
+    _assert_same(sd, single[0])
+    assert loss == pytest.approx(single[1], rel=1e-4)
+
+
+def test_ulysses_sp2_with_wp2_matches_single_process(single):
+    sd, loss, _ = _launch(4, PP=1, WP=(1, 2), SP=2, gas=4, iters=2)
     _assert_same(sd, single[0])
     assert loss == pytest.approx(single[1], rel=1e-4)
 
