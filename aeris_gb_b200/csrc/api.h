@@ -25,6 +25,16 @@ int aeris_attn_bwd(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0,
                    int ldo, const float* lse, float* delta, void* dqkv, int ldg, int n_win, int N, int H,
                    int head_dim, float scale, int* status, void* stream);
 
+int aeris_gemm_scatter_heads(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int b_mn,
+                             const void* const* peers, int sp, int sp_rank, int n_local, int L, int sec_w, int* status,
+                             void* stream);
+int aeris_attn_fwd_push(const void* qkv, int ld, int H_local, void* o, int ldo, float* lse, int n_win, int N,
+                        int head_dim, float scale, const void* const* o_peers, int sp, int n_local, int push_ld,
+                        int push_col0, int* status, void* stream);
+int aeris_attn_bwd_push(const void* qkv, int ld, int H_local, const void* o, const void* d_o, int ldo, const float* lse,
+                        float* delta, int n_win, int N, int head_dim, float scale, const void* const* dq_peers, int sp,
+                        int n_local, int push_ld, int push_sec_w, int push_col0, int* status, void* stream);
+
 int aeris_modnorm_fwd(const void* x, const void* gidx, const void* const* peer_ptrs, int n_peers, void* x_out,
                       const float* scale, const float* shift, const void* w, void* h, int rows, int D, int mode,
                       float eps, void* stream);

@@ -26,6 +26,10 @@ struct AttnFwdParams {
   int q_col0, k_col0, v_col0;
   float scale_log2;
   int* status;
+  // Ulysses output push (all null / 0 when unused): row `grow` of window `win` belongs to rank grow / push_n_local and
+  // is stored at row win * push_n_local + grow % push_n_local, column push_col0 + head * d of that rank's buffer.
+  void* o_peers[8];
+  int push_n_local, push_ld, push_col0;
 };
 
 // Byte offset of 16-byte vector `v` (0..7) of row `r` inside a [rows x 64] bf16 tile stored with the 128-byte swizzle.
@@ -316,7 +320,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (grow < N) {
             const float inv = 1.f / l;
             const size_t trow = static_cast<size_t>(win) * N + grow;
-            __nv_bfloat16* dst = p.O + trow * p.ldo + head * HD;
+            __nv_bfloat16* dst = p.O ? p.O + trow * p.ldo + head * HD : nullptr;
+            __nv_bfloat16* pdst = nullptr;
+            if (p.push_n_local > 0) {
+              const int owner = grow / p.push_n_local;
+              pdst = reinterpret_cast<__nv_bfloat16*>(p.o_peers[owner]) +
+                     (static_cast<size_t>(win) * p.push_n_local + (grow - owner * p.push_n_local)) * p.push_ld +
+                     p.push_col0 + head * HD;
+            }
 #pragma unroll
             for (int c = 0; c < HD; c += 8) {
               uint4 u;
@@ -324,7 +335,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               u.y = pack_bf16x2(acc[c + 2] * inv, acc[c + 3] * inv);
               u.z = pack_bf16x2(acc[c + 4] * inv, acc[c + 5] * inv);
               u.w = pack_bf16x2(acc[c + 6] * inv, acc[c + 7] * inv);
-              *reinterpret_cast<uint4*>(dst + c) = u;
+              if (dst) *reinterpret_cast<uint4*>(dst + c) = u;
+              if (pdst) *reinterpret_cast<uint4*>(pdst + c) = u;
             }
             if (p.lse) p.lse[(static_cast<size_t>(win) * p.H + head) * N + grow] = m + log2f(l);
           }
@@ -372,8 +384,24 @@ struct AttnBwdParams {
   int q_col0, k_col0, v_col0;
   float scale_log2, scale;
   int* status;
+  // Ulysses gradient push (null / 0 when unused): the gradient row of token `grow` goes to rank grow / push_n_local,
+  // row win * push_n_local + grow % push_n_local, column section * push_sec_w + push_col0 + head * d.
+  void* dq_peers[8];
+  int push_n_local, push_ld, push_sec_w, push_col0;
 };
-constexpr int BT = 64;  // streamed tile rows in the backward kernels
+constexpr int BT = 64;
+
+template <int HD>
+__device__ __forceinline__ __nv_bfloat16* bwd_dst(const AttnBwdParams& p, int win, int grow, int head, int section,
+                                                  int local_col0) {
+  if (p.push_n_local > 0) {
+    const int owner = grow / p.push_n_local;
+    return reinterpret_cast<__nv_bfloat16*>(p.dq_peers[owner]) +
+           (static_cast<size_t>(win) * p.push_n_local + (grow - owner * p.push_n_local)) * p.push_ld +
+           section * p.push_sec_w + p.push_col0 + head * HD;
+  }
+  return p.dQKV + (static_cast<size_t>(win) * p.N + grow) * p.ldg + local_col0 + head * HD;
+}  // streamed tile rows in the backward kernels
 
 // Both backward kernels stream 64-row tiles but run the tensor core and the math warps at a granularity of 32 score
 // columns ("halves"), double buffered in TMEM: while the math warps turn half g into dS (and P), the tensor core is
@@ -596,7 +624,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     if (ok && mbar_wait(dq_full, 0, p.status, ERR_TIMEOUT_ATTN)) {
       tc_fence_after();
-      __nv_bfloat16* dst = p.dQKV + trow * p.ldg + p.q_col0 + head * HD;
+      __nv_bfloat16* dst = bwd_dst<HD>(p, win, row_ok ? grow : 0, head, 0, p.q_col0);
 #pragma unroll
       for (int c = 0; c < HD; c += 32) {
         uint32_t v[32];
@@ -818,8 +846,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (ok && mbar_wait(acc_full, 0, p.status, ERR_TIMEOUT_ATTN)) {
       tc_fence_after();
       const size_t trow = static_cast<size_t>(win) * N + (row_ok ? grow : 0);
-      __nv_bfloat16* dk = p.dQKV + trow * p.ldg + p.k_col0 + head * HD;
-      __nv_bfloat16* dv = p.dQKV + trow * p.ldg + p.v_col0 + head * HD;
+      __nv_bfloat16* dk = bwd_dst<HD>(p, win, row_ok ? grow : 0, head, 1, p.k_col0);
+      __nv_bfloat16* dv = bwd_dst<HD>(p, win, row_ok ? grow : 0, head, 2, p.v_col0);
+      (void)trow;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const uint32_t t = which ? tdV : tdK;
@@ -881,13 +910,39 @@ static int launch_attn_bwd(const CUtensorMap& tq128, const CUtensorMap& tk64, co
 using namespace aeris;
 
 // q, k, v: base pointers of row-major [n_win * N, ld*] bf16 tensors; *_col0 = column of head 0.
+static int attn_fwd_impl(const void* q, int ldq, int q_col0, const void* k, int ldk, int k_col0, const void* v,
+                         int ldv, int v_col0, void* o, int ldo, float* lse, int n_win, int N, int H, int head_dim,
+                         float scale, int* status, void* stream_, const void* const* o_peers, int sp,
+                         int push_n_local, int push_ld, int push_col0);
+
 extern "C" int aeris_attn_fwd(const void* q, int ldq, int q_col0, const void* k, int ldk, int k_col0, const void* v,
                               int ldv, int v_col0, void* o, int ldo, float* lse, int n_win, int N, int H,
                               int head_dim, float scale, int* status, void* stream_) {
+  return attn_fwd_impl(q, ldq, q_col0, k, ldk, k_col0, v, ldv, v_col0, o, ldo, lse, n_win, N, H, head_dim, scale, status,
+                       stream_, nullptr, 0, 0, 0, 0);
+}
+
+// Forward whose output rows are (also) pushed to the ranks that own the tokens (Ulysses return exchange fused into the
+// attention epilogue). `o` may be null when only the pushed copy is wanted.
+extern "C" int aeris_attn_fwd_push(const void* qkv, int ld, int H_local, void* o, int ldo, float* lse, int n_win, int N,
+                                   int head_dim, float scale, const void* const* o_peers, int sp, int n_local,
+                                   int push_ld, int push_col0, int* status, void* stream_) {
+  const int hd = H_local * head_dim;
+  return attn_fwd_impl(qkv, ld, 0, qkv, ld, hd, qkv, ld, 2 * hd, o, ldo, lse, n_win, N, H_local, head_dim, scale,
+                       status, stream_, o_peers, sp, n_local, push_ld, push_col0);
+}
+
+static int attn_fwd_impl(const void* q, int ldq, int q_col0, const void* k, int ldk, int k_col0, const void* v,
+                         int ldv, int v_col0, void* o, int ldo, float* lse, int n_win, int N, int H, int head_dim,
+                         float scale, int* status, void* stream_, const void* const* o_peers, int sp,
+                         int push_n_local, int push_ld, int push_col0) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (head_dim != 64 && head_dim != 128) return -1;
   if (n_win <= 0 || N <= 0 || H <= 0 || n_win > 65535 || H > 65535) return -2;
+  if (sp < 0 || sp > 8 || (!o && !o_peers)) return -3;
   AttnFwdParams p{};
+  for (int i = 0; i < sp; ++i) p.o_peers[i] = const_cast<void*>(o_peers[i]);
+  p.push_n_local = o_peers ? push_n_local : 0; p.push_ld = push_ld; p.push_col0 = push_col0;
   p.O = reinterpret_cast<__nv_bfloat16*>(o); p.ldo = ldo; p.lse = lse; p.N = N; p.H = H; p.n_win = n_win;
   p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
@@ -901,13 +956,39 @@ extern "C" int aeris_attn_fwd(const void* q, int ldq, int q_col0, const void* k,
 
 // Backward. qkv: fused [T, ldq] tensor (q/k/v column blocks at *_col0); o, d_o: [T, ldo]; dqkv: [T, ldg] (same
 // column layout as qkv); lse from the forward; delta: scratch [n_win*H*N] fp32 written by the first kernel.
+static int attn_bwd_impl(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0, const void* o, const void* d_o,
+                         int ldo, const float* lse, float* delta, void* dqkv, int ldg, int n_win, int N, int H,
+                         int head_dim, float scale, int* status, void* stream_, const void* const* dq_peers, int sp,
+                         int push_n_local, int push_ld, int push_sec_w, int push_col0);
+
 extern "C" int aeris_attn_bwd(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0, const void* o,
                               const void* d_o, int ldo, const float* lse, float* delta, void* dqkv, int ldg,
                               int n_win, int N, int H, int head_dim, float scale, int* status, void* stream_) {
+  return attn_bwd_impl(qkv, ldq, q_col0, k_col0, v_col0, o, d_o, ldo, lse, delta, dqkv, ldg, n_win, N, H, head_dim,
+                       scale, status, stream_, nullptr, 0, 0, 0, 0, 0);
+}
+
+// Backward whose dQ / dK / dV rows are pushed to the ranks that own the tokens (layout [tokens_local, 3 * heads * d]).
+extern "C" int aeris_attn_bwd_push(const void* qkv, int ld, int H_local, const void* o, const void* d_o, int ldo,
+                                   const float* lse, float* delta, int n_win, int N, int head_dim, float scale,
+                                   const void* const* dq_peers, int sp, int n_local, int push_ld, int push_sec_w,
+                                   int push_col0, int* status, void* stream_) {
+  const int hd = H_local * head_dim;
+  return attn_bwd_impl(qkv, ld, 0, hd, 2 * hd, o, d_o, ldo, lse, delta, nullptr, 0, n_win, N, H_local, head_dim, scale,
+                       status, stream_, dq_peers, sp, n_local, push_ld, push_sec_w, push_col0);
+}
+
+static int attn_bwd_impl(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0, const void* o, const void* d_o,
+                         int ldo, const float* lse, float* delta, void* dqkv, int ldg, int n_win, int N, int H,
+                         int head_dim, float scale, int* status, void* stream_, const void* const* dq_peers, int sp,
+                         int push_n_local, int push_ld, int push_sec_w, int push_col0) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (head_dim != 64 && head_dim != 128) return -1;
   if (n_win <= 0 || N <= 0 || H <= 0 || n_win > 65535 || H > 65535) return -2;
+  if (sp < 0 || sp > 8 || (!dqkv && !dq_peers)) return -3;
   AttnBwdParams p{};
+  for (int i = 0; i < sp; ++i) p.dq_peers[i] = const_cast<void*>(dq_peers[i]);
+  p.push_n_local = dq_peers ? push_n_local : 0; p.push_ld = push_ld; p.push_sec_w = push_sec_w; p.push_col0 = push_col0;
   p.O = reinterpret_cast<const __nv_bfloat16*>(o); p.dO = reinterpret_cast<const __nv_bfloat16*>(d_o); p.ldo = ldo;
   p.lse = lse; p.delta = delta; p.dQKV = reinterpret_cast<__nv_bfloat16*>(dqkv); p.ldg = ldg;
   p.N = N; p.H = H; p.n_win = n_win; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;

@@ -319,3 +319,27 @@ extern "C" int aeris_gemm_bf16_2cta(const void* A, const void* B, void* C, int M
   if (a_mn && !b_mn) return launch_gemm2<1, 0>(ta, tb, p, stream);
   return launch_gemm2<1, 1>(ta, tb, p, stream);
 }
+
+// QKV (or dO) projection whose epilogue performs the Ulysses head<->sequence exchange: C is not written locally;
+// every head's tile goes straight into the symmetric buffer of the rank that owns the head (`peers[owner]`).
+// A: [M, K] row-major tokens (M = windows * n_local), B: [N, K] weights (or stored [K, N] with b_mn).
+extern "C" int aeris_gemm_scatter_heads(const void* A, const void* B, int M, int N, int K, int lda, int ldb,
+                                        int b_mn, const void* const* peers, int sp, int sp_rank, int n_local, int L,
+                                        int sec_w, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N % G2_BN != 0 || K <= 0 || sp < 1 || sp > 8) return -1;
+  if (sec_w % sp != 0 || (sec_w / sp) % 32 != 0 || N % sec_w != 0 || M % n_local != 0) return -2;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.epi = EPI_SCATTER_HEADS; p.C = nullptr; p.ldc = 0;
+  p.rows_per_gate = M; p.k_splits = 1; p.status = status;
+  p.b_tile_stride = G2_BN; p.b_half_off = G2_BN / 2;
+  for (int i = 0; i < sp; ++i) p.scat_peers[i] = const_cast<void*>(peers[i]);
+  p.scat_rank = sp_rank; p.scat_n_local = n_local; p.scat_L = L; p.scat_sec_w = sec_w; p.scat_own_w = sec_w / sp;
+  p.scat_ld = (N / sec_w) * (sec_w / sp);
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d_bf16(&ta, A, K, M, lda, G2_BK, G2_BM);
+  if (r) return r;
+  r = b_mn ? make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, G2_BK) : make_tmap_2d_bf16(&tb, B, K, N, ldb, G2_BK, G2_BN / 2);
+  if (r) return r - 100;
+  return b_mn ? launch_gemm2<0, 1>(ta, tb, p, stream) : launch_gemm2<0, 0>(ta, tb, p, stream);
+}

@@ -6,7 +6,9 @@ namespace aeris {
 
 enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GATE_RESID = 2, EPI_ACC_F32 = 3, EPI_STORE_F32 = 4,
               EPI_SWIGLU_BOTH = 5,   // EPI_SWIGLU that also stores the raw [gate | up] product to aux [M, 2F]
-              EPI_SWIGLU_BWD = 6 };  // acc = d(act); reads u = [gate | up] from resid [M, 2F], writes d(u) to C [M, 2F]
+              EPI_SWIGLU_BWD = 6,    // acc = d(act); reads u = [gate | up] from resid [M, 2F], writes d(u) to C [M, 2F]
+              EPI_SCATTER_HEADS = 7 };  // Ulysses: every head's columns are stored into the buffer of the rank that
+                                        // owns the head (peer memory), rows re-indexed to whole-window order
 
 struct GemmParams {
   int M, N, K;
@@ -23,6 +25,11 @@ struct GemmParams {
   int b_half_off;              // row offset of the second half-box of B (BN/2, or F for SwiGLU)
   int k_splits;
   int swiglu_f;                // F for the SwiGLU epilogues
+  // EPI_SCATTER_HEADS: source columns are `n_sec` sections of width sec_w (q | k | v, or one section); inside a section
+  // the columns of rank r's heads are [r * own_w, (r + 1) * own_w). Source row (window w, local token i) goes to row
+  // w * L + rank * n_local + i of the owner's [*, n_sec * own_w] buffer.
+  void* scat_peers[8];
+  int scat_rank, scat_n_local, scat_L, scat_sec_w, scat_own_w, scat_ld;
   int* status;
 };
 
@@ -33,7 +40,30 @@ template <int BN>
 __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t taddr, int row, bool row_ok, int tn,
                                                   bool kempty) {
 
-  if (p.epi == EPI_SWIGLU_BWD) {
+  if (p.epi == EPI_SCATTER_HEADS) {
+    const int w = row / p.scat_n_local;
+    const size_t drow = static_cast<size_t>(w) * p.scat_L + p.scat_rank * p.scat_n_local + (row - w * p.scat_n_local);
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c, v);
+      tmem_wait_ld();
+      if (row_ok) {
+        const int c0 = tn * BN + c;
+        const int sec = c0 / p.scat_sec_w;
+        const int hc = c0 - sec * p.scat_sec_w;
+        const int owner = hc / p.scat_own_w;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld +
+                             sec * p.scat_own_w + (hc - owner * p.scat_own_w);
+        uint32_t o[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+      }
+    }
+  } else if (p.epi == EPI_SWIGLU_BWD) {
     // d(gate) = d(act) * up * dsilu(gate), d(up) = d(act) * silu(gate); u is read and d(u) written in place
     const __nv_bfloat16* usrc = p.resid + static_cast<size_t>(row) * p.ldr + tn * BN;
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * BN;

@@ -43,12 +43,16 @@ def wp_grid_for(n: int) -> tuple[int, int]:
 class Trainer:
     def __init__(self, model_cfg: AerisConfig, optim_cfg: OptimConfig, diff_cfg: DiffusionConfig, device,
                  seed: int = 1234, wp_group=None, dp_size: int = 1, dp_rank: int = 0, model: AerisModel | None = None,
-                 fused_dp: bool | None = None, use_multicast: bool = True):
+                 fused_dp: bool | None = None, use_multicast: bool = True, sp_group=None):
         self.cfg, self.ocfg, self.dcfg = model_cfg, optim_cfg, diff_cfg
         self.device = torch.device(device)
+        # `wp_group`: every rank that shares a sample (WP grid x SP), ordered (wp_y, wp_x, sp); `sp_group`: the ranks that
+        # share this rank's windows (Ulysses)
         self.wp_group = wp_group
-        self.wp_size = model_cfg.wp[0] * model_cfg.wp[1]
+        self.sp_group = sp_group
+        self.wp_size = model_cfg.wp[0] * model_cfg.wp[1] * model_cfg.sp
         self.wp_rank = dist.get_rank(wp_group) if (self.wp_size > 1) else 0
+        self.sp_rank = self.wp_rank % model_cfg.sp
         self.dp_size, self.dp_rank = dp_size, dp_rank
         torch.manual_seed(seed)   # identical initial weights on every rank
         self.model = (model or AerisModel(model_cfg)).to(self.device)
@@ -75,12 +79,19 @@ class Trainer:
             self.halo = HaloExchange(wp_group, self.device)
         self.timers: dict[str, float] = {}
         self.last_norm = 0.0
+        self._sp_exchange = None
 
     # ------------------------------------------------------------------------------------------------ helpers
     def context(self, batch: int) -> StreamContext:
         if batch not in self._ctx:
             peer_fn = self.halo.peer_fn if self.halo is not None else None
-            self._ctx[batch] = StreamContext(self.cfg, batch, self.wp_rank, peer_fn)
+            ctx = StreamContext(self.cfg, batch, self.wp_rank, peer_fn, wp_group=self.wp_group, sp_group=self.sp_group)
+            if self.cfg.sp > 1 and self.device.type == "cuda":
+                if self._sp_exchange is None:
+                    from ..models.fused import SPExchange
+                    self._sp_exchange = SPExchange(self.sp_group, self.device)
+                ctx.sp_exchange = self._sp_exchange
+            self._ctx[batch] = ctx
         return self._ctx[batch]
 
     def w_lat_tokens(self) -> torch.Tensor:
@@ -95,6 +106,9 @@ class Trainer:
         B, hb, wb, C = block.shape
         g = self.grid
         x = block.view(B, g.nwy_loc, g.ws_y, g.nwx_loc, g.ws_x, C).permute(0, 1, 3, 2, 4, 5)
+        x = x.reshape(B * g.windows_per_rank, g.L, C)
+        if g.sp > 1:      # this rank's contiguous slice of every window's token sequence
+            x = x[:, self.sp_rank * g.n_local:(self.sp_rank + 1) * g.n_local]
         return x.reshape(B * g.tokens_per_rank, C)
 
     def tokens_to_block(self, tok: torch.Tensor, B: int) -> torch.Tensor:

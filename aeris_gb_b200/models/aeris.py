@@ -87,6 +87,7 @@ class StreamContext:
         self.cfg = cfg
         self.wp_group = wp_group      # torch.distributed group of the WP peers (CPU re-partition, result gathers)
         self.sp_group = sp_group      # Ulysses sequence-parallel group, None when SP = 1
+        self.sp_exchange = None       # CUDA path: fused.SPExchange of that group
         self.grid = cfg.grid()
         self.batch = batch
         self.rank = rank
@@ -263,9 +264,9 @@ class SwinLayer(nn.Module):
             if use_fused(x):
                 from . import fused
                 from ..ops import elementwise as E
-                meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.L, cfg.heads, cfg.head_dim,
+                meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.n_local, cfg.heads, cfg.head_dim,
                                        E.MODE_MOD_THEN_NORM if cfg.after_mod_norm else E.MODE_NORM_THEN_MOD,
-                                       eps, cfg.chunk_windows)
+                                       eps, cfg.chunk_windows, sp=ctx.sp_exchange if ctx.grid.sp > 1 else None)
                 rg = None
                 if j == 0 and regroup is not None:
                     rg = (ctx.table(regroup[0], regroup[1], x.device), ctx.table(regroup[1], regroup[0], x.device),

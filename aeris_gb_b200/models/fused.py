@@ -29,6 +29,7 @@ class BlockMeta:
     mode: int                  # E.MODE_MOD_THEN_NORM or E.MODE_NORM_THEN_MOD
     eps: float
     chunk_windows: int = 64
+    sp: "SPExchange | None" = None     # Ulysses sequence parallelism: L is then the LOCAL token count of a window
 
 
 class Workspace:
@@ -61,10 +62,106 @@ def workspace() -> Workspace:
     return _WS
 
 
+class SPExchange:
+    """Symmetric buffers and rank barrier of one Ulysses sequence-parallel group.
+
+    The exchanges of src/aeris/parallelism/sequence_parallel.py:40-86 (three all-to-alls before and one after every
+    attention, and their mirrors in backward) do not exist as separate operations here: the QKV GEMM's epilogue stores
+    each head's tile into the buffer of the rank that owns the head, and the attention kernels store their output
+    (forward) and dQ/dK/dV (backward) into the buffers of the ranks that own the tokens. What is left of the
+    collective is a flag barrier between producer and consumer kernels.
+    """
+
+    def __init__(self, group, device, timeout_s: float = 20.0):
+        import torch.distributed as dist
+        from ..engine.fused_dp import RankBarrier
+        self.group, self.device = group, torch.device(device)
+        self.sp, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.barrier = RankBarrier(group, self.device, timeout_s)
+        self._bufs: dict[str, tuple] = {}
+
+    def buffer(self, name: str, shape: tuple[int, int]) -> tuple[torch.Tensor, list[int]]:
+        """Symmetric bf16 buffer of at least ``shape`` (every rank must ask for the same sizes in the same order)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        n = shape[0] * shape[1]
+        ent = self._bufs.get(name)
+        if ent is None or ent[0].numel() < n:
+            t = symm_mem.empty(n, dtype=torch.bfloat16, device=self.device)
+            hdl = symm_mem.rendezvous(t, self.group)
+            ent = (t, [int(x) for x in hdl.buffer_ptrs], hdl)
+            self._bufs[name] = ent
+        return ent[0][:n].view(*shape), ent[1]
+
+
+def _scatter_heads(a: torch.Tensor, w: torch.Tensor, sp: "SPExchange", peers: list[int], n_local: int, L: int,
+                   sec_w: int, b_t: bool = False):
+    """``a @ w^T`` (or ``a @ w`` with ``b_t``) whose head tiles go to their owner ranks (GEMM-epilogue Ulysses)."""
+    import ctypes
+    from ..ops import lib as _l
+    M, K = a.shape
+    N = w.shape[1] if b_t else w.shape[0]
+    arr = (ctypes.c_void_p * len(peers))(*peers)
+    rc = _l.lib().aeris_gemm_scatter_heads(_l.ptr(a), _l.ptr(w), M, N, K, a.stride(0), w.stride(0), int(b_t), arr,
+                                           sp.sp, sp.rank, n_local, L, sec_w, _l.ptr(_l.status_word()),
+                                           _l.stream_ptr())
+    _l.check(rc, "aeris_gemm_scatter_heads")
+
+
 def _chunks(meta: BlockMeta):
     step = min(meta.chunk_windows, meta.n_win_per_sample)
     for w0 in range(0, meta.n_win_per_sample, step):
         yield w0, min(step, meta.n_win_per_sample - w0)
+
+
+def _sp_attention_fwd(meta: BlockMeta, h: torch.Tensor, wqkv: torch.Tensor, nw: int, keep_local: bool):
+    """Sequence-parallel attention of one chunk. ``h`` [nw * n_local, D] -> o [nw * n_local, heads * d] (tokens of this
+    rank, all heads). Returns (o, state for the backward pass)."""
+    import ctypes
+    from ..ops import lib as _l
+    sp = meta.sp
+    n_local, L = meta.L, meta.L * sp.sp
+    hl, d = meta.heads // sp.sp, meta.head_dim
+    HD = meta.heads * d
+    n, nf = nw * n_local, nw * L
+    qkv_full, qkv_peers = sp.buffer("qkv_full", (nf, 3 * hl * d))
+    o_loc, o_peers = sp.buffer("o_loc", (n, HD))
+    _scatter_heads(h, wqkv, sp, qkv_peers, n_local, L, HD)
+    sp.barrier()                                  # every rank's q/k/v tiles for my heads have landed
+    o_full = _WS.get("sp_o_full", (nf, hl * d), torch.bfloat16, h.device) if keep_local else None
+    lse = _WS.get("sp_lse", (nw, hl, L), torch.float32, h.device)
+    arr = (ctypes.c_void_p * sp.sp)(*o_peers)
+    rc = _l.lib().aeris_attn_fwd_push(_l.ptr(qkv_full), qkv_full.stride(0), hl, _l.ptr(o_full),
+                                      o_full.stride(0) if o_full is not None else 0, _l.ptr(lse), nw, L, d,
+                                      _l._c_float(1.0 / d ** 0.5), arr, sp.sp, n_local, HD, sp.rank * hl * d,
+                                      _l.ptr(_l.status_word()), _l.stream_ptr())
+    _l.check(rc, "aeris_attn_fwd_push")
+    sp.barrier()                                  # every rank's output rows for my tokens have landed
+    return o_loc, (qkv_full, o_full, lse)
+
+
+def _sp_attention_bwd(meta: BlockMeta, dx1: torch.Tensor, wog: torch.Tensor, nw: int, state):
+    """Backward of :func:`_sp_attention_fwd` up to d(qkv) for this rank's tokens [nw * n_local, 3 * heads * d]."""
+    import ctypes
+    from ..ops import lib as _l
+    sp = meta.sp
+    qkv_full, o_full, lse = state
+    n_local, L = meta.L, meta.L * sp.sp
+    hl, d = meta.heads // sp.sp, meta.head_dim
+    HD = meta.heads * d
+    n, nf = nw * n_local, nw * L
+    do_full, do_peers = sp.buffer("do_full", (nf, hl * d))
+    dqkv_loc, dq_peers = sp.buffer("dqkv_loc", (n, 3 * HD))
+    _scatter_heads(dx1, wog, sp, do_peers, n_local, L, HD, b_t=True)     # d(o) = (dx1 * g1) @ wo, pushed by head
+    sp.barrier()
+    delta = _WS.get("sp_delta", (nw, hl, L), torch.float32, dx1.device)
+    arr = (ctypes.c_void_p * sp.sp)(*dq_peers)
+    rc = _l.lib().aeris_attn_bwd_push(_l.ptr(qkv_full), qkv_full.stride(0), hl, _l.ptr(o_full), _l.ptr(do_full),
+                                      o_full.stride(0), _l.ptr(lse), _l.ptr(delta), nw, L, d,
+                                      _l._c_float(1.0 / d ** 0.5), arr, sp.sp, n_local, 3 * HD, HD, sp.rank * hl * d,
+                                      _l.ptr(_l.status_word()), _l.stream_ptr())
+    _l.check(rc, "aeris_attn_bwd_push", kernels=2)
+    sp.barrier()
+    return dqkv_loc
 
 
 def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv, wo, wn2, w1, w2,
@@ -102,10 +199,14 @@ def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv
                               gather_idx=table[r0:r0 + n], peer_ptrs=peers, x_out=xc, rows=n)
             else:
                 E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h[:n])
-            G.gemm(h[:n], wqkv, out=qkv[:n])
-            A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n],
-                       lse=lse[:n * meta.heads].view(nw, meta.heads, meta.L))
-            G.gemm(o[:n], wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
+            if meta.sp is None:
+                G.gemm(h[:n], wqkv, out=qkv[:n])
+                A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n],
+                           lse=lse[:n * meta.heads].view(nw, meta.heads, meta.L))
+                oc = o[:n]
+            else:
+                oc = _sp_attention_fwd(meta, h[:n], wqkv, nw, keep_local=False)[0]
+            G.gemm(oc, wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
             E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=h[:n])
             G.gemm(h[:n], w1, out=act[:n], epi=G.EPI_SWIGLU)
             G.gemm(act[:n], w2, out=y[r0:r0 + n], epi=G.EPI_GATE_RESID, resid=x1[:n], gate=g2)
@@ -157,9 +258,13 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
             lse_c = lse[:n * meta.heads].view(nw, meta.heads, meta.L)
             # ---- recompute the chunk's forward internals
             E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h1[:n])
-            G.gemm(h1[:n], wqkv, out=qkv[:n])
-            A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n], lse=lse_c)
-            G.gemm(o[:n], wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
+            if meta.sp is None:
+                G.gemm(h1[:n], wqkv, out=qkv[:n])
+                A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n], lse=lse_c)
+                oc = o[:n]
+            else:
+                oc, sp_state = _sp_attention_fwd(meta, h1[:n], wqkv, nw, keep_local=True)
+            G.gemm(oc, wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
             E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=h2[:n])
             G.gemm(h2[:n], w1, out=act[:n], epi=G.EPI_SWIGLU_BOTH, aux=u[:n])         # act and the raw [gate | up]
             # ---- MLP half: y = x1 + g2 * (act @ w2^T)
@@ -171,12 +276,16 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
             E.modnorm_bwd(x1[:n], dh[:n], dyc, sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, dx=dx1[:n],
                           dscale=dsc2, dshift=dsh2, dw=grads["n2"])
             # ---- attention half: x1 = x + g1 * (o @ wo^T)
-            G.gemm(dx1[:n], wog, b_t=True, out=d_o[:n])                                # do = (dx1 * g1) @ wo
-            G.gemm(dx1[:n], o[:n], a_t=True, b_t=True, out=Go, epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
-            A.attn_bwd(qkv[:n], o[:n], d_o[:n], lse_c, nw, meta.L, meta.heads, meta.head_dim, dqkv=dqkv[:n],
-                       delta=delta[:n * meta.heads].view(nw, meta.heads, meta.L))
-            G.gemm(dqkv[:n], wqkv, b_t=True, out=dh[:n])                               # dh1 = dqkv @ wqkv
-            G.gemm(dqkv[:n], h1[:n], a_t=True, b_t=True, out=grads["to_qkv"], epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+            G.gemm(dx1[:n], oc, a_t=True, b_t=True, out=Go, epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+            if meta.sp is None:
+                G.gemm(dx1[:n], wog, b_t=True, out=d_o[:n])                            # do = (dx1 * g1) @ wo
+                A.attn_bwd(qkv[:n], o[:n], d_o[:n], lse_c, nw, meta.L, meta.heads, meta.head_dim, dqkv=dqkv[:n],
+                           delta=delta[:n * meta.heads].view(nw, meta.heads, meta.L))
+                dq_c = dqkv[:n]
+            else:
+                dq_c = _sp_attention_bwd(meta, dx1[:n], wog, nw, sp_state)
+            G.gemm(dq_c, wqkv, b_t=True, out=dh[:n])                                   # dh1 = dqkv @ wqkv
+            G.gemm(dq_c, h1[:n], a_t=True, b_t=True, out=grads["to_qkv"], epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
             E.modnorm_bwd(xc, dh[:n], dx1[:n], sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, dx=dx[r0:r0 + n],
                           dscale=dsc1, dshift=dsh1, dw=grads["n1"])
         # per-sample gate handling: dW += g * G ; dg = rowsum(W * G) ; G <- 0

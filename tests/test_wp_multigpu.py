@@ -9,14 +9,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("n", [2, 4])
-def test_wp_parity(n):
+@pytest.mark.parametrize("n,sp", [(2, 1), (4, 1), (2, 2), (4, 2)])
+def test_wp_parity(n, sp):
+    """Window parallelism (halo pulled from peer memory) and Ulysses sequence parallelism (head<->sequence exchange
+    fused into the QKV GEMM epilogue and the attention epilogues) against the single-GPU result."""
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
     worker = os.path.join(os.path.dirname(__file__), "wp_worker.py")
-    port = 29500 + n
+    port = 29500 + n + 10 * sp
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-                        "--master-addr", "127.0.0.1", "--master-port", str(port), worker],
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), worker, str(sp)],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
 

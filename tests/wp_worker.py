@@ -25,8 +25,9 @@ def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=dev)
-    wp = wp_grid_for(world)
-    base = dict(img=(64, 128), window=(16, 16), in_channels=12, out_channels=6, dim=128, heads=2, head_dim=64,
+    sp = int(sys.argv[1]) if len(sys.argv) > 1 else 1
+    wp = wp_grid_for(world // sp)
+    base = dict(img=(64, 128), window=(16, 16), in_channels=12, out_channels=6, dim=256, heads=4, head_dim=64,
                 mlp_dim=256, n_layers=3, sublayers=1, norm_eps=1e-3, chunk_windows=3)
     B = 2
     torch.manual_seed(7)
@@ -34,7 +35,7 @@ def main():
     for n, p in ref.named_parameters():
         if "modulation" in n and p.dim() == 2:
             torch.nn.init.normal_(p, std=0.05)
-    par = AerisModel(AerisConfig(**base, wp=wp)).to(dev)
+    par = AerisModel(AerisConfig(**base, wp=wp, sp=sp)).to(dev)
     par.load_state_dict(ref.state_dict())
     g = torch.Generator(device="cpu").manual_seed(3)
     x = torch.randn(B, 64, 128, 12, generator=g).to(dev)
@@ -48,6 +49,15 @@ def main():
     grid = cfg.grid()
     halo = HaloExchange(dist.group.WORLD, dev)
     ctx = StreamContext(cfg, B, rank, halo.peer_fn)
+    if sp > 1:
+        from aeris_gb_b200.models.fused import SPExchange
+        sp_group = None
+        for r0 in range(0, world, sp):          # consecutive ranks form an SP group (sp is the fastest grid axis)
+            g_ = dist.new_group(list(range(r0, r0 + sp)))
+            if r0 <= rank < r0 + sp:
+                sp_group = g_
+        ctx.sp_group = sp_group
+        ctx.sp_exchange = SPExchange(sp_group, dev)
     tok = LY.image_to_tokens(x, grid, (0, 0), rank)
     rt = LY.image_to_tokens(r, grid, (0, 0), rank)
     y = par.forward_tokens(tok, t, ctx)
@@ -66,7 +76,7 @@ def main():
     dist.all_reduce(flag, op=dist.ReduceOp.MAX)
     if rank == 0:
         bad = {k: v for k, v in errs.items() if v > 3e-2}
-        print(f"wp={wp} worst rel err {flag.item():.4f} out {errs['out']:.5f} bad={bad}", flush=True)
+        print(f"wp={wp} sp={sp} worst rel err {flag.item():.4f} out {errs['out']:.5f} bad={bad}", flush=True)
     dist.destroy_process_group()
     sys.exit(0 if flag.item() < 3e-2 else 1)
 
