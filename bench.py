@@ -78,19 +78,19 @@ class ClockSampler:
                 "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def flagship_config(n_gpus: int, scale: str):
+def flagship_config(n_gpus: int, scale: str, sp: int = 1):
     import torch
     from aeris_gb_b200.engine.trainer import wp_grid_for
     from aeris_gb_b200.models.aeris import AerisConfig
-    wp = wp_grid_for(n_gpus)
+    wp = wp_grid_for(n_gpus // sp)
     if scale == "full":
         return AerisConfig(img=(720, 1440), window=(30, 30), in_channels=144, out_channels=70, dim=1536, heads=24,
-                           head_dim=64, mlp_dim=4096, n_layers=40, sublayers=1, wp=wp, chunk_windows=72)
+                           head_dim=64, mlp_dim=4096, n_layers=40, sublayers=1, wp=wp, sp=sp, chunk_windows=72)
     if scale == "quarter":   # development size: a quarter of the pixels, a quarter of the depth
         return AerisConfig(img=(360, 720), window=(30, 30), in_channels=144, out_channels=70, dim=1536, heads=24,
-                           head_dim=64, mlp_dim=4096, n_layers=10, sublayers=1, wp=wp, chunk_windows=72)
+                           head_dim=64, mlp_dim=4096, n_layers=10, sublayers=1, wp=wp, sp=sp, chunk_windows=72)
     return AerisConfig(img=(120, 240), window=(30, 30), in_channels=144, out_channels=70, dim=256, heads=4,
-                       head_dim=64, mlp_dim=512, n_layers=4, sublayers=1, wp=wp, chunk_windows=8)
+                       head_dim=64, mlp_dim=512, n_layers=4, sublayers=1, wp=wp, sp=sp, chunk_windows=8)
 
 
 def main():
@@ -103,6 +103,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the number of Swin layers (development only)")
     ap.add_argument("--chunk-windows", type=int, default=0)
+    ap.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel degree (WP = gpus / sp)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -124,7 +125,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
 
-    cfg = flagship_config(world, args.scale)
+    cfg = flagship_config(world, args.scale, args.sp)
     if args.layers:
         cfg.n_layers = args.layers
     if args.chunk_windows:
@@ -132,7 +133,13 @@ def main():
     W = max(args.warmup, 3)
     K = args.steps
     B = world                                   # global batch N, every sample split over the N WP ranks
-    trainer = Trainer(cfg, OptimConfig(), DiffusionConfig(), dev, wp_group=group)
+    sp_group = None
+    if args.sp > 1:
+        for r0 in range(0, world, args.sp):     # consecutive ranks share windows (sp is the fastest grid axis)
+            g_ = dist.new_group(list(range(r0, r0 + args.sp)))
+            if r0 <= rank < r0 + args.sp:
+                sp_group = g_
+    trainer = Trainer(cfg, OptimConfig(), DiffusionConfig(), dev, wp_group=group, sp_group=sp_group)
     g = cfg.grid()
     hb, wb = cfg.img[0] // cfg.wp[0], cfg.img[1] // cfg.wp[1]
     gen = torch.Generator().manual_seed(100 + rank)
@@ -197,7 +204,7 @@ def main():
             "config": {"model": f"AERIS Swin TrigFlow dim{cfg.dim} x{cfg.n_blocks} blocks heads{cfg.heads} "
                                 f"mlp{cfg.mlp_dim} window{cfg.window[0]}x{cfg.window[1]} "
                                 f"({cfg.param_count() / 1e9:.2f}B params)",
-                       "global_batch": B, "seq_len": cfg.img[0] * cfg.img[1], "parallelism": f"wp{world}",
+                       "global_batch": B, "seq_len": cfg.img[0] * cfg.img[1], "parallelism": f"wp{world // args.sp}" + (f"xsp{args.sp}" if args.sp > 1 else ""),
                        "scale": args.scale, "activation_checkpointing": "per block",
                        "l2": "inputs (597 MB/step/GPU) and activations are far larger than L2"},
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
