@@ -35,12 +35,14 @@ int aeris_attn_bwd_push(const void* qkv, int ld, int H_local, const void* o, con
                         float* delta, int n_win, int N, int head_dim, float scale, const void* const* dq_peers, int sp,
                         int n_local, int push_ld, int push_sec_w, int push_col0, int* status, void* stream);
 
+// `w` is the bf16 norm weight, or null with the fp32 weight in `w_f32`; `h_lo` (optional) receives the bf16 rounding
+// residual of `h`, so that h + h_lo carries the fp32 result (used by the fp32 output head).
 int aeris_modnorm_fwd(const void* x, const void* gidx, const void* const* peer_ptrs, int n_peers, void* x_out,
                       const float* scale, const float* shift, const void* w, void* h, int rows, int D, int mode,
-                      float eps, void* stream);
+                      float eps, const float* w_f32, void* h_lo, void* stream);
 int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres, const float* scale, const float* shift,
                       const void* w, void* dx, float* dscale, float* dshift, float* dw, int rows, int D, int mode,
-                      float eps, void* stream);
+                      float eps, const float* w_f32, void* stream);
 int aeris_gather_rows(const void* gidx, const void* const* peer_ptrs, int n_peers, void* out, long long rows, int D,
                       void* stream);
 int aeris_swiglu_fwd(const void* u, void* act, long long rows, int F, void* stream);
@@ -62,6 +64,26 @@ int aeris_shard_adamw_allgather(float* master, const float* grad, float* m, floa
                                 const void* const* param_ptrs, void* mc_params, int world, long long lo, long long n,
                                 const double* norm_sq, float lr, float beta1, float beta2, float eps,
                                 float weight_decay, int step, float max_norm, float ema_beta, void* stream);
+
+// Geometry of one rank's token stream and image block (see csrc/diffusion.cu).
+typedef struct TokGeom {
+  int B, nwy_loc, nwx_loc, ws_y, ws_x, n_local, sp_rank;
+  int y0, x0, H, W;
+  long long sample0;
+} TokGeom;
+int aeris_embed_pack(const float* x_img, const float* c_img, const float* cs, const TokGeom* g, int Cx, int Cc,
+                     const float* ape_y, const float* ape_x, int ape_ch, unsigned long long seed, float sd, int noise,
+                     void* out, int KP, long long row0, long long rows, void* stream);
+int aeris_trigflow_loss(const float* pred, int ldp, const float* x_img, const float* cs, const TokGeom* g, int Cx,
+                        unsigned long long seed, float sd, const float* w_var, const float* w_lat, float inv_rows,
+                        float gscale, void* dpred, int ldd, double* loss, long long row0, long long rows, void* stream);
+int aeris_sampler_update(float* x_out, const float* x_base, const float* pa, const float* pb, int ldp, float ca,
+                         float cb, const TokGeom* g, int Cx, void* stream);
+int aeris_noise_mix(float* x, float a, float b, unsigned long long seed, const TokGeom* g, int Cx, void* stream);
+int aeris_affine_channels(float* out, const float* in, const float* a, const float* b, const float* add, long long n,
+                          int C, void* stream);
+int aeris_gemv_bias_act(const void* W, int w_f32, const float* bias, const float* x, float* y, int N, int K, int B,
+                        int act, int silu_in, void* stream);
 
 #ifdef __cplusplus
 }

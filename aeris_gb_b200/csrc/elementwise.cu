@@ -74,7 +74,8 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
                                    PeerPtrs peers, __nv_bfloat16* __restrict__ x_out,
                                    const float* __restrict__ scale, const float* __restrict__ shift,
                                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h, int rows,
-                                   int D, int mode, float eps, int rows_per_cta) {
+                                   int D, int mode, float eps, int rows_per_cta, const float* __restrict__ wf,
+                                   __nv_bfloat16* __restrict__ h_lo) {
   __shared__ float red[2 * FWD_RPI * 32];
   const int c0 = threadIdx.x * 8;
   const bool active = c0 < D;
@@ -84,7 +85,7 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
   if (active) {
     if (scale) loadf8(scale + c0, sc);
     if (shift) loadf8(shift + c0, sh);
-    load8(w + c0, wv);
+    if (wf) loadf8(wf + c0, wv); else load8(w + c0, wv);
   }
   const int r0 = blockIdx.x * rows_per_cta;
   const int r1 = min(rows, r0 + rows_per_cta);
@@ -130,6 +131,11 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
           o[i] = (mode == 0) ? n : fmaf(n, sc[i], n) + sh[i];
         }
         store8(h + static_cast<size_t>(rr) * D + c0, o);
+        if (h_lo) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] -= __bfloat162float(__float2bfloat16_rn(o[i]));
+          store8(h_lo + static_cast<size_t>(rr) * D + c0, o);
+        }
       }
     }
   }
@@ -142,7 +148,7 @@ __global__ void modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __
                                    const float* __restrict__ shift, const __nv_bfloat16* __restrict__ w,
                                    __nv_bfloat16* __restrict__ dx, float* __restrict__ dscale,
                                    float* __restrict__ dshift, float* __restrict__ dw, int rows, int D, int mode,
-                                   float eps, int rows_per_cta) {
+                                   float eps, int rows_per_cta, const float* __restrict__ wf) {
   __shared__ float red[2 * 2 * 32];
   const int c0 = threadIdx.x * 8;
   const bool active = c0 < D;
@@ -152,7 +158,7 @@ __global__ void modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   if (active) {
     if (scale) loadf8(scale + c0, sc);
     if (shift) loadf8(shift + c0, sh);
-    load8(w + c0, wv);
+    if (wf) loadf8(wf + c0, wv); else load8(w + c0, wv);
   }
   const int r0 = blockIdx.x * rows_per_cta;
   const int r1 = min(rows, r0 + rows_per_cta);
@@ -412,8 +418,9 @@ static int pick_rows_per_cta(int rows) {
 
 extern "C" int aeris_modnorm_fwd(const void* x, const void* gidx, const void* const* peer_ptrs, int n_peers,
                                  void* x_out, const float* scale, const float* shift, const void* w, void* h,
-                                 int rows, int D, int mode, float eps, void* stream) {
-  if (D % 8 || D > 8192 || rows <= 0) return -1;
+                                 int rows, int D, int mode, float eps, const float* w_f32, void* h_lo,
+                                 void* stream) {
+  if (D % 8 || D > 8192 || rows <= 0 || (!w && !w_f32)) return -1;
   PeerPtrs pp{};
   for (int i = 0; i < n_peers && i < 16; ++i) pp.p[i] = reinterpret_cast<const __nv_bfloat16*>(peer_ptrs[i]);
   if (gidx && n_peers <= 0) return -2;
@@ -422,21 +429,21 @@ extern "C" int aeris_modnorm_fwd(const void* x, const void* gidx, const void* co
   modnorm_fwd_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const uint32_t*>(gidx), pp,
       reinterpret_cast<__nv_bfloat16*>(x_out), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
-      reinterpret_cast<__nv_bfloat16*>(h), rows, D, mode, eps, rpc);
+      reinterpret_cast<__nv_bfloat16*>(h), rows, D, mode, eps, rpc, w_f32, reinterpret_cast<__nv_bfloat16*>(h_lo));
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 extern "C" int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres, const float* scale,
                                  const float* shift, const void* w, void* dx, float* dscale, float* dshift,
-                                 float* dw, int rows, int D, int mode, float eps, void* stream) {
-  if (D % 8 || D > 8192 || rows <= 0) return -1;
+                                 float* dw, int rows, int D, int mode, float eps, const float* w_f32, void* stream) {
+  if (D % 8 || D > 8192 || rows <= 0 || (!w && !w_f32)) return -1;
   int rpc = pick_rows_per_cta(rows);
   if (rpc < 16) rpc = rows < 16 ? rows : 16;  // amortise the atomic flush of the column sums
   const int grid = (rows + rpc - 1) / rpc;
   modnorm_bwd_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(dh),
       reinterpret_cast<const __nv_bfloat16*>(dres), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
-      reinterpret_cast<__nv_bfloat16*>(dx), dscale, dshift, dw, rows, D, mode, eps, rpc);
+      reinterpret_cast<__nv_bfloat16*>(dx), dscale, dshift, dw, rows, D, mode, eps, rpc, w_f32);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 

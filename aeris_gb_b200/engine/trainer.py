@@ -43,7 +43,8 @@ def wp_grid_for(n: int) -> tuple[int, int]:
 class Trainer:
     def __init__(self, model_cfg: AerisConfig, optim_cfg: OptimConfig, diff_cfg: DiffusionConfig, device,
                  seed: int = 1234, wp_group=None, dp_size: int = 1, dp_rank: int = 0, model: AerisModel | None = None,
-                 fused_dp: bool | None = None, use_multicast: bool = True, sp_group=None):
+                 fused_dp: bool | None = None, use_multicast: bool = True, sp_group=None,
+                 fused_io: bool | None = None):
         self.cfg, self.ocfg, self.dcfg = model_cfg, optim_cfg, diff_cfg
         self.device = torch.device(device)
         # `wp_group`: every rank that shares a sample (WP grid x SP), ordered (wp_y, wp_x, sp); `sp_group`: the ranks that
@@ -77,6 +78,12 @@ class Trainer:
         if self.wp_size > 1:
             from ..parallel.symm import HaloExchange
             self.halo = HaloExchange(wp_group, self.device)
+        # noising, embedding, output head and loss on this library's kernels (counter-based noise that does not depend
+        # on the WP/SP layout) or, with fused_io=False, the PyTorch formulation with torch.randn noise
+        self.fused_io = (self.device.type == "cuda") if fused_io is None else fused_io
+        self.seed = seed
+        self.step_count = 0
+        self._io_tables = None
         self.timers: dict[str, float] = {}
         self.last_norm = 0.0
         self._sp_exchange = None
@@ -131,6 +138,26 @@ class Trainer:
         err = (sd * pred - TF.v_target(x_tok, z, tr)) ** 2 * self._w_var * w_lat
         return err.sum(dim=-1).view(B, rows).mean(dim=1).sum()
 
+    def io_plan(self, batch: int, noise: bool = True, seed: int | None = None):
+        from ..models import fused_io
+        from ..ops import diffusion as DF
+        if self._io_tables is None:
+            ay, ax = fused_io.ape_tables(self.cfg, self.device)
+            w_lat = TF.latitude_weights(self.cfg.img[0], self.dcfg.w_lat_add).to(self.device).contiguous()
+            self._io_tables = (ay, ax, w_lat)
+        ay, ax, w_lat = self._io_tables
+        geom = DF.make_geom(self.grid, batch, self.wp_rank, sample0=self.dp_rank * batch)
+        if seed is None:
+            seed = (self.seed << 32) + self.step_count
+        return fused_io.IoPlan(geom, self.dcfg.sigma_data, seed, noise, ay, ax, self._w_var, w_lat,
+                               self.cfg.eps(self.cfg.data_dtype))
+
+    def loss_images(self, x: torch.Tensor, c: torch.Tensor, t: torch.Tensor, seed: int | None = None) -> torch.Tensor:
+        """Fused-kernel counterpart of :meth:`loss_tokens`: x [B, hb, wb, C_out], c [B, hb, wb, C_cond] on the device."""
+        B = x.shape[0]
+        cs = torch.stack([torch.cos(t), torch.sin(t)], dim=1).float().contiguous()
+        return self.model.loss_images(x.contiguous(), c.contiguous(), cs, t, self.context(B), self.io_plan(B, seed=seed))
+
     def train_step(self, target_host: torch.Tensor, cond_host: torch.Tensor, read_loss: bool = True):
         """One optimizer step on this rank's blocks of ``B`` samples. target_host: [B, H/wp_y, W/wp_x, C_out] fp32
         (standardised residual), cond_host: [B, H/wp_y, W/wp_x, C_cond] fp32; both pinned host tensors.
@@ -139,13 +166,17 @@ class Trainer:
         x = target_host.to(dev, non_blocking=True)
         c = cond_host.to(dev, non_blocking=True)
         B = x.shape[0]
-        x_tok, c_tok = self.block_to_tokens(x), self.block_to_tokens(c)
         t = TF.sample_noise_level(B, self.dcfg.sigma_min, self.dcfg.sigma_max, self.dcfg.sigma_data,
                                   generator=self.nl_rng, device=dev, law=self.dcfg.noise_law)
-        z = torch.randn(x_tok.shape, generator=self.rng, device=dev) * self.dcfg.sigma_data
-        loss = self.loss_tokens(x_tok, c_tok, t, z)
+        if self.fused_io:
+            loss = self.loss_images(x, c, t)
+        else:
+            x_tok, c_tok = self.block_to_tokens(x), self.block_to_tokens(c)
+            z = torch.randn(x_tok.shape, generator=self.rng, device=dev) * self.dcfg.sigma_data
+            loss = self.loss_tokens(x_tok, c_tok, t, z)
         loss.backward()
         self.reduce_and_step(B)
+        self.step_count += 1
         self.last_loss = loss.detach()
         return float(self.last_loss.item()) / B if read_loss else None
 

@@ -228,10 +228,22 @@ class InputStage(nn.Module):
             for r in range(0, rows, step):
                 sl = slice(b * rows + r, b * rows + min(rows, r + step))
                 out[sl] = self.proj(x_tok[sl].to(cfg.data_dtype) + ape[r:r + step]).to(cfg.model_dtype)
+        return out, self.noise_embedding(t)
+
+    def noise_embedding(self, t: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
         emb = O.timestep_embedding(t.to(cfg.data_dtype), cfg.dim, cfg.max_period)
         if not cfg.layerwise_t_emb:
             emb = self.latent_embed(emb)
-        return out, emb.to(cfg.model_dtype)
+        return emb.to(cfg.model_dtype)
+
+    def forward_images(self, x_img: torch.Tensor, c_img: torch.Tensor, cs: torch.Tensor, t: torch.Tensor, plan):
+        """CUDA path from image-layout fields: x_img [B, hb, wb, C_out] (clean target when ``plan.noise``, else the
+        noisy state), c_img [B, hb, wb, C_cond], cs [B, 2] = (cos t, sin t) (or (1, 0) when sampling). Noising,
+        position encoding, window partition and the projection run in :mod:`.fused_io`."""
+        from . import fused_io
+        out = fused_io.EmbedFn.apply(x_img, c_img, cs, self.proj.weight, self.proj.bias, plan)
+        return out, self.noise_embedding(t)
 
 
 class SwinLayer(nn.Module):
@@ -317,6 +329,26 @@ class OutputStage(nn.Module):
         return _HeadFn.apply(x, shift, scale, self.norm.weight, self.head.weight, self)
 
 
+def _out_loss_images(self, x, dt, x_img, cs, plan):
+    """TrigFlow loss of the output stage straight from the stream (CUDA path; see :mod:`.fused_io`)."""
+    from . import fused_io
+    shift, scale = self.modulation(dt.to(self.cfg.data_dtype)).chunk(2, dim=1)
+    return fused_io.HeadLossFn.apply(x, shift, scale, self.norm.weight, self.head.weight, x_img, cs, plan)
+
+
+def _out_predict_tokens(self, x, dt):
+    """Network output in token order, fp32 ``[T, 128]`` (channels past ``out_channels`` are zero); no autograd."""
+    from . import fused_io
+    with torch.no_grad():
+        shift, scale = self.modulation(dt.to(self.cfg.data_dtype)).chunk(2, dim=1)
+        return fused_io.head_forward(x, shift, scale, self.norm.weight, self.head.weight,
+                                     self.cfg.eps(self.cfg.data_dtype))
+
+
+OutputStage.loss_images = _out_loss_images
+OutputStage.predict_tokens = _out_predict_tokens
+
+
 class _HeadFn(torch.autograd.Function):
     """Output stage over a long token stream in 64k-row chunks. Only the (bf16) input is kept for the backward pass,
     which recomputes each chunk in fp32 and writes the input gradient chunk by chunk into one preallocated buffer,
@@ -375,15 +407,30 @@ class AerisModel(nn.Module):
         self.layers = nn.ModuleList([SwinLayer(cfg) for _ in range(cfg.n_layers)]).to(cfg.model_dtype)
         self.output_stage = OutputStage(cfg)
 
-    def forward_tokens(self, x_tok: torch.Tensor, t: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
-        x, dt = self.input_stage(x_tok, t, ctx)
+    def trunk(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
         cur = (0, 0)
         for i, layer in enumerate(self.layers):
             nxt = self.cfg.layer_shift(i)
             x = layer(x, dt, ctx, regroup=(cur, nxt))
             cur = nxt
-        x = ctx.regroup_unfused(x, cur, (0, 0))
-        return self.output_stage(x, dt, ctx)
+        return ctx.regroup_unfused(x, cur, (0, 0))
+
+    def forward_tokens(self, x_tok: torch.Tensor, t: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
+        x, dt = self.input_stage(x_tok, t, ctx)
+        return self.output_stage(self.trunk(x, dt, ctx), dt, ctx)
+
+    def loss_images(self, x_img, c_img, cs, t, ctx: StreamContext, plan) -> torch.Tensor:
+        """Training loss from image-layout fields on the CUDA kernels end to end (noise drawn on the device from
+        ``plan.seed``). Returns the sum over the local batch of the per-sample local-token-mean losses."""
+        x, dt = self.input_stage.forward_images(x_img, c_img, cs, t, plan)
+        return self.output_stage.loss_images(self.trunk(x, dt, ctx), dt, x_img, cs, plan)
+
+    @torch.no_grad()
+    def predict_images(self, x_img, c_img, t, ctx: StreamContext, plan) -> torch.Tensor:
+        """One network evaluation for the sampler: ``x_img`` is the noisy state; returns F in token order [T, 128]."""
+        cs = torch.tensor([[1.0, 0.0]], device=x_img.device).repeat(x_img.shape[0], 1)
+        x, dt = self.input_stage.forward_images(x_img, c_img, cs, t, plan)
+        return self.output_stage.predict_tokens(self.trunk(x, dt, ctx), dt)
 
     def forward(self, x_img: torch.Tensor, t: torch.Tensor) -> torch.Tensor:
         """x_img: [B, H, W, in_channels] fp32; t: [B]. Returns [B, H, W, out_channels] fp32 (single rank)."""

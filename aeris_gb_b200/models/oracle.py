@@ -43,22 +43,29 @@ def timestep_embedding(t: torch.Tensor, dim: int, max_period: float = 10_000) ->
     return emb.reshape(emb.shape[0], 2, -1).flip(1).reshape(*emb.shape)
 
 
+def positional_tables(channels: int, h: int, w: int, max_positions: float = 10_000,
+                      device=None) -> tuple[torch.Tensor, torch.Tensor]:
+    """The two separable factors of :func:`positional_encoding_2d`: a per-row table ``[h, ch]`` for channels
+    ``[0, ch)`` and a per-column table ``[w, ch]`` for channels ``[ch, 2 ch)``, ``ch = 2 ceil(channels / 4)``."""
+    ch = int(math.ceil(channels / 4) * 2)
+    inv_freq = 1.0 / (max_positions ** (torch.arange(0, ch, 2, dtype=torch.float32, device=device) / ch))
+
+    def emb(n):
+        s = torch.arange(n, dtype=torch.float32, device=device).unsqueeze(1) * inv_freq
+        return torch.stack((s.sin(), s.cos()), dim=-1).flatten(-2, -1)
+
+    return emb(h), emb(w)
+
+
 def positional_encoding_2d(channels: int, h: int, w: int, max_positions: float = 10_000,
                            dtype=torch.float32, device=None) -> torch.Tensor:
     """Additive 2-D sinusoidal encoding on the input channels, returned as ``[h, w, channels]``
     (parallel_swin.py:120-155: interleaved sin/cos per axis, first half of the channels for rows, second for
     columns, truncated to ``channels``)."""
-    ch = int(math.ceil(channels / 4) * 2)
-    inv_freq = 1.0 / (max_positions ** (torch.arange(0, ch, 2, dtype=torch.float32, device=device) / ch))
-    pos_y = torch.arange(h, dtype=torch.float32, device=device)
-    pos_x = torch.arange(w, dtype=torch.float32, device=device)
-
-    def emb(pos):
-        s = pos.unsqueeze(1) * inv_freq
-        return torch.stack((s.sin(), s.cos()), dim=-1).flatten(-2, -1)
-
-    ey = emb(pos_y).unsqueeze(1).expand(h, w, ch)
-    ex = emb(pos_x).unsqueeze(0).expand(h, w, ch)
+    ty, tx = positional_tables(channels, h, w, max_positions, device)
+    ch = ty.shape[1]
+    ey = ty.unsqueeze(1).expand(h, w, ch)
+    ex = tx.unsqueeze(0).expand(h, w, ch)
     return torch.cat([ey, ex], dim=-1)[..., :channels].to(dtype)
 
 

@@ -19,15 +19,17 @@ def _peer_array(ptrs: list[int]):
 def modnorm_fwd(x: torch.Tensor, scale: torch.Tensor | None, shift: torch.Tensor | None, w: torch.Tensor, *,
                 mode: int, eps: float, out: torch.Tensor | None = None, gather_idx: torch.Tensor | None = None,
                 peer_ptrs: list[int] | None = None, x_out: torch.Tensor | None = None,
-                rows: int | None = None) -> torch.Tensor:
+                rows: int | None = None, out_lo: torch.Tensor | None = None) -> torch.Tensor:
+    """``w`` bf16, or fp32 (the output head's norm); ``out_lo`` optionally receives ``h - bf16(h)``."""
     D = w.numel()
     rows = rows if rows is not None else (gather_idx.numel() if gather_idx is not None else x.shape[0])
     if out is None:
         out = torch.empty((rows, D), dtype=torch.bfloat16, device=w.device)
     peers = _peer_array(peer_ptrs) if gather_idx is not None else None
+    w32, w = (w, None) if w.dtype == torch.float32 else (None, w)
     rc = _l.lib().aeris_modnorm_fwd(_l.ptr(x), _l.ptr(gather_idx), peers, len(peer_ptrs) if peer_ptrs else 0,
                                     _l.ptr(x_out), _l.ptr(scale), _l.ptr(shift), _l.ptr(w), _l.ptr(out), rows, D,
-                                    mode, _l._c_float(eps), _l.stream_ptr())
+                                    mode, _l._c_float(eps), _l.ptr(w32), _l.ptr(out_lo), _l.stream_ptr())
     _l.check(rc, "aeris_modnorm_fwd")
     return out
 
@@ -36,9 +38,10 @@ def modnorm_bwd(x: torch.Tensor, dh: torch.Tensor, dres: torch.Tensor | None, sc
                 shift: torch.Tensor | None, w: torch.Tensor, *, mode: int, eps: float, dx: torch.Tensor,
                 dscale: torch.Tensor | None, dshift: torch.Tensor | None, dw: torch.Tensor | None) -> torch.Tensor:
     rows, D = x.shape
+    w32, w = (w, None) if w.dtype == torch.float32 else (None, w)
     rc = _l.lib().aeris_modnorm_bwd(_l.ptr(x), _l.ptr(dh), _l.ptr(dres), _l.ptr(scale), _l.ptr(shift), _l.ptr(w),
                                     _l.ptr(dx), _l.ptr(dscale), _l.ptr(dshift), _l.ptr(dw), rows, D, mode,
-                                    _l._c_float(eps), _l.stream_ptr())
+                                    _l._c_float(eps), _l.ptr(w32), _l.stream_ptr())
     _l.check(rc, "aeris_modnorm_bwd")
     return dx
 
