@@ -21,7 +21,7 @@ import torch
 import torch.distributed as dist
 
 from ..data.sharding import gather_blocks, shard_block
-from ..diffusion.rollout import Forecaster, SamplerConfig
+from ..diffusion.rollout import DeviceForecaster, Forecaster, SamplerConfig
 from ..diffusion import trigflow as TF
 from ..engine.checkpoint import convert_inference_checkpoint
 from ..eval.metrics import EnsembleMetrics
@@ -109,7 +109,11 @@ def main(argv=None):
     stats = {k: torch.zeros(C_out, device=device) if "mean" in k else torch.ones(C_out, device=device)
              for k in ("x_mean", "x_std", "t_mean", "t_std")}
     gen = torch.Generator(device=device).manual_seed(a.seed * 1000 + rank)
-    fc = Forecaster(denoise, stats, sampler, C_out)
+    if device.type == "cuda":     # sampler, (un)standardisation, embedding and head on the CUDA kernels
+        fc = DeviceForecaster(model, ctx, stats, sampler, C_out, seed=a.seed,
+                              member0=(dp_rank * ((a.members + dp - 1) // dp) if a.member_parallel else 0))
+    else:
+        fc = Forecaster(denoise, stats, sampler, C_out)
     w_lat = TF.latitude_weights(H, float(cfg.model.get("w_lat_add", 0.0))).to(device)
     w_lat_blk = w_lat.view(wp[0], hb)[wp_rank // wp[1]]
     metrics = EnsembleMetrics(steps, C_out, H * W, device, group=wp_group)

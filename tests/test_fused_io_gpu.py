@@ -182,3 +182,37 @@ def test_sampler_affine_gemv():
     assert rel_err(y, ref) < 1e-4
     y32 = DF.gemv_bias_act(W.float(), None, v)
     assert rel_err(y32, v @ W.float().t()) < 1e-5
+
+
+@pytest.mark.parametrize("heun,churn", [(True, 0.0), (False, 0.0), (True, 1.0)])
+def test_device_forecaster_matches_pytorch_sampler(heun, churn):
+    from aeris_gb_b200.diffusion.rollout import DeviceForecaster, Forecaster, SamplerConfig
+    from aeris_gb_b200.models.aeris import AerisModel, StreamContext
+    torch.manual_seed(3)
+    cfg = _cfg()
+    grid = cfg.grid()
+    model = AerisModel(cfg).cuda().eval()
+    torch.nn.init.normal_(model.output_stage.head.weight, std=0.05)
+    M, C = 2, cfg.out_channels
+    C_f = cfg.in_channels - 2 * C
+    ctx = StreamContext(cfg, M)
+    stats = {"x_mean": torch.randn(C, device="cuda"), "x_std": torch.rand(C, device="cuda") + 0.5,
+             "t_mean": torch.randn(C, device="cuda") * 0.1, "t_std": torch.rand(C, device="cuda") + 0.5}
+    sampler = SamplerConfig(n_steps=3, sigma_min=0.2, sigma_max=80.0, sigma_data=1.0, heun=heun, s_churn=churn)
+    state = torch.randn(M, 32, 64, C, device="cuda")
+    forcing = torch.randn(M, 32, 64, C_f, device="cuda")
+    dev_fc = DeviceForecaster(model, ctx, stats, sampler, C, seed=4)
+    out = dev_fc.step(state, forcing)
+    assert out.shape == state.shape and torch.isfinite(out).all()
+    if churn > 0:
+        # fresh noise at every churned step: a second call differs, and differs from a churn-free run
+        assert not torch.allclose(out, DeviceForecaster(model, ctx, stats, sampler, C, seed=5).step(state, forcing))
+        return
+
+    def denoise(model_in, t):
+        with torch.no_grad():
+            return model(model_in, t)
+
+    z = _noise_image(grid, M, (4 << 32) + 1, C) * sampler.sigma_data
+    ref = Forecaster(denoise, stats, sampler, C).step(state, forcing, x_init=z)
+    assert rel_err(out - state, ref - state) < 3e-2
