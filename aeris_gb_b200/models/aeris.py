@@ -272,10 +272,10 @@ class SwinLayer(nn.Module):
         if regroup is not None and regroup[0] == regroup[1]:
             regroup = None
         for j, (n1, attn, n2, ff, mod) in enumerate(self.modulelist):
-            m = mod(dt.to(mod.modulation[-1].weight.dtype))
             if use_fused(x):
                 from . import fused
                 from ..ops import elementwise as E
+                m = fused.modulation(mod.modulation, dt)
                 meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.n_local, cfg.heads, cfg.head_dim,
                                        E.MODE_MOD_THEN_NORM if cfg.after_mod_norm else E.MODE_NORM_THEN_MOD,
                                        eps, cfg.chunk_windows, sp=ctx.sp_exchange if ctx.grid.sp > 1 else None)
@@ -286,6 +286,7 @@ class SwinLayer(nn.Module):
                 x = fused.FusedBlock.apply(x, m, meta, n1.weight, attn.to_qkv.weight, attn.wo.weight, n2.weight,
                                            ff.w1.weight, ff.w2.weight, rg)
             else:
+                m = mod(dt.to(mod.modulation[-1].weight.dtype))
                 if j == 0 and regroup is not None:
                     x = ctx.regroup_unfused(x, regroup[0], regroup[1])
                 p = {"n1": n1.weight, "to_qkv": attn.to_qkv.weight, "wo": attn.wo.weight, "n2": n2.weight,
@@ -331,16 +332,16 @@ class OutputStage(nn.Module):
 
 def _out_loss_images(self, x, dt, x_img, cs, plan):
     """TrigFlow loss of the output stage straight from the stream (CUDA path; see :mod:`.fused_io`)."""
-    from . import fused_io
-    shift, scale = self.modulation(dt.to(self.cfg.data_dtype)).chunk(2, dim=1)
+    from . import fused, fused_io
+    shift, scale = fused.modulation(self.modulation, dt).chunk(2, dim=1)
     return fused_io.HeadLossFn.apply(x, shift, scale, self.norm.weight, self.head.weight, x_img, cs, plan)
 
 
 def _out_predict_tokens(self, x, dt):
     """Network output in token order, fp32 ``[T, 128]`` (channels past ``out_channels`` are zero); no autograd."""
-    from . import fused_io
+    from . import fused, fused_io
     with torch.no_grad():
-        shift, scale = self.modulation(dt.to(self.cfg.data_dtype)).chunk(2, dim=1)
+        shift, scale = fused.modulation(self.modulation, dt).chunk(2, dim=1)
         return fused_io.head_forward(x, shift, scale, self.norm.weight, self.head.weight,
                                      self.cfg.eps(self.cfg.data_dtype))
 

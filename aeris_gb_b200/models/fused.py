@@ -342,6 +342,50 @@ class FusedBlock(torch.autograd.Function):
         return (dx, dmod.to(mod.dtype), None, *out, None)
 
 
+class GemvLinearFn(torch.autograd.Function):
+    """``silu?(x) @ W^T + b`` for the handful of rows of a modulation MLP (one row per sample): the forward streams the
+    weight once through the GEMV kernel; weight gradients are rank-B updates added to the fp32 gradient buffers."""
+
+    @staticmethod
+    def forward(ctx, x, W, b, silu_in: bool):
+        from ..ops import diffusion as DF
+        x32 = x.float().contiguous()
+        y = DF.gemv_bias_act(W.detach(), b.detach().float() if b is not None else None, x32, act=0, silu_in=silu_in)
+        ctx.silu_in, ctx.x_dtype = silu_in, x.dtype
+        ctx.save_for_backward(x32, W, b)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .fused_io import _grad_slot
+        x32, W, b = ctx.saved_tensors
+        dy = dy.float()
+        sig = torch.sigmoid(x32) if ctx.silu_in else None
+        h = x32 * sig if ctx.silu_in else x32
+        sW, rW = _grad_slot(W)
+        sW.addmm_(dy.t(), h)
+        rb = None
+        if b is not None:
+            sb, rb = _grad_slot(b)
+            sb += dy.sum(0)
+        dx = (dy.to(W.dtype) @ W).float()
+        if ctx.silu_in:
+            dx = dx * (sig * (1 + x32 * (1 - sig)))
+        return (dx.to(ctx.x_dtype), rW.to(W.dtype) if rW is not None else None,
+                rb.to(b.dtype) if rb is not None else None, None)
+
+
+def modulation(seq: torch.nn.Sequential, emb: torch.Tensor) -> torch.Tensor:
+    """The AdaLN modulation MLP ``[Linear,] SiLU, Linear`` (src/aeris/models/parallel_swin.py:321-325) of at most 8
+    samples on the GEMV kernel; fp32 result ``[B, out]``."""
+    if emb.shape[0] > 8:
+        return seq(emb.to(seq[-1].weight.dtype)).float()
+    x = emb
+    if len(seq) == 3:
+        x = GemvLinearFn.apply(x, seq[0].weight, seq[0].bias, False)
+    return GemvLinearFn.apply(x, seq[-1].weight, seq[-1].bias, True)
+
+
 class Regroup(torch.autograd.Function):
     """Row gather between two window layouts through a table; the backward pass is the gather with the inverse
     table. ``peers`` lists the base addresses of every WP rank's source buffer (just the local one without WP)."""
