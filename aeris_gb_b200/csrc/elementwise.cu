@@ -393,6 +393,40 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ gra
   }
 }
 
+// Owner side of the row reduce-scatter: out = resid + gate[col] * sum_s slots[s * rows + r] (bf16 slots, fp32 sum).
+__global__ void rs_finalize_kernel(const __nv_bfloat16* __restrict__ slots, int world, long long rows, int D,
+                                   const __nv_bfloat16* __restrict__ resid, const float* __restrict__ gate,
+                                   __nv_bfloat16* __restrict__ out) {
+  const int vec = D / 8;
+  const long long total = rows * vec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec;
+    const int c = static_cast<int>(i - r * vec) * 8;
+    float acc[8];
+    load8(slots + r * D + c, acc);
+    for (int s = 1; s < world; ++s) {
+      float t[8];
+      load8(slots + (static_cast<long long>(s) * rows + r) * D + c, t);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += t[k];
+    }
+    if (gate) {
+      float g[8];
+      loadf8(gate + c, g);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] *= g[k];
+    }
+    if (resid) {
+      float t[8];
+      load8(resid + r * D + c, t);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += t[k];
+    }
+    store8(out + r * D + c, acc);
+  }
+}
+
 static inline int grid_for(long long work, int threads, int max_blocks) {
   long long b = (work + threads - 1) / threads;
   if (b > max_blocks) b = max_blocks;
@@ -511,5 +545,15 @@ extern "C" int aeris_adamw(float* master, float* grad, float* m, float* v, void*
   const int grid = grid_for(n, 256, aeris_num_sms() * 16);
   adamw_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       master, grad, m, v, reinterpret_cast<__nv_bfloat16*>(wbf16), ema, norm_sq, n, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_rs_finalize(const void* slots, int world, long long rows, int D, const void* resid,
+                                 const float* gate, void* out, void* stream) {
+  if (D % 8 || rows <= 0 || world < 1) return -1;
+  const int grid = grid_for(rows * (D / 8), 256, aeris_num_sms() * 16);
+  rs_finalize_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(slots), world, rows, D, reinterpret_cast<const __nv_bfloat16*>(resid), gate,
+      reinterpret_cast<__nv_bfloat16*>(out));
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

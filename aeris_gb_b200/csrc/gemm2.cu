@@ -343,3 +343,27 @@ extern "C" int aeris_gemm_scatter_heads(const void* A, const void* B, int M, int
   if (r) return r - 100;
   return b_mn ? launch_gemm2<0, 1>(ta, tb, p, stream) : launch_gemm2<0, 0>(ta, tb, p, stream);
 }
+
+// GEMM -> reduce-scatter by rows in one kernel: rank `rank` computes its partial product for all `world *
+// rows_per_rank` rows (A: [M, K] with K this rank's slice of the reduction dimension) and the epilogue stores each bf16
+// tile into slot `rank` of the owner's [world * rows_per_rank, N] buffer `peers[owner]` (peer memory), so the
+// transfer rides along tile by tile. The owner sums its `world` slots afterwards (aeris_rs_finalize).
+extern "C" int aeris_gemm_rs_push(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int b_mn,
+                                  const void* const* peers, int world, int rank, int rows_per_rank, int ld_dst,
+                                  int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N % G2_BN != 0 || K <= 0 || world < 1 || world > 8 || rank < 0 || rank >= world) return -1;
+  if (M != world * rows_per_rank || ld_dst % 8 != 0 || ld_dst < N) return -2;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.epi = EPI_RS_PUSH; p.C = nullptr; p.ldc = 0;
+  p.rows_per_gate = M; p.k_splits = 1; p.status = status;
+  p.b_tile_stride = G2_BN; p.b_half_off = G2_BN / 2;
+  for (int i = 0; i < world; ++i) p.scat_peers[i] = const_cast<void*>(peers[i]);
+  p.scat_rank = rank; p.scat_n_local = rows_per_rank; p.scat_ld = ld_dst;
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d_bf16(&ta, A, K, M, lda, G2_BK, G2_BM);
+  if (r) return r;
+  r = b_mn ? make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, G2_BK) : make_tmap_2d_bf16(&tb, B, K, N, ldb, G2_BK, G2_BN / 2);
+  if (r) return r - 100;
+  return b_mn ? launch_gemm2<0, 1>(ta, tb, p, stream) : launch_gemm2<0, 0>(ta, tb, p, stream);
+}

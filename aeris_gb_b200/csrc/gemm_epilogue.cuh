@@ -7,8 +7,10 @@ namespace aeris {
 enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GATE_RESID = 2, EPI_ACC_F32 = 3, EPI_STORE_F32 = 4,
               EPI_SWIGLU_BOTH = 5,   // EPI_SWIGLU that also stores the raw [gate | up] product to aux [M, 2F]
               EPI_SWIGLU_BWD = 6,    // acc = d(act); reads u = [gate | up] from resid [M, 2F], writes d(u) to C [M, 2F]
-              EPI_SCATTER_HEADS = 7 };  // Ulysses: every head's columns are stored into the buffer of the rank that
+              EPI_SCATTER_HEADS = 7,    // Ulysses: every head's columns are stored into the buffer of the rank that
                                         // owns the head (peer memory), rows re-indexed to whole-window order
+              EPI_RS_PUSH = 8 };        // reduce-scatter by rows: the bf16 partial tile of row block `o` is stored into
+                                        // slot `rank` of owner o's [world * rows_per_rank, N] buffer (peer memory)
 
 struct GemmParams {
   int M, N, K;
@@ -28,8 +30,16 @@ struct GemmParams {
   // EPI_SCATTER_HEADS: source columns are `n_sec` sections of width sec_w (q | k | v, or one section); inside a section
   // the columns of rank r's heads are [r * own_w, (r + 1) * own_w). Source row (window w, local token i) goes to row
   // w * L + rank * n_local + i of the owner's [*, n_sec * own_w] buffer.
+  // EPI_RS_PUSH reuses scat_peers / scat_rank / scat_ld with scat_n_local = rows owned by one rank.
   void* scat_peers[8];
   int scat_rank, scat_n_local, scat_L, scat_sec_w, scat_own_w, scat_ld;
+  // All-gather fused into the A operand (one-CTA kernel only): A's rows are `ag_world` chunks of `ag_rows` rows; chunk
+  // ag_rank is already in place, copier warps pull the others from `ag_peers[c]` (same layout on every rank) into
+  // the local buffer `ag_local` and bump `ag_count[c]` once per CTA; tiles of a chunk wait for gridDim.x bumps.
+  const void* ag_peers[8];
+  void* ag_local;
+  unsigned* ag_count;
+  int ag_world, ag_rank, ag_rows;
   int* status;
 };
 
@@ -55,6 +65,25 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
         const int owner = hc / p.scat_own_w;
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld +
                              sec * p.scat_own_w + (hc - owner * p.scat_own_w);
+        uint32_t o[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+      }
+    }
+  } else if (p.epi == EPI_RS_PUSH) {
+    const int owner = row / p.scat_n_local;
+    const size_t drow = static_cast<size_t>(p.scat_rank) * p.scat_n_local + (row - owner * p.scat_n_local);
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c, v);
+      tmem_wait_ld();
+      if (row_ok) {
+        __nv_bfloat16* dst =
+            reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld + tn * BN + c;
         uint32_t o[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));

@@ -33,3 +33,16 @@ def test_fused_gradient_reduce_adamw_allgather(multicast):
                         "--master-addr", "127.0.0.1", "--master-port", str(29520 + multicast), worker, str(multicast)],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_tensor_parallel_mlp(n):
+    """All-gather -> GEMM (copier warps + arrival counters) and GEMM -> reduce-scatter (epilogue pushes) against the
+    unsharded MLP, forward and backward."""
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    worker = os.path.join(os.path.dirname(__file__), "tp_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29540 + n), worker],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
