@@ -35,7 +35,8 @@ struct GemmSmem {
   static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
 
-constexpr int AG_COPY_THREADS = 64;   // two copier warps (6, 7) in the all-gather variant
+constexpr int AG_COPY_THREADS = 128;  // four copier warps (6..9) in the all-gather variant
+constexpr int AG_UNROLL = 16;         // 16-byte loads in flight per copier thread (32 KB per SM)
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned* p) {
   uint32_t v;
@@ -63,7 +64,7 @@ __device__ __forceinline__ bool ag_wait_chunk(const GemmParams& p, int c) {
 }
 
 // AG = true: the A operand is all-gathered over peer memory inside the kernel (see GemmParams::ag_*): tiles are
-// visited starting with this rank's own row chunk, while two extra warps stream the other chunks over NVLink into
+// visited starting with this rank's own row chunk, while four extra warps stream the other chunks over NVLink into
 // local memory, so each remote row crosses the link once and the copy hides behind the first chunk's math.
 template <int BN, int A_MN, int B_MN, bool AG = false>
 __global__ void __launch_bounds__(AG ? GEMM_THREADS + AG_COPY_THREADS : GEMM_THREADS, 1)
@@ -212,7 +213,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
     }
   } else if (AG && warp >= 6) {
-    // ------------------------------------------------------------ all-gather copiers (warps 6, 7)
+    // ------------------------------------------------------------ all-gather copiers (warps 6..9)
     if constexpr (AG) {
       const int cid = threadIdx.x - GEMM_THREADS;
       const long long vecs = static_cast<long long>(p.ag_rows) * p.K / 8;   // 16-byte vectors per chunk
@@ -224,15 +225,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.ag_peers[c]) + off);
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.ag_local) + off);
         long long i = v0 + cid;
-        for (; i + 7 * AG_COPY_THREADS < v1; i += 8 * AG_COPY_THREADS) {
-          uint4 t[8];
+        for (; i + (AG_UNROLL - 1) * AG_COPY_THREADS < v1; i += AG_UNROLL * AG_COPY_THREADS) {
+          uint4 t[AG_UNROLL];
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
+          for (int u = 0; u < AG_UNROLL; ++u)
             asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(t[u].x), "=r"(t[u].y), "=r"(t[u].z), "=r"(t[u].w)
                          : "l"(src + i + u * AG_COPY_THREADS));
 #pragma unroll
-          for (int u = 0; u < 8; ++u) dst[i + u * AG_COPY_THREADS] = t[u];
+          for (int u = 0; u < AG_UNROLL; ++u) dst[i + u * AG_COPY_THREADS] = t[u];
         }
         for (; i < v1; i += AG_COPY_THREADS) {
           uint4 t;

@@ -28,7 +28,8 @@ constexpr int G2_STAGES = 6;
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;         // 16 KB
 constexpr int G2_B_BYTES = (G2_BN / 2) * G2_BK * 2;   // 16 KB: this CTA's half of B
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
-constexpr int G2_SMEM = G2_STAGES * G2_STAGE_BYTES + 512 + 1024;
+constexpr int G2_PUSH_OFF = G2_STAGES * G2_STAGE_BYTES + 512;     // staging of the peer-push epilogues, 8 KB per warp
+constexpr int G2_SMEM = G2_PUSH_OFF + 4 * PUSH_STAGE_BYTES + 1024;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -231,7 +232,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       const int row = tm * 2 * G2_BM + crank * G2_BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * G2_BN + (static_cast<uint32_t>(q * 32) << 16);
       const bool kempty = (split * kb_per_split) >= kb_total;
-      gemm_epilogue_row<G2_BN>(p, taddr, row, row < p.M, tn, kempty);
+      gemm_epilogue_row<G2_BN>(p, taddr, row, row < p.M, tn, kempty, smem + G2_PUSH_OFF + q * PUSH_STAGE_BYTES);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(leader_tempty0 + acc * 8);

@@ -44,52 +44,86 @@ struct GemmParams {
 };
 
 
+// Peer-memory pushes: a thread that owns one accumulator row would write 16-byte pieces of 32 different rows per store
+// instruction, which crosses NVLink as 32 small packets. The push epilogues therefore stage 32 rows x 128 bf16 columns
+// per warp in shared memory (`stage`, 8 KB, 16-byte chunks XOR-swizzled by row) and write them out as 256-byte row
+// segments, two rows per store instruction.
+constexpr int PUSH_STAGE_BYTES = 8192;
+__device__ __forceinline__ void push_stage_put(uint8_t* stage, int lane, int col, const uint32_t (&o)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(stage + lane * 256 + (((col / 8 + i) ^ (lane & 15)) << 4)) =
+        make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+}
+// `dst_row`: where this lane's row stores its 128 staged columns (null: row not written).
+__device__ __forceinline__ void push_stage_flush(uint8_t* stage, int lane, __nv_bfloat16* dst_row) {
+  __syncwarp();
+  const unsigned long long mine = reinterpret_cast<unsigned long long>(dst_row);
+  const int ch = lane & 15;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int r = 2 * i + (lane >> 4);
+    const unsigned long long d = __shfl_sync(0xffffffffu, mine, r);
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4));
+    if (d) *reinterpret_cast<uint4*>(d + ch * 16) = v;
+  }
+  __syncwarp();
+}
+
 // One thread = one accumulator row (TMEM lane) of a BN-column tile whose first accumulator column is `taddr`.
 // `row` is the global output row, `tn` the tile's index along N, `kempty` marks a split-K slice without work.
+// `stage`: this warp's PUSH_STAGE_BYTES of shared memory for the push epilogues, or null (direct stores).
 template <int BN>
 __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t taddr, int row, bool row_ok, int tn,
-                                                  bool kempty) {
+                                                  bool kempty, uint8_t* stage = nullptr) {
+  const int lane = threadIdx.x & 31;
 
   if (p.epi == EPI_SCATTER_HEADS) {
     const int w = row / p.scat_n_local;
     const size_t drow = static_cast<size_t>(w) * p.scat_L + p.scat_rank * p.scat_n_local + (row - w * p.scat_n_local);
+    const bool staged = stage != nullptr && (p.scat_own_w % 128) == 0;   // a 128-column group has one owner
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {
       uint32_t v[32];
       tmem_ld32(taddr + c, v);
       tmem_wait_ld();
-      if (row_ok) {
-        const int c0 = tn * BN + c;
-        const int sec = c0 / p.scat_sec_w;
-        const int hc = c0 - sec * p.scat_sec_w;
-        const int owner = hc / p.scat_own_w;
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld +
-                             sec * p.scat_own_w + (hc - owner * p.scat_own_w);
-        uint32_t o[16];
+      const int c0 = tn * BN + (staged ? (c & ~127) : c);
+      const int sec = c0 / p.scat_sec_w;
+      const int hc = c0 - sec * p.scat_sec_w;
+      const int owner = hc / p.scat_own_w;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld +
+                           sec * p.scat_own_w + (hc - owner * p.scat_own_w);
+      uint32_t o[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+      for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+      if (staged) {
+        push_stage_put(stage, lane, c & 127, o);
+        if ((c & 127) == 96) push_stage_flush(stage, lane, row_ok ? dst : nullptr);
+      } else if (row_ok) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
       }
     }
   } else if (p.epi == EPI_RS_PUSH) {
-    const int owner = row / p.scat_n_local;
+    const int owner = row_ok ? row / p.scat_n_local : 0;
     const size_t drow = static_cast<size_t>(p.scat_rank) * p.scat_n_local + (row - owner * p.scat_n_local);
+    __nv_bfloat16* rowdst = reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld + tn * BN;
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {
       uint32_t v[32];
       tmem_ld32(taddr + c, v);
       tmem_wait_ld();
-      if (row_ok) {
-        __nv_bfloat16* dst =
-            reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld + tn * BN + c;
-        uint32_t o[16];
+      uint32_t o[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+      for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+      if (stage) {
+        push_stage_put(stage, lane, c & 127, o);
+        if ((c & 127) == 96) push_stage_flush(stage, lane, row_ok ? rowdst + (c - 96) : nullptr);
+      } else if (row_ok) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          *reinterpret_cast<uint4*>(rowdst + c + 8 * i) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
       }
     }
   } else if (p.epi == EPI_SWIGLU_BWD) {

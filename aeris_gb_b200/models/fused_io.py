@@ -209,7 +209,7 @@ class HeadLossFn(torch.autograd.Function):
             E.modnorm_fwd(x[r0:r0 + n], scale32[b], shift32[b], norm_w, mode=E.MODE_NORM_THEN_MOD, eps=plan.eps,
                           out=y_hi[:n])
             dp = dpred[r0:r0 + n]
-            G.gemm(dp, y_hi[:n], a_t=True, b_t=True, out=Gh, epi=G.EPI_ACC_F32, k_splits=16, bn=256)
+            G.gemm(dp, y_hi[:n], a_t=True, b_t=True, out=Gh, epi=G.EPI_ACC_F32, k_splits=16, two_cta=False)
             G.gemm(dp, w_hi, b_t=True, out=dy[:n])
             E.modnorm_bwd(x[r0:r0 + n], dy[:n], None, scale32[b], shift32[b], norm_w, mode=E.MODE_NORM_THEN_MOD,
                           eps=plan.eps, dx=dx[r0:r0 + n], dscale=dscale[b], dshift=dshift[b], dw=dnw)
