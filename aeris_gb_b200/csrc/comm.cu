@@ -133,26 +133,50 @@ __global__ void shard_adamw_allgather_kernel(float* __restrict__ master, const f
     if (c < 1.f) clip = c;
   }
   const long long n8 = n / 8;
+  const bool do_ema = ema && a.ema_beta >= 0.f;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    // 16-byte vector loads: two per array and thread, all issued before the first use
+    float4 g4[2], p4[2], m4[2], v4[2], e4[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long j = 2 * i + h;
+      g4[h] = reinterpret_cast<const float4*>(grad)[j];
+      p4[h] = reinterpret_cast<const float4*>(master)[j];
+      m4[h] = reinterpret_cast<const float4*>(m)[j];
+      v4[h] = reinterpret_cast<const float4*>(v)[j];
+      if (do_ema) e4[h] = reinterpret_cast<const float4*>(ema)[j];
+    }
     float pw[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const long long j = 8 * i + k;
-      float g = grad[j] * clip;
-      if (g != g) g = 0.f;
-      else if (g > 3.0e38f) g = a.nan_clamp;
-      else if (g < -3.0e38f) g = -a.nan_clamp;
-      float p = master[j];
-      const float mi = a.beta1 * m[j] + (1.f - a.beta1) * g;
-      const float vi = a.beta2 * v[j] + (1.f - a.beta2) * g * g;
-      m[j] = mi;
-      v[j] = vi;
-      p *= (1.f - a.lr * a.weight_decay);
-      p -= a.lr * (mi / a.bias1) / (sqrtf(vi / a.bias2) + a.eps);
-      master[j] = p;
-      if (ema && a.ema_beta >= 0.f) ema[j] = p + a.ema_beta * (ema[j] - p);
-      pw[k] = p;
+    for (int h = 0; h < 2; ++h) {
+      float* gg = reinterpret_cast<float*>(&g4[h]);
+      float* pp = reinterpret_cast<float*>(&p4[h]);
+      float* mm = reinterpret_cast<float*>(&m4[h]);
+      float* vv = reinterpret_cast<float*>(&v4[h]);
+      float* ee = reinterpret_cast<float*>(&e4[h]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float g = gg[k] * clip;
+        if (g != g) g = 0.f;
+        else if (g > 3.0e38f) g = a.nan_clamp;
+        else if (g < -3.0e38f) g = -a.nan_clamp;
+        float p = pp[k];
+        const float mi = a.beta1 * mm[k] + (1.f - a.beta1) * g;
+        const float vi = a.beta2 * vv[k] + (1.f - a.beta2) * g * g;
+        mm[k] = mi;
+        vv[k] = vi;
+        p *= (1.f - a.lr * a.weight_decay);
+        p -= a.lr * (mi / a.bias1) / (sqrtf(vi / a.bias2) + a.eps);
+        pp[k] = p;
+        if (do_ema) ee[k] = p + a.ema_beta * (ee[k] - p);
+        pw[4 * h + k] = p;
+      }
+      const long long j = 2 * i + h;
+      reinterpret_cast<float4*>(master)[j] = p4[h];
+      reinterpret_cast<float4*>(m)[j] = m4[h];
+      reinterpret_cast<float4*>(v)[j] = v4[h];
+      if (do_ema) reinterpret_cast<float4*>(ema)[j] = e4[h];
     }
     uint4 u;
     u.x = pack_bf16x2(pw[0], pw[1]);

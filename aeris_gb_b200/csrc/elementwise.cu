@@ -87,18 +87,18 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
     if (shift) loadf8(shift + c0, sh);
     if (wf) loadf8(wf + c0, wv); else load8(w + c0, wv);
   }
-  const int r0 = blockIdx.x * rows_per_cta;
-  const int r1 = min(rows, r0 + rows_per_cta);
-  int parity = 0;
-  for (int r = r0; r < r1; r += FWD_RPI, parity ^= 1) {
-    float y[FWD_RPI][8];
-    float ss[FWD_RPI];
+  // CTAs sweep the rows together (CTA b takes row groups b, b + grid, ...). The rows of the next group are requested
+  // before the current group is reduced, so every thread keeps up to eight 16-byte loads in flight across the
+  // block-wide reduction.
+  (void)rows_per_cta;
+  const int r1 = rows;
+  const int stride = gridDim.x * FWD_RPI;
+  uint4 nxt[FWD_RPI];
+  auto fetch = [&](int r) {
 #pragma unroll
     for (int k = 0; k < FWD_RPI; ++k) {
-      float v[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0.f;
       const int rr = r + k;
+      nxt[k] = make_uint4(0u, 0u, 0u, 0u);
       if (active && rr < r1) {
         const __nv_bfloat16* src;
         if (gidx) {
@@ -107,9 +107,34 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
         } else {
           src = x + static_cast<size_t>(rr) * D + c0;
         }
-        load8(src, v);
-        if (x_out) store8(x_out + static_cast<size_t>(rr) * D + c0, v);
+        nxt[k] = *reinterpret_cast<const uint4*>(src);
       }
+    }
+  };
+  int parity = 0;
+  int r = blockIdx.x * FWD_RPI;
+  if (r < r1) fetch(r);
+  for (; r < r1; r += stride, parity ^= 1) {
+    float y[FWD_RPI][8];
+    float ss[FWD_RPI];
+    uint4 cur[FWD_RPI];
+#pragma unroll
+    for (int k = 0; k < FWD_RPI; ++k) cur[k] = nxt[k];
+    if (r + stride < r1) fetch(r + stride);
+#pragma unroll
+    for (int k = 0; k < FWD_RPI; ++k) {
+      float v[8];
+      {
+        const uint32_t w4[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t = unpack_bf16x2(w4[i]);
+          v[2 * i] = t.x;
+          v[2 * i + 1] = t.y;
+        }
+      }
+      const int rr = r + k;
+      if (active && rr < r1 && x_out) *reinterpret_cast<uint4*>(x_out + static_cast<size_t>(rr) * D + c0) = cur[k];
       ss[k] = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -160,19 +185,35 @@ __global__ void modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __
     if (shift) loadf8(shift + c0, sh);
     if (wf) loadf8(wf + c0, wv); else load8(w + c0, wv);
   }
-  const int r0 = blockIdx.x * rows_per_cta;
-  const int r1 = min(rows, r0 + rows_per_cta);
+  (void)rows_per_cta;
+  const int r1 = rows;
   int parity = 0;
-  for (int r = r0; r < r1; ++r, parity ^= 1) {
-    float v[8], g[8], dr[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { v[i] = 0.f; g[i] = 0.f; dr[i] = 0.f; }
+  // the next row's three vectors are requested before the current row is reduced
+  uint4 nx = make_uint4(0u, 0u, 0u, 0u), ng = nx, nr = nx;
+  auto fetch = [&](int r) {
     if (active) {
       const size_t off = static_cast<size_t>(r) * D + c0;
-      load8(x + off, v);
-      load8(dh + off, g);
-      if (dres) load8(dres + off, dr);
+      nx = *reinterpret_cast<const uint4*>(x + off);
+      ng = *reinterpret_cast<const uint4*>(dh + off);
+      if (dres) nr = *reinterpret_cast<const uint4*>(dres + off);
     }
+  };
+  auto unpack8 = [](const uint4& u, float (&f)[8]) {
+    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = unpack_bf16x2(w4[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  };
+  if (static_cast<int>(blockIdx.x) < r1) fetch(blockIdx.x);
+  for (int r = blockIdx.x; r < r1; r += gridDim.x, parity ^= 1) {
+    float v[8], g[8], dr[8];
+    unpack8(nx, v);
+    unpack8(ng, g);
+    unpack8(nr, dr);
+    if (r + static_cast<int>(gridDim.x) < r1) fetch(r + gridDim.x);
     float o[8];
     if (mode == 0) {
       // y = x(1+sc)+sh ; h = y * rinv * w
@@ -372,24 +413,53 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ gra
     if (c < 1.f) clip = c;
   }
   const float gs = a.grad_scale * clip;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float g = grad[i] * gs;
+  const bool do_ema = ema && a.ema_beta >= 0.f;
+  auto update = [&](float g, float& p, float& mi, float& vi, float& e) {
+    g *= gs;
     if (g != g) g = 0.f;
     else if (g > 3.0e38f) g = a.nan_clamp;
     else if (g < -3.0e38f) g = -a.nan_clamp;
-    float p = master[i];
-    const float mi = a.beta1 * m[i] + (1.f - a.beta1) * g;
-    const float vi = a.beta2 * v[i] + (1.f - a.beta2) * g * g;
-    m[i] = mi;
-    v[i] = vi;
+    mi = a.beta1 * mi + (1.f - a.beta1) * g;
+    vi = a.beta2 * vi + (1.f - a.beta2) * g * g;
     p *= (1.f - a.lr * a.weight_decay);
-    const float denom = sqrtf(vi / a.bias2) + a.eps;
-    p -= a.lr * (mi / a.bias1) / denom;
-    master[i] = p;
-    if (wbf16) wbf16[i] = __float2bfloat16_rn(p);
-    if (ema && a.ema_beta >= 0.f) ema[i] = p + a.ema_beta * (ema[i] - p);  // lerp(p, ema, beta)
-    grad[i] = 0.f;
+    p -= a.lr * (mi / a.bias1) / (sqrtf(vi / a.bias2) + a.eps);
+    if (do_ema) e = p + a.ema_beta * (e - p);  // lerp(p, ema, beta)
+  };
+  // main part: four elements per thread and iteration through 16-byte vectors (buffers are 16-byte aligned)
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 g4 = reinterpret_cast<const float4*>(grad)[i];
+    float4 p4 = reinterpret_cast<const float4*>(master)[i];
+    float4 m4 = reinterpret_cast<const float4*>(m)[i];
+    float4 v4 = reinterpret_cast<const float4*>(v)[i];
+    float4 e4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (do_ema) e4 = reinterpret_cast<const float4*>(ema)[i];
+    update(g4.x, p4.x, m4.x, v4.x, e4.x);
+    update(g4.y, p4.y, m4.y, v4.y, e4.y);
+    update(g4.z, p4.z, m4.z, v4.z, e4.z);
+    update(g4.w, p4.w, m4.w, v4.w, e4.w);
+    reinterpret_cast<float4*>(master)[i] = p4;
+    reinterpret_cast<float4*>(m)[i] = m4;
+    reinterpret_cast<float4*>(v)[i] = v4;
+    if (do_ema) reinterpret_cast<float4*>(ema)[i] = e4;
+    if (wbf16) {
+      uint2 u;
+      u.x = pack_bf16x2(p4.x, p4.y);
+      u.y = pack_bf16x2(p4.z, p4.w);
+      reinterpret_cast<uint2*>(wbf16)[i] = u;
+    }
+    reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (long long i = n4 * 4; i < n; ++i) {
+      float p = master[i], mi = m[i], vi = v[i], e = do_ema ? ema[i] : 0.f;
+      update(grad[i], p, mi, vi, e);
+      master[i] = p; m[i] = mi; v[i] = vi;
+      if (do_ema) ema[i] = e;
+      if (wbf16) wbf16[i] = __float2bfloat16_rn(p);
+      grad[i] = 0.f;
+    }
   }
 }
 
@@ -459,7 +529,8 @@ extern "C" int aeris_modnorm_fwd(const void* x, const void* gidx, const void* co
   for (int i = 0; i < n_peers && i < 16; ++i) pp.p[i] = reinterpret_cast<const __nv_bfloat16*>(peer_ptrs[i]);
   if (gidx && n_peers <= 0) return -2;
   const int rpc = pick_rows_per_cta(rows);
-  const int grid = (rows + rpc - 1) / rpc;
+  int grid = (rows + FWD_RPI - 1) / FWD_RPI;
+  if (grid > aeris_num_sms() * 8) grid = aeris_num_sms() * 8;
   modnorm_fwd_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const uint32_t*>(gidx), pp,
       reinterpret_cast<__nv_bfloat16*>(x_out), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
@@ -473,7 +544,7 @@ extern "C" int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres
   if (D % 8 || D > 8192 || rows <= 0 || (!w && !w_f32)) return -1;
   int rpc = pick_rows_per_cta(rows);
   if (rpc < 16) rpc = rows < 16 ? rows : 16;  // amortise the atomic flush of the column sums
-  const int grid = (rows + rpc - 1) / rpc;
+  const int grid = (rows + rpc - 1) / rpc;    // every CTA takes about rpc rows, interleaved with the others
   modnorm_bwd_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(dh),
       reinterpret_cast<const __nv_bfloat16*>(dres), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
@@ -537,12 +608,15 @@ extern "C" int aeris_adamw(float* master, float* grad, float* m, float* v, void*
                            float weight_decay, int step, float grad_scale, float max_norm, float ema_beta,
                            void* stream) {
   if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(m) |
+       reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(ema)) & 15) return -3;
+  if (reinterpret_cast<uintptr_t>(wbf16) & 7) return -3;
   AdamArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
   a.bias1 = 1.f - powf(beta1, static_cast<float>(step));
   a.bias2 = 1.f - powf(beta2, static_cast<float>(step));
   a.grad_scale = grad_scale; a.max_norm = max_norm; a.ema_beta = ema_beta; a.nan_clamp = 1.0e5f;
-  const int grid = grid_for(n, 256, aeris_num_sms() * 16);
+  const int grid = grid_for(n / 4 + 1, 256, aeris_num_sms() * 16);
   adamw_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       master, grad, m, v, reinterpret_cast<__nv_bfloat16*>(wbf16), ema, norm_sq, n, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

@@ -1,9 +1,14 @@
-"""Kernel micro-benchmarks: ``python -m aeris_gb_b200.ops.microbench <gemm|attn_fwd|attn_bwd|modnorm|swiglu|adamw> ...``
+"""Kernel micro-benchmarks: ``python -m aeris_gb_b200.ops.microbench <gemm|attn_fwd|attn_bwd|modnorm|modnorm_bwd|swiglu|adamw|embed|loss> ...``
 
 Times one kernel with CUDA events (3 warm-up launches, then ``--iters`` launches, inputs larger than L2) and prints
 one JSON line with achieved TFLOP/s or GB/s and, when ``MEASURED_PEAKS.json`` is present at the repository root, the
 fraction of the measured cuBLAS / copy peak. Also the small fixed workload that the committed ncu summaries were
 captured on.
+
+The ``fused_*`` kernels are the compute+collective kernels run on ONE GPU with the second rank's buffers placed in the
+same GPU's memory (``peers`` = two local buffers): the same code path, instruction mix and tile pipeline as in a
+multi-GPU run, minus the NVLink latency, which is what a single-process profiler capture can show. Their multi-GPU
+timings come from ``aeris_gb_b200.parallel.fused_bench``.
 """
 from __future__ import annotations
 
@@ -43,7 +48,9 @@ def _time(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "modnorm", "swiglu", "adamw"])
+    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "modnorm", "modnorm_bwd", "swiglu", "adamw",
+                                       "embed", "loss", "fused_ag_gemm", "fused_rs_gemm", "fused_scatter_heads",
+                                       "fused_grad_rs", "fused_shard_adamw", "fused_modnorm_gather"])
     ap.add_argument("--m", type=int, default=32768)
     ap.add_argument("--n", type=int, default=4608)
     ap.add_argument("--k", type=int, default=1536)
@@ -69,6 +76,8 @@ def main():
         kw = {}
         if a.epi == G.EPI_ACC_F32:
             kw["out"] = torch.zeros(a.m, a.n, device=dev)
+        if a.epi == G.EPI_SWIGLU_BOTH:
+            kw["aux"] = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
         if a.epi == G.EPI_GATE_RESID:
             kw["resid"] = torch.randn(a.m, a.n, device=dev).bfloat16()
             kw["gate"] = torch.randn(1, a.n, device=dev)
@@ -103,6 +112,121 @@ def main():
         by = 2.0 * x.numel() * 2
         out.update(shape=[a.rows, a.dim], ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / ms / 1e6 / bw_peak,
                    peak_source=src)
+    elif a.kernel == "modnorm_bwd":
+        x = torch.randn(a.rows, a.dim, device=dev).bfloat16()
+        dh, dres = torch.randn_like(x), torch.randn_like(x)
+        sc, sh = torch.randn(a.dim, device=dev), torch.randn(a.dim, device=dev)
+        w = torch.ones(a.dim, device=dev).bfloat16()
+        dx = torch.empty_like(x)
+        acc = [torch.zeros(a.dim, device=dev) for _ in range(3)]
+        ms = _time(lambda: E.modnorm_bwd(x, dh, dres, sc, sh, w, mode=0, eps=1e-3, dx=dx, dscale=acc[0],
+                                         dshift=acc[1], dw=acc[2]), a.iters)
+        by = 4.0 * x.numel() * 2
+        out.update(shape=[a.rows, a.dim], ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / ms / 1e6 / bw_peak,
+                   peak_source=src)
+    elif a.kernel in ("embed", "loss"):
+        from ..models import layout as LY
+        from . import diffusion as DF
+        grid = LY.Grid(720, 1440, 30, 30)
+        geom = DF.make_geom(grid, 1, 0)
+        x = torch.randn(1, 720, 1440, 70, device=dev)
+        cs = torch.tensor([[0.6, 0.8]], device=dev)
+        if a.kernel == "embed":
+            c = torch.randn(1, 720, 1440, 74, device=dev)
+            ay, ax = torch.randn(720, 72, device=dev), torch.randn(1440, 72, device=dev)
+            A_ = torch.empty(geom.rows, 512, device=dev, dtype=torch.bfloat16)
+            ms = _time(lambda: DF.embed_pack(x, c, cs, geom, ay, ax, 1, 1.0, True, A_), a.iters)
+            by = geom.rows * (144 * 4 + 512 * 2.0)
+        else:
+            pred = torch.randn(geom.rows, 128, device=dev)
+            dpred = torch.empty(geom.rows, 128, device=dev, dtype=torch.bfloat16)
+            loss = torch.zeros(1, device=dev, dtype=torch.float64)
+            wv, wl = torch.rand(70, device=dev), torch.rand(720, device=dev)
+            ms = _time(lambda: DF.trigflow_loss(pred, x, cs, geom, 1, 1.0, wv, wl, 1.0 / geom.rows, loss, dpred=dpred),
+                       a.iters)
+            by = geom.rows * (128 * 4 + 70 * 4 + 128 * 2.0)
+        out.update(rows=geom.rows, ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / ms / 1e6 / bw_peak, peak_source=src)
+    elif a.kernel.startswith("fused_"):
+        import ctypes
+        lib = L.lib()
+        arr = lambda ts: (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+        st, sp_ = L.ptr(L.status_word()), L.stream_ptr
+        if a.kernel == "fused_ag_gemm":
+            M, K, N = a.m // 2 * 2, a.k, a.n
+            bufs = [torch.randn(M, K, device=dev).bfloat16() for _ in range(2)]
+            w = torch.randn(N, K, device=dev).bfloat16()
+            c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            cnt = torch.zeros(8, device=dev, dtype=torch.int32)
+            full = torch.cat([bufs[0][:M // 2], bufs[1][M // 2:]])
+            run = lambda: L.check(lib.aeris_gemm_allgather_a(L.ptr(bufs[0]), arr(bufs), 2, 0, M // 2, L.ptr(w), L.ptr(c), N,
+                                                             K, K, N, 0, 0, None, 0, None, 0, 0, L.ptr(cnt), st, sp_()), "ag")
+            run()
+            ref = G.gemm(full, w)
+            out["max_abs_diff_vs_plain_gemm"] = (c.float() - ref.float()).abs().max().item()
+            ms = _time(run, a.iters)
+            out.update(shape=[M, N, K], ms=ms, tflops=2.0 * M * N * K / ms / 1e9,
+                       frac_of_peak=2.0 * M * N * K / ms / 1e9 / tf_peak, peak_source=src)
+        elif a.kernel == "fused_rs_gemm":
+            M, K, N = a.m // 2 * 2, a.k, a.n
+            x = torch.randn(M, K, device=dev).bfloat16()
+            w = torch.randn(N, K, device=dev).bfloat16()
+            slots = [torch.zeros(M, N, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+            run = lambda: L.check(lib.aeris_gemm_rs_push(L.ptr(x), L.ptr(w), M, N, K, K, K, 0, arr(slots), 2, 0, M // 2, N,
+                                                         st, sp_()), "rs")
+            run()
+            ref = G.gemm(x, w)
+            got = torch.cat([slots[0][:M // 2], slots[1][:M // 2]])
+            out["max_abs_diff_vs_plain_gemm"] = (got.float() - ref.float()).abs().max().item()
+            ms = _time(run, a.iters)
+            out.update(shape=[M, N, K], ms=ms, tflops=2.0 * M * N * K / ms / 1e9,
+                       frac_of_peak=2.0 * M * N * K / ms / 1e9 / tf_peak, peak_source=src)
+        elif a.kernel == "fused_scatter_heads":
+            nw, L_, n_loc, H, d, K = a.windows, a.tokens, a.tokens // 2, a.heads, a.head_dim, a.dim
+            HD = H * d
+            x = torch.randn(nw * n_loc, K, device=dev).bfloat16()
+            w = torch.randn(3 * HD, K, device=dev).bfloat16()
+            dst = [torch.zeros(nw * L_, 3 * HD // 2, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+            run = lambda: L.check(lib.aeris_gemm_scatter_heads(L.ptr(x), L.ptr(w), nw * n_loc, 3 * HD, K, K, K, 0, arr(dst),
+                                                               2, 0, n_loc, L_, HD, st, sp_()), "scatter")
+            ms = _time(run, a.iters)
+            fl = 2.0 * nw * n_loc * 3 * HD * K
+            out.update(shape=[nw * n_loc, 3 * HD, K], ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tf_peak,
+                       peak_source=src)
+        elif a.kernel in ("fused_grad_rs", "fused_shard_adamw"):
+            n = a.rows * a.dim // 16 * 16
+            per = n // 2
+            if a.kernel == "fused_grad_rs":
+                grads = [torch.randn(n, device=dev) for _ in range(2)]
+                o = torch.empty(per, device=dev)
+                ssq = torch.zeros(1, device=dev, dtype=torch.float64)
+                run = lambda: L.check(lib.aeris_grad_reduce_scatter(arr(grads), None, 2, L._c_ll(0), L._c_ll(per),
+                                                                    L._c_float(0.5), L.ptr(o), L.ptr(ssq), sp_()), "rs")
+                by = per * 4 * 3.0
+            else:
+                params = [torch.empty(n, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+                b5 = [torch.randn(per, device=dev) for _ in range(5)]
+                b5[3].abs_()
+                f = L._c_float
+                run = lambda: L.check(lib.aeris_shard_adamw_allgather(
+                    L.ptr(b5[0]), L.ptr(b5[1]), L.ptr(b5[2]), L.ptr(b5[3]), L.ptr(b5[4]), arr(params), None, 2,
+                    L._c_ll(0), L._c_ll(per), None, f(1e-4), f(0.9), f(0.99), f(1e-8), f(0.0), 3, f(0.0), f(0.999),
+                    sp_()), "adamw")
+                by = per * (5 * 4 + 4 * 4 + 2 * 2.0)
+            ms = _time(run, a.iters)
+            out.update(n=per, ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / ms / 1e6 / bw_peak, peak_source=src)
+        else:
+            from ..models import layout as LY
+            grid = LY.Grid(720, 1440, 30, 30, 1, 2)
+            rows, D = grid.tokens_per_rank, a.dim
+            table = LY.gather_table(grid, (0, 0), grid.half_shift(), 0).to(dev)
+            xs = [torch.randn(rows, D, device=dev).bfloat16() for _ in range(2)]
+            sc, sh = torch.randn(D, device=dev), torch.randn(D, device=dev)
+            w = torch.ones(D, device=dev).bfloat16()
+            h, xg = torch.empty_like(xs[0]), torch.empty_like(xs[0])
+            ms = _time(lambda: E.modnorm_fwd(None, sc, sh, w, mode=0, eps=1e-3, out=h, gather_idx=table,
+                                             peer_ptrs=[t.data_ptr() for t in xs], x_out=xg, rows=rows), a.iters)
+            by = rows * D * 2 * 3.0
+            out.update(shape=[rows, D], ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / ms / 1e6 / bw_peak, peak_source=src)
     elif a.kernel == "swiglu":
         u = torch.randn(a.rows, 2 * a.dim, device=dev).bfloat16()
         act = torch.empty(a.rows, a.dim, device=dev, dtype=torch.bfloat16)
