@@ -65,9 +65,10 @@ int aeris_shard_adamw_allgather(float* master, const float* grad, float* m, floa
                                 const double* norm_sq, float lr, float beta1, float beta2, float eps,
                                 float weight_decay, int step, float max_norm, float ema_beta, void* stream);
 
-int aeris_gemm_allgather_a(void* A, const void* const* peers, int world, int rank, int rows_per_rank, const void* B,
-                           void* C, int N, int K, int ldb, int ldc, int b_mn, int epi, const void* resid, int ldr,
-                           void* aux, int ld_aux, int swiglu_f, unsigned* counters, int* status, void* stream);
+int aeris_gemm_allgather_a(void* A, const void* const* peers, const void* const* counter_peers, int world, int rank,
+                           int rows_per_rank, unsigned call_index, const void* B, void* C, int N, int K, int ldb,
+                           int ldc, int b_mn, int epi, const void* resid, int ldr, void* aux, int ld_aux, int swiglu_f,
+                           int* status, void* stream);
 int aeris_gemm_rs_push(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int b_mn,
                        const void* const* peers, int world, int rank, int rows_per_rank, int ld_dst, int* status,
                        void* stream);

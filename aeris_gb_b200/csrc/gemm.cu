@@ -35,39 +35,8 @@ struct GemmSmem {
   static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
 
-constexpr int AG_COPY_THREADS = 128;  // four copier warps (6..9) in the all-gather variant
-constexpr int AG_UNROLL = 16;         // 16-byte loads in flight per copier thread (32 KB per SM)
-
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Waits (bounded) until every CTA has copied its slice of chunk `c`.
-__device__ __forceinline__ bool ag_wait_chunk(const GemmParams& p, int c) {
-  const unsigned want = gridDim.x;
-  if (ld_acquire_gpu(p.ag_count + c) >= want) return true;
-  const uint64_t t0 = globaltimer_ns();
-#pragma unroll 1
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      if (ld_acquire_gpu(p.ag_count + c) >= want) return true;
-      __nanosleep(64);
-    }
-    if (globaltimer_ns() - t0 > AERIS_WAIT_TIMEOUT_NS) {
-      if (p.status) atomicCAS(p.status, 0, ERR_TIMEOUT_SIGNAL);
-      return false;
-    }
-    if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return false;
-  }
-}
-
-// AG = true: the A operand is all-gathered over peer memory inside the kernel (see GemmParams::ag_*): tiles are
-// visited starting with this rank's own row chunk, while four extra warps stream the other chunks over NVLink into
-// local memory, so each remote row crosses the link once and the copy hides behind the first chunk's math.
-template <int BN, int A_MN, int B_MN, bool AG = false>
-__global__ void __launch_bounds__(AG ? GEMM_THREADS + AG_COPY_THREADS : GEMM_THREADS, 1)
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const GemmParams p) {
   using S = GemmSmem<BN>;
@@ -94,9 +63,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb_per_split = (kb_total + p.k_splits - 1) / p.k_splits;
   const int total_tiles = m_tiles * n_tiles * p.k_splits;
-  // all-gather variant: rotate the m-tile order so that the tiles of the local chunk come first
-  const int tm_rot = AG ? (p.ag_rank * p.ag_rows) / BM : 0;
-  auto phys_tm = [&](int tm) { return AG ? (tm + tm_rot) % m_tiles : tm; };
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_a);
@@ -126,23 +92,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      [[maybe_unused]] uint32_t ag_ready = 0;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int split = tile / (m_tiles * n_tiles);
         const int mn = tile - split * (m_tiles * n_tiles);
-        const int tm = phys_tm(mn / n_tiles), tn = mn - (mn / n_tiles) * n_tiles;
+        const int tm = mn / n_tiles, tn = mn - tm * n_tiles;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb_total, kb0 + kb_per_split);
-        if constexpr (AG) {
-          const int c_lo = (tm * BM) / p.ag_rows, c_hi = (min(p.M, tm * BM + BM) - 1) / p.ag_rows;
-          for (int c = c_lo; c <= c_hi && ok; ++c) {
-            if (c == p.ag_rank || (ag_ready >> c) & 1u) continue;
-            if (!ag_wait_chunk(p, c)) { ok = false; break; }
-            ag_ready |= 1u << c;
-            asm volatile("fence.proxy.async;" ::: "memory");   // copied rows were written through the generic proxy
-          }
-          if (!ok) break;
-        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
@@ -212,41 +167,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else if (AG && warp >= 6) {
-    // ------------------------------------------------------------ all-gather copiers (warps 6..9)
-    if constexpr (AG) {
-      const int cid = threadIdx.x - GEMM_THREADS;
-      const long long vecs = static_cast<long long>(p.ag_rows) * p.K / 8;   // 16-byte vectors per chunk
-      const long long per = (vecs + gridDim.x - 1) / gridDim.x;
-      const long long v0 = per * blockIdx.x, v1 = min(vecs, v0 + per);
-      for (int j = 1; j < p.ag_world; ++j) {
-        const int c = (p.ag_rank + j) % p.ag_world;
-        const size_t off = static_cast<size_t>(c) * p.ag_rows * p.K * 2;
-        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.ag_peers[c]) + off);
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.ag_local) + off);
-        long long i = v0 + cid;
-        for (; i + (AG_UNROLL - 1) * AG_COPY_THREADS < v1; i += AG_UNROLL * AG_COPY_THREADS) {
-          uint4 t[AG_UNROLL];
-#pragma unroll
-          for (int u = 0; u < AG_UNROLL; ++u)
-            asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(t[u].x), "=r"(t[u].y), "=r"(t[u].z), "=r"(t[u].w)
-                         : "l"(src + i + u * AG_COPY_THREADS));
-#pragma unroll
-          for (int u = 0; u < AG_UNROLL; ++u) dst[i + u * AG_COPY_THREADS] = t[u];
-        }
-        for (; i < v1; i += AG_COPY_THREADS) {
-          uint4 t;
-          asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w) : "l"(src + i));
-          dst[i] = t;
-        }
-        asm volatile("fence.proxy.async;" ::: "memory");
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(AG_COPY_THREADS) : "memory");
-        if (cid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_count + c) : "memory");
-      }
-    }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -256,7 +176,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int split = tile / (m_tiles * n_tiles);
       const int mn = tile - split * (m_tiles * n_tiles);
-      const int tm = phys_tm(mn / n_tiles), tn = mn - (mn / n_tiles) * n_tiles;
+      const int tm = mn / n_tiles, tn = mn - tm * n_tiles;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int row = tm * BM + q * 32 + lane;
@@ -335,11 +255,11 @@ int num_sms() {
   return g_num_sms;
 }
 
-template <int BN, int A_MN, int B_MN, bool AG = false>
+template <int BN, int A_MN, int B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
   using S = GemmSmem<BN>;
   static bool configured = false;
-  auto kern = gemm_kernel<BN, A_MN, B_MN, AG>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return -20;
@@ -348,7 +268,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   const int m_tiles = (p.M + BM - 1) / BM;
   const int tiles = m_tiles * (p.N / BN) * p.k_splits;
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  kern<<<grid, AG ? GEMM_THREADS + AG_COPY_THREADS : GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, p);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
@@ -405,42 +325,3 @@ extern "C" int aeris_gemm_bf16(const void* A, const void* B, void* C, int M, int
 #undef AERIS_DISPATCH
 }
 
-// All-gather -> GEMM in one kernel. `A` is this rank's [world * rows_per_rank, K] buffer (row pitch K) whose chunk
-// `rank` is filled; `peers[c]` is rank c's buffer of the same layout (peer memory). On return of the kernel the whole
-// gathered A is also resident in `A` (the weight-gradient product reuses it). `counters`: 8 zero-initialisable words
-// of device memory owned by the caller. The caller synchronises the ranks before (peers' chunks written) and after
-// (peers done reading) the call. Epilogues: EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_BOTH, EPI_SWIGLU_BWD.
-extern "C" int aeris_gemm_allgather_a(void* A, const void* const* peers, int world, int rank, int rows_per_rank,
-                                      const void* B, void* C, int N, int K, int ldb, int ldc, int b_mn, int epi,
-                                      const void* resid, int ldr, void* aux, int ld_aux, int swiglu_f,
-                                      unsigned* counters, int* status, void* stream_) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  const int bn = 256;
-  if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_per_rank <= 0 || N <= 0 || K <= 0) return -1;
-  if (N % bn != 0 || K % 8 != 0 || (static_cast<long long>(rows_per_rank) * K) % 8 != 0) return -2;
-  const bool swiglu_fwd = (epi == EPI_SWIGLU || epi == EPI_SWIGLU_BOTH);
-  if (swiglu_fwd && b_mn) return -3;
-  if (epi != EPI_STORE && !swiglu_fwd && epi != EPI_SWIGLU_BWD) return -4;
-  const int M = world * rows_per_rank;
-  GemmParams p{};
-  p.M = M; p.N = N; p.K = K; p.epi = epi; p.C = C; p.ldc = ldc;
-  p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.ldr = ldr;
-  p.rows_per_gate = M; p.aux = reinterpret_cast<__nv_bfloat16*>(aux); p.ld_aux = ld_aux;
-  p.k_splits = 1; p.status = status; p.swiglu_f = swiglu_f;
-  if (swiglu_fwd) { p.b_tile_stride = bn / 2; p.b_half_off = swiglu_f; }
-  else            { p.b_tile_stride = bn;     p.b_half_off = bn / 2; }
-  for (int i = 0; i < world; ++i) p.ag_peers[i] = peers[i];
-  p.ag_local = A; p.ag_count = counters; p.ag_world = world; p.ag_rank = rank; p.ag_rows = rows_per_rank;
-  if (cudaMemsetAsync(counters, 0, 8 * sizeof(unsigned), stream) != cudaSuccess) return -22;
-  CUtensorMap ta, tb;
-  int r = make_tmap_2d_bf16(&ta, A, K, M, K, BK, BM);
-  if (r) return r;
-  if (!b_mn) {
-    const uint64_t brows = swiglu_fwd ? static_cast<uint64_t>(2) * swiglu_f : static_cast<uint64_t>(N);
-    r = make_tmap_2d_bf16(&tb, B, K, brows, ldb, BK, bn / 2);
-  } else {
-    r = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);
-  }
-  if (r) return r - 100;
-  return b_mn ? launch_gemm<256, 0, 1, true>(ta, tb, p, stream) : launch_gemm<256, 0, 0, true>(ta, tb, p, stream);
-}

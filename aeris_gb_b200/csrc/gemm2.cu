@@ -14,6 +14,7 @@
 #include "api.h"
 #include "host.h"
 #include "gemm_epilogue.cuh"
+#include "gemm_ag.cuh"
 
 #include <stdio.h>
 #include <stdlib.h>
@@ -89,8 +90,12 @@ __device__ __forceinline__ void umma2_ss(uint32_t tmem_d, uint64_t adesc, uint64
       : "memory");
 }
 
-template <int A_MN, int B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+// AG = true: the A operand is all-gathered over peer memory inside the kernel (GemmParams::ag_*): m-tiles are visited
+// starting with this rank's own row chunk while two extra warps (6, 7) of every CTA push that chunk into the peers'
+// buffers; the producer of each CTA waits for the chunks its 128 rows come from. The grid is then always the full
+// number of CTA pairs, so that every call adds the same amount to the arrival counters.
+template <int A_MN, int B_MN, bool AG = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AG ? G2_THREADS + AG_COPY_THREADS : G2_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
              const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -112,6 +117,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   const int kb_total = (p.K + G2_BK - 1) / G2_BK;
   const int kb_per_split = (kb_total + p.k_splits - 1) / p.k_splits;
   const int total_tiles = m_tiles * n_tiles * p.k_splits;
+  const int tm_rot = AG ? (p.ag_rank * p.ag_rows) / (2 * G2_BM) : 0;
+  auto phys_tm = [&](int tm) { return AG ? (tm + tm_rot) % m_tiles : tm; };
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_a);
@@ -142,13 +149,17 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      [[maybe_unused]] uint32_t ag_ready = 0;
       for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
         const int split = tile / (m_tiles * n_tiles);
         const int mn = tile - split * (m_tiles * n_tiles);
-        const int tm = mn / n_tiles, tn = mn - tm * n_tiles;
+        const int tm = phys_tm(mn / n_tiles), tn = mn - (mn / n_tiles) * n_tiles;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb_total, kb0 + kb_per_split);
         const int m0 = tm * 2 * G2_BM + crank * G2_BM;
+        if constexpr (AG) {
+          if (m0 < p.M && !ag_wait_rows(p, m0, m0 + G2_BM, ag_ready)) { ok = false; break; }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_poll(&empty_bar[stage], phase ^ 1, p.status, ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * G2_STAGE_BYTES;
@@ -216,6 +227,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         }
       }
     }
+  } else if (AG && warp >= 6) {
+    // ------------------------------------------------------------ all-gather copiers (warps 6, 7 of both CTAs)
+    if constexpr (AG) ag_push_chunk(p, threadIdx.x - G2_THREADS);
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
     const int q = warp & 3;
@@ -226,7 +240,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
       const int split = tile / (m_tiles * n_tiles);
       const int mn = tile - split * (m_tiles * n_tiles);
-      const int tm = mn / n_tiles, tn = mn - tm * n_tiles;
+      const int tm = phys_tm(mn / n_tiles), tn = mn - (mn / n_tiles) * n_tiles;
       if (!mbar_wait_poll(&tfull_bar[acc], acc_phase, p.status, ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int row = tm * 2 * G2_BM + crank * G2_BM + q * 32 + lane;
@@ -247,10 +261,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   if (warp == 1) tmem_dealloc2(tmem_base, 2 * G2_BN);
 }
 
-template <int A_MN, int B_MN>
-static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+template <int A_MN, int B_MN, bool AG = false>
+static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p_in, cudaStream_t stream) {
   static bool configured = false;
-  auto kern = gemm2_kernel<A_MN, B_MN>;
+  GemmParams p = p_in;
+  constexpr int THREADS = AG ? G2_THREADS + AG_COPY_THREADS : G2_THREADS;
+  auto kern = gemm2_kernel<A_MN, B_MN, AG>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM) != cudaSuccess) return -20;
     configured = true;
@@ -262,7 +278,7 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   if (max_clusters == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_sms(), 1, 1);
-    cfg.blockDim = dim3(G2_THREADS, 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
     cfg.dynamicSmemBytes = G2_SMEM;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -274,8 +290,9 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     if (getenv("AERIS_DEBUG")) fprintf(stderr, "gemm2: max active clusters %d\n", n);
   }
   int clusters = max_clusters;
-  if (tiles < clusters) clusters = tiles;
-  kern<<<2 * clusters, G2_THREADS, G2_SMEM, stream>>>(ta, tb, p);
+  if (tiles < clusters && !AG) clusters = tiles;
+  if (AG) p.ag_expect *= static_cast<unsigned>(2 * clusters);   // came in as the call index
+  kern<<<2 * clusters, THREADS, G2_SMEM, stream>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
@@ -367,4 +384,47 @@ extern "C" int aeris_gemm_rs_push(const void* A, const void* B, int M, int N, in
   r = b_mn ? make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, G2_BK) : make_tmap_2d_bf16(&tb, B, K, N, ldb, G2_BK, G2_BN / 2);
   if (r) return r - 100;
   return b_mn ? launch_gemm2<0, 1>(ta, tb, p, stream) : launch_gemm2<0, 0>(ta, tb, p, stream);
+}
+
+// All-gather -> GEMM in one kernel (two-CTA tiles). `A` is this rank's [world * rows_per_rank, K] buffer (row pitch K)
+// whose chunk `rank` is filled; `peers[p]` is rank p's buffer of the same layout and `counter_peers[p]` its array of 8
+// arrival words (peer memory; zero before the first call, never reset). `call_index` counts the calls made on this
+// exchange (1, 2, ...; the same on every rank). On return of the kernel the whole gathered A is resident in `A` (the
+// weight-gradient product reuses it). The caller synchronises the ranks before the call (every rank is done with the
+// previous contents of the buffers). Epilogues: EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_BOTH, EPI_SWIGLU_BWD.
+extern "C" int aeris_gemm_allgather_a(void* A, const void* const* peers, const void* const* counter_peers, int world,
+                                      int rank, int rows_per_rank, unsigned call_index, const void* B, void* C, int N,
+                                      int K, int ldb, int ldc, int b_mn, int epi, const void* resid, int ldr, void* aux,
+                                      int ld_aux, int swiglu_f, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_per_rank <= 0 || N <= 0 || K <= 0) return -1;
+  if (N % G2_BN != 0 || K % 8 != 0 || (static_cast<long long>(rows_per_rank) * K) % 8 != 0) return -2;
+  const bool swiglu_fwd = (epi == EPI_SWIGLU || epi == EPI_SWIGLU_BOTH);
+  if (swiglu_fwd && b_mn) return -3;
+  if (epi != EPI_STORE && !swiglu_fwd && epi != EPI_SWIGLU_BWD) return -4;
+  const int M = world * rows_per_rank;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.epi = epi; p.C = C; p.ldc = ldc;
+  p.resid = reinterpret_cast<const __nv_bfloat16*>(resid); p.ldr = ldr;
+  p.rows_per_gate = M; p.aux = reinterpret_cast<__nv_bfloat16*>(aux); p.ld_aux = ld_aux;
+  p.k_splits = 1; p.status = status; p.swiglu_f = swiglu_f;
+  if (swiglu_fwd) { p.b_tile_stride = G2_BN / 2; p.b_half_off = swiglu_f; }
+  else            { p.b_tile_stride = G2_BN;     p.b_half_off = G2_BN / 2; }
+  for (int i = 0; i < world; ++i) {
+    p.ag_peers[i] = const_cast<void*>(peers[i]);
+    p.ag_count_peers[i] = reinterpret_cast<unsigned*>(const_cast<void*>(counter_peers[i]));
+  }
+  p.ag_local = A; p.ag_count = p.ag_count_peers[rank]; p.ag_world = world; p.ag_rank = rank; p.ag_rows = rows_per_rank;
+  p.ag_expect = call_index;     // multiplied by the grid size at launch
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d_bf16(&ta, A, K, M, K, G2_BK, G2_BM);
+  if (r) return r;
+  if (!b_mn) {
+    const uint64_t brows = swiglu_fwd ? static_cast<uint64_t>(2) * swiglu_f : static_cast<uint64_t>(N);
+    r = make_tmap_2d_bf16(&tb, B, K, brows, ldb, G2_BK, G2_BN / 2);
+  } else {
+    r = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, G2_BK);
+  }
+  if (r) return r - 100;
+  return b_mn ? launch_gemm2<0, 1, true>(ta, tb, p, stream) : launch_gemm2<0, 0, true>(ta, tb, p, stream);
 }

@@ -33,12 +33,16 @@ struct GemmParams {
   // EPI_RS_PUSH reuses scat_peers / scat_rank / scat_ld with scat_n_local = rows owned by one rank.
   void* scat_peers[8];
   int scat_rank, scat_n_local, scat_L, scat_sec_w, scat_own_w, scat_ld;
-  // All-gather fused into the A operand (one-CTA kernel only): A's rows are `ag_world` chunks of `ag_rows` rows; chunk
-  // ag_rank is already in place, copier warps pull the others from `ag_peers[c]` (same layout on every rank) into
-  // the local buffer `ag_local` and bump `ag_count[c]` once per CTA; tiles of a chunk wait for gridDim.x bumps.
-  const void* ag_peers[8];
-  void* ag_local;
-  unsigned* ag_count;
+  // All-gather fused into the A operand (one-CTA kernel only): A's rows are `ag_world` chunks of `ag_rows` rows. Chunk
+  // ag_rank is this rank's own and already in place in `ag_local`; copier warps PUSH it into every peer's buffer
+  // `ag_peers[p]` (same layout on every rank; posted stores, nearest consumer first) and then add 1 to word `ag_rank` of
+  // that peer's counter array `ag_count_peers[p]`. Tiles of chunk c wait until the local word `ag_count[c]` reaches
+  // `ag_expect` (counters only ever grow: expect = calls so far x CTAs per call).
+  void* ag_peers[8];
+  unsigned* ag_count_peers[8];
+  const void* ag_local;
+  const unsigned* ag_count;
+  unsigned ag_expect;
   int ag_world, ag_rank, ag_rows;
   int* status;
 };

@@ -156,10 +156,18 @@ def main():
             bufs = [torch.randn(M, K, device=dev).bfloat16() for _ in range(2)]
             w = torch.randn(N, K, device=dev).bfloat16()
             c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            cnt = torch.zeros(8, device=dev, dtype=torch.int32)
-            full = torch.cat([bufs[0][:M // 2], bufs[1][M // 2:]])
-            run = lambda: L.check(lib.aeris_gemm_allgather_a(L.ptr(bufs[0]), arr(bufs), 2, 0, M // 2, L.ptr(w), L.ptr(c), N,
-                                                             K, K, N, 0, 0, None, 0, None, 0, 0, L.ptr(cnt), st, sp_()), "ag")
+            # rank 0's view: its own counters and a second array standing in for rank 1's; the chunk "pushed by rank 1"
+            # is pre-filled and its arrival word pre-set, so the wait path runs and returns at once
+            cnts = [torch.zeros(8, device=dev, dtype=torch.int32) for _ in range(2)]
+            cnts[0][1] = 1 << 30
+            full = bufs[0].clone()
+            calls = [0]
+
+            def run():
+                calls[0] += 1
+                L.check(lib.aeris_gemm_allgather_a(L.ptr(bufs[0]), arr(bufs), arr(cnts), 2, 0, M // 2,
+                                                   ctypes.c_uint(calls[0]), L.ptr(w), L.ptr(c), N, K, K, N, 0, 0, None,
+                                                   0, None, 0, 0, st, sp_()), "ag")
             run()
             ref = G.gemm(full, w)
             out["max_abs_diff_vs_plain_gemm"] = (c.float() - ref.float()).abs().max().item()

@@ -3,7 +3,7 @@
 The token rows are sharded over the ``tp`` ranks (the layout Ulysses sequence parallelism already gives the residual
 stream), ``w1`` is split by output features and ``w2`` by input features:
 
-    X_full = all_gather_rows(h)                 -- fused: copier warps of the w1 GEMM pull the peers' rows over NVLink
+    X_full = all_gather_rows(h)                 -- fused: copier warps of the w1 GEMM push this rank's rows to the peers
     U_r    = X_full @ w1_r^T ; act_r = silu(gate) * up          while its tiles start on the local rows
     Y      = reduce_scatter_rows(act_r @ w2_r^T)  -- fused: the w2 GEMM's epilogue stores each bf16 partial tile into
                                                     the owner rank's slot buffer; the owner sums its slots
@@ -34,8 +34,16 @@ class TPExchange:
         self.group, self.device = group, torch.device(device)
         self.tp, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.barrier = RankBarrier(group, self.device, timeout_s)
-        self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)
+        import torch.distributed._symmetric_memory as symm_mem
+        # arrival words of the fused all-gather: word s of rank r counts the CTAs of rank s that have pushed their
+        # slice into r's buffer; they only ever grow (expected value = calls so far x CTAs per call)
+        self.counters = symm_mem.empty(8, dtype=torch.int32, device=self.device)
+        self.counters.zero_()
+        self._cnt_hdl = symm_mem.rendezvous(self.counters, group)
+        self.counter_ptrs = (ctypes.c_void_p * self.tp)(*[int(x) for x in self._cnt_hdl.buffer_ptrs])
+        self.ag_calls = 0
         self._bufs: dict[str, tuple] = {}
+        dist.barrier(group)
 
     def buffer(self, name: str, shape: tuple[int, int]):
         """Symmetric bf16 buffer (every rank asks for the same names and sizes in the same order)."""
@@ -62,12 +70,13 @@ def gemm_allgather_a(tpx: TPExchange, a_buf: torch.Tensor, peers, b: torch.Tenso
         swiglu_f = N // 2
     elif epi == G.EPI_SWIGLU_BWD:
         swiglu_f = N
+    tpx.ag_calls += 1
     rc = _l.lib().aeris_gemm_allgather_a(
-        _l.ptr(a_buf), peers, tpx.tp, tpx.rank, M // tpx.tp, _l.ptr(b), _l.ptr(out), N, K, b.stride(0),
-        out.stride(0), int(b_t), epi, _l.ptr(resid), resid.stride(0) if resid is not None else 0, _l.ptr(aux),
-        aux.stride(0) if aux is not None else 0, swiglu_f, _l.ptr(tpx.counters), _l.ptr(_l.status_word()),
-        _l.stream_ptr())
-    _l.check(rc, "aeris_gemm_allgather_a", kernels=2)
+        _l.ptr(a_buf), peers, tpx.counter_ptrs, tpx.tp, tpx.rank, M // tpx.tp, ctypes.c_uint(tpx.ag_calls),
+        _l.ptr(b), _l.ptr(out), N, K, b.stride(0), out.stride(0), int(b_t), epi, _l.ptr(resid),
+        resid.stride(0) if resid is not None else 0, _l.ptr(aux), aux.stride(0) if aux is not None else 0, swiglu_f,
+        _l.ptr(_l.status_word()), _l.stream_ptr())
+    _l.check(rc, "aeris_gemm_allgather_a")
     return out
 
 
