@@ -134,7 +134,10 @@ def bench_dp(a, dev, res):
         res[f"dp_step_{tag}_ms"] = t_all - t_fill
         link_rs = (world - 1) / world * nparams * 4
         link_ag = (world - 1) / world * nparams * 2
-        hbm = nparams * 4 + nparams / world * (4 * 4 * 2 + 2)     # own gradient read + shard state read/write
+        # HBM bytes per rank: every gradient word is read once from this rank's memory (by itself or a peer) and
+        # zeroed once; the shard reads 5 and writes 4 fp32 arrays plus the reduced gradient; every rank's bf16 shard
+        # is written into this rank's parameter buffer
+        hbm = nparams * 8 + nparams / world * (40 + 2 * world)
         roof = max((link_rs + link_ag) / (a.link_gbs * 1e6), hbm / (a.hbm_gbs * 1e6))
         res[f"dp_roofline_{tag}_ms"] = roof
         res[f"dp_frac_of_roofline_{tag}"] = roof / res[f"dp_step_{tag}_ms"]
