@@ -43,12 +43,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // -------------------------------------------------------------------------------------------------------- forward
 // grid = (q_tiles, H, n_win). One CTA owns a 128-row Q tile and streams the window's K/V in 64-row tiles through a
-// three-stage TMA ring. S = Q K^T is double buffered in TMEM, so the tensor core computes the scores of tile j+1 while
-// the four softmax warps (one thread per query row) work on tile j; each tile's 64 scores are read from TMEM once
-// and stay in registers for the exact row maximum, the exponentials and the bf16 probabilities that go back to shared
-// memory (double buffered) as the A operand of P V. The P V product of every tile lands in one of two TMEM buffers
-// and is folded into the register-resident running output with the online-softmax rescale.
+// two-stage TMA ring. Per tile: S = Q K^T lands in TMEM, the four softmax warps (one thread per query row) read its 64
+// scores once into registers and release the buffer at once, so the tensor core computes the next tile's scores under
+// the exponentials; the bf16 probabilities go to shared memory as the A operand of P V, which ACCUMULATES in one TMEM
+// buffer over all tiles. The running output is therefore never read back per tile: the exponentials use a reference
+// maximum that is only raised (and the TMEM accumulator and row sum rescaled) when a row's maximum grows by more than
+// 2^8, which bounds the probabilities by 256 and is exact after the final division by the row sum. The small footprint
+// (64 KB shared memory, 128 TMEM columns, no register-resident output) lets three CTAs share an SM at head_dim 64.
 constexpr int KVT = 64;
+constexpr float RESCALE_LOG2 = 8.0f;
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -56,29 +59,44 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// acc[lane row, 0..cols) *= alpha in TMEM, eight columns at a time: it runs only when a row maximum jumps and must not add
+// to the register pressure of the caller, whose 64 scores are live.
+__device__ __forceinline__ void rescale_tmem_rows(uint32_t taddr, int cols, float alpha) {
+#pragma unroll 1
+  for (int c = 0; c < cols; c += 8) {
+    uint32_t v[8];
+    tmem_ld8(taddr + c, v);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+    tmem_st8(taddr + c, v);
+  }
+  tmem_wait_st();
+}
+
 template <int DCH>
-__global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 2 : 1)
+__global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 3 : 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
   constexpr int HD = 64 * DCH;
   constexpr int Q_BYTES = DCH * 16384;
   constexpr int KV_BYTES = 2 * DCH * 8192;  // K tile + V tile (64 rows each)
-  constexpr int NST = 3;
+  constexpr int NST = 2;
   constexpr int P_BYTES = 16384;            // [128 x 64] bf16
-  constexpr int TMEM_COLS = (DCH == 1) ? 256 : 512;
+  constexpr int TMEM_COLS = (DCH == 1) ? 128 : 256;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Q_BYTES;
   uint8_t* sP = sKV + NST * KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;    // [3]
-  uint64_t* kv_empty = bars + 4;   // [3]
-  uint64_t* s_full = bars + 7;     // [2]
-  uint64_t* p_full = bars + 9;     // [2]
-  uint64_t* o_full = bars + 11;    // [2]
-  uint64_t* o_free = bars + 13;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* kv_full = bars + 1;    // [2]
+  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;     // scores of tile j are in TMEM
+  uint64_t* s_free = bars + 6;     // every softmax warp has read them into registers
+  uint64_t* p_full = bars + 7;     // probabilities of tile j are in shared memory
+  uint64_t* pv_done = bars + 8;    // P V of tile j has completed (P buffer reusable, accumulator up to date)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -103,10 +121,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
     mbar_init(q_full, 1);
     for (int i = 0; i < NST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4);
-      mbar_init(&o_full[i], 1); mbar_init(&o_free[i], 4);
-    }
+    // only the softmax warps that own at least one real query row take part in the hand-shakes: a warp without rows
+    // would run a tile ahead of the others and its arrivals would complete a phase that belongs to the slower warps
+    const int n_valid_warps = min(4, (N - qt * TILE + 31) / 32);
+    mbar_init(s_full, 1); mbar_init(s_free, n_valid_warps); mbar_init(p_full, n_valid_warps); mbar_init(pv_done, 1);
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -114,8 +132,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS0 = tmem_base;          // S[2] : 2 x 64 columns
-  const uint32_t tO0 = tmem_base + 128;    // O_part[2] : 2 x HD columns
+  const uint32_t tS = tmem_base;          // S : 64 columns
+  const uint32_t tO = tmem_base + 64;     // O : HD columns, accumulated over all tiles
 
   if (warp == 0) {
     if (elect_one_sync()) {
@@ -142,7 +160,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (elect_one_sync()) {
       bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_ATTN);
       const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aKV = smem_u32(sKV);
-      // S[j & 1] = Q K_j^T  (A = Q K-major, B = K K-major, reduction over d)
+      // S = Q K_j^T  (A = Q K-major, B = K K-major, reduction over d)
       auto issue_qk = [&](int j) -> bool {
         const int st = j % NST;
         if (!mbar_wait(&kv_full[st], (j / NST) & 1, p.status, ERR_TIMEOUT_ATTN)) return false;
@@ -154,29 +172,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int kk = 0; kk < 4 * DCH; ++kk) {
           const uint32_t qoff = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t koff = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_ss(tS0 + (j & 1) * 64, make_smem_desc(aQ + qoff, 0, 1024), make_smem_desc(aK + koff, 0, 1024),
-                  idesc_qk, kk > 0);
+          umma_ss(tS, make_smem_desc(aQ + qoff, 0, 1024), make_smem_desc(aK + koff, 0, 1024), idesc_qk, kk > 0);
         }
-        tc_commit(&s_full[j & 1]);
+        tc_commit(s_full);
         return true;
       };
       if (ok) ok = issue_qk(0);
-      if (ok && nkv > 1) ok = issue_qk(1);
       for (int j = 0; j < nkv && ok; ++j) {
-        const int b = j & 1, st = j % NST;
+        const int st = j % NST;
         const int ncur = (j == nkv - 1) ? n_last : KVT;
-        if (!mbar_wait(&p_full[b], (j >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
-        if (!mbar_wait(&o_free[b], ((j >> 1) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+        if (j + 1 < nkv) {     // the next tile's scores, as soon as this tile's have been read out of TMEM
+          if (!mbar_wait(s_free, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+          tc_fence_after();
+          if (!issue_qk(j + 1)) { ok = false; break; }
+        }
+        if (!mbar_wait(p_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
         tc_fence_after();
-        // O_part[b] = P_j V_j  (A = P K-major over kv, B = V MN-major: d contiguous, kv rows strided)
+        // O += P_j V_j  (A = P K-major over kv, B = V MN-major: d contiguous, kv rows strided)
         const uint32_t aV = aKV + st * KV_BYTES + DCH * 8192;
         const uint32_t idesc_pv = make_idesc_bf16(TILE, HD, 0, 1);
         for (int kk = 0; kk < ncur / 16; ++kk)
-          umma_ss(tO0 + b * HD, make_smem_desc(aP + b * P_BYTES + kk * 32, 0, 1024),
-                  make_smem_desc(aV + kk * 2048, 8192, 1024), idesc_pv, kk > 0);
-        tc_commit(&o_full[b]);
+          umma_ss(tO, make_smem_desc(aP + kk * 32, 0, 1024), make_smem_desc(aV + kk * 2048, 8192, 1024), idesc_pv,
+                  (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(pv_done);
         tc_commit(&kv_empty[st]);
-        if (j + 2 < nkv) ok = issue_qk(j + 2);   // S[b] is free: the softmax warps signalled p_full[b] after reading it
       }
     }
   } else {
@@ -186,25 +205,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool warp_valid = (qt * TILE + q * 32) < N;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const float sl2 = p.scale_log2;
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
-    float acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+    float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < nkv && ok; ++j) {
-      const int b = j & 1;
+    // Raises the reference maximum to m_new: rescales the TMEM accumulator (once P V of the previous tile is done) and l.
+    auto rescale = [&](int j, float m_new, bool& waited) -> bool {
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) return false;
+        waited = true;
+        tc_fence_after();
+        const float alpha = fast_exp2(m_ref - m_new);
+        rescale_tmem_rows(tO + lane_addr, HD, alpha);
+        tc_fence_before();
+        l *= alpha;
+      }
+      m_ref = m_new;
+      return true;
+    };
+    for (int j = 0; j < nkv && ok && warp_valid; ++j) {
       const bool last = (j == nkv - 1);
-      if (!mbar_wait(&s_full[b], (j >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+      if (!mbar_wait(s_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
       tc_fence_after();
-      float alpha = 1.f;
-      uint8_t* sPb = sP + b * P_BYTES;
-      if (warp_valid) {
-        if (!last || rem == 0) {
-          // full 64-column tile: one TMEM read, scores stay in registers
-          uint32_t v0[32], v1[32];
-          tmem_ld32(tS0 + b * 64 + lane_addr, v0);
-          tmem_ld32(tS0 + b * 64 + lane_addr + 32, v1);
+      bool waited = false;
+      if (!last || rem == 0) {
+        // full 64-column tile: one TMEM read, scores stay in registers, the TMEM buffer is released at once
+        uint32_t v0[32], v1[32];
+        if (warp_valid) {
+          tmem_ld32(tS + lane_addr, v0);
+          tmem_ld32(tS + lane_addr + 32, v1);
           tmem_wait_ld();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+        if (warp_valid) {
           float mx = max3(__uint_as_float(v0[0]), __uint_as_float(v0[1]), __uint_as_float(v1[0]));
 #pragma unroll
           for (int i = 1; i < 16; ++i) {
@@ -212,59 +245,60 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mx = max3(mx, __uint_as_float(v1[2 * i - 1]), __uint_as_float(v1[2 * i]));
           }
           mx = fmaxf(mx, __uint_as_float(v1[31]));
-          const float m_new = fmaxf(m, mx * sl2);
-          alpha = fast_exp2(m - m_new);  // first tile: exp2(-inf) = 0
+          const float m_new = fmaxf(m_ref, mx * sl2);
+          if (__any_sync(0xffffffffu, m_new - m_ref > RESCALE_LOG2)) {
+            if (!rescale(j, m_new, waited)) { ok = false; break; }
+          }
+          uint32_t pk[32];
           float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint32_t pk[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(v0[8 * g + 2 * i]), sl2, -m_new));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(v0[8 * g + 2 * i + 1]), sl2, -m_new));
-              rs0 += p0; rs1 += p1;
-              pk[i] = pack_bf16x2(p0, p1);
-            }
-            *reinterpret_cast<uint4*>(sPb + swz128(row, g)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v0[2 * i]), sl2, -m_ref));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v0[2 * i + 1]), sl2, -m_ref));
+            rs0 += p0; rs1 += p1;
+            pk[i] = pack_bf16x2(p0, p1);
           }
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint32_t pk[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(v1[8 * g + 2 * i]), sl2, -m_new));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(v1[8 * g + 2 * i + 1]), sl2, -m_new));
-              rs0 += p0; rs1 += p1;
-              pk[i] = pack_bf16x2(p0, p1);
-            }
-            *reinterpret_cast<uint4*>(sPb + swz128(row, 4 + g)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v1[2 * i]), sl2, -m_ref));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v1[2 * i + 1]), sl2, -m_ref));
+            rs0 += p0; rs1 += p1;
+            pk[16 + i] = pack_bf16x2(p0, p1);
           }
-          l = l * alpha + (rs0 + rs1);
-          m = m_new;
-        } else {
-          // last, partial tile: n_last (multiple of 16) columns computed, `rem` of them valid
+          l += rs0 + rs1;
+          if (j > 0 && !waited && !mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<uint4*>(sP + swz128(row, g)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+        }
+      } else {
+        // last, partial tile: n_last (multiple of 16) columns computed, `rem` of them valid; no tile follows
+        if (warp_valid) {
           float mx = -INFINITY;
 #pragma unroll 1
           for (int c = 0; c < n_last; c += 16) {
             uint32_t v[16];
-            tmem_ld16(tS0 + b * 64 + lane_addr + c, v);
+            tmem_ld16(tS + lane_addr + c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               if (c + i < rem) mx = fmaxf(mx, __uint_as_float(v[i]));
           }
-          const float m_new = fmaxf(m, mx * sl2);
-          alpha = fast_exp2(m - m_new);
+          const float m_new = fmaxf(m_ref, mx * sl2);
+          if (__any_sync(0xffffffffu, m_new - m_ref > RESCALE_LOG2)) {
+            if (!rescale(j, m_new, waited)) { ok = false; break; }
+          }
+          if (j > 0 && !waited && !mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
           float rs = 0.f;
 #pragma unroll 1
           for (int c = 0; c < n_last; c += 16) {
             uint32_t v[16], pk[8];
-            tmem_ld16(tS0 + b * 64 + lane_addr + c, v);
+            tmem_ld16(tS + lane_addr + c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), sl2, -m_new));
-              float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sl2, -m_new));
+              float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), sl2, -m_ref));
+              float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sl2, -m_ref));
               if (c + 2 * i >= rem) p0 = 0.f;
               if (c + 2 * i + 1 >= rem) p1 = 0.f;
               rs += p0 + p1;
@@ -272,75 +306,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
 #pragma unroll
             for (int g = 0; g < 2; ++g)
-              *reinterpret_cast<uint4*>(sPb + swz128(row, (c >> 3) + g)) =
+              *reinterpret_cast<uint4*>(sP + swz128(row, (c >> 3) + g)) =
                   make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
           }
-          l = l * alpha + rs;
-          m = m_new;
+          l += rs;
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[b]);
-      // fold in the previous tile's P V product
-      if (j > 0) {
-        const int pb = (j - 1) & 1;
-        if (!mbar_wait(&o_full[pb], ((j - 1) >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
-        tc_fence_after();
-        if (warp_valid) {
-#pragma unroll
-          for (int c = 0; c < HD; c += 32) {
-            uint32_t v[32];
-            tmem_ld32(tO0 + pb * HD + lane_addr + c, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(acc[c + i], alpha_prev, __uint_as_float(v[i]));
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&o_free[pb]);
-      }
-      alpha_prev = alpha;
+      if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok) {
-      const int pb = (nkv - 1) & 1;
-      if (mbar_wait(&o_full[pb], ((nkv - 1) >> 1) & 1, p.status, ERR_TIMEOUT_ATTN)) {
-        tc_fence_after();
-        if (warp_valid) {
+    if (ok && warp_valid && mbar_wait(pv_done, (nkv - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) {
+      tc_fence_after();
+      {
+        const float inv = 1.f / l;
+        const size_t trow = static_cast<size_t>(win) * N + grow;
+        __nv_bfloat16* dst = (p.O && grow < N) ? p.O + trow * p.ldo + head * HD : nullptr;
+        __nv_bfloat16* pdst = nullptr;
+        if (p.push_n_local > 0 && grow < N) {
+          const int owner = grow / p.push_n_local;
+          pdst = reinterpret_cast<__nv_bfloat16*>(p.o_peers[owner]) +
+                 (static_cast<size_t>(win) * p.push_n_local + (grow - owner * p.push_n_local)) * p.push_ld +
+                 p.push_col0 + head * HD;
+        }
 #pragma unroll
-          for (int c = 0; c < HD; c += 32) {
-            uint32_t v[32];
-            tmem_ld32(tO0 + pb * HD + lane_addr + c, v);
-            tmem_wait_ld();
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tO + lane_addr + c, v);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(acc[c + i], alpha_prev, __uint_as_float(v[i]));
-          }
-          if (grow < N) {
-            const float inv = 1.f / l;
-            const size_t trow = static_cast<size_t>(win) * N + grow;
-            __nv_bfloat16* dst = p.O ? p.O + trow * p.ldo + head * HD : nullptr;
-            __nv_bfloat16* pdst = nullptr;
-            if (p.push_n_local > 0) {
-              const int owner = grow / p.push_n_local;
-              pdst = reinterpret_cast<__nv_bfloat16*>(p.o_peers[owner]) +
-                     (static_cast<size_t>(win) * p.push_n_local + (grow - owner * p.push_n_local)) * p.push_ld +
-                     p.push_col0 + head * HD;
-            }
-#pragma unroll
-            for (int c = 0; c < HD; c += 8) {
-              uint4 u;
-              u.x = pack_bf16x2(acc[c] * inv, acc[c + 1] * inv);
-              u.y = pack_bf16x2(acc[c + 2] * inv, acc[c + 3] * inv);
-              u.z = pack_bf16x2(acc[c + 4] * inv, acc[c + 5] * inv);
-              u.w = pack_bf16x2(acc[c + 6] * inv, acc[c + 7] * inv);
-              if (dst) *reinterpret_cast<uint4*>(dst + c) = u;
-              if (pdst) *reinterpret_cast<uint4*>(pdst + c) = u;
-            }
-            if (p.lse) p.lse[(static_cast<size_t>(win) * p.H + head) * N + grow] = m + log2f(l);
+          for (int g = 0; g < 4; ++g) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(v[8 * g]) * inv, __uint_as_float(v[8 * g + 1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv);
+            if (dst) *reinterpret_cast<uint4*>(dst + c + 8 * g) = u;
+            if (pdst) *reinterpret_cast<uint4*>(pdst + c + 8 * g) = u;
           }
         }
+        if (p.lse && grow < N) p.lse[(static_cast<size_t>(win) * p.H + head) * N + grow] = m_ref + log2f(l);
       }
     }
   }
@@ -353,7 +362,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 template <int DCH>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const AttnFwdParams& p, cudaStream_t stream) {
-  constexpr int SMEM = DCH * 16384 + 3 * 2 * DCH * 8192 + 2 * 16384 + 256;
+  constexpr int SMEM = DCH * 16384 + 2 * 2 * DCH * 8192 + 16384 + 256;
   static bool configured = false;
   auto kern = attn_fwd_kernel<DCH>;
   if (!configured) {

@@ -80,6 +80,27 @@ def test_attention_fwd_bwd(nw, N, H, d):
     assert (lse - lref).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("N,d", [(900, 64), (900, 128), (320, 64)])
+def test_attention_fwd_rising_scores(N, d):
+    """Scores that grow along the key sequence by far more than 2^8: the forward kernel must raise its reference
+    maximum (and rescale its TMEM accumulator) many times, in full and in partial tiles."""
+    from aeris_gb_b200.ops import attention as A
+    nw, H = 4, 3
+    g = torch.Generator(device=DEV).manual_seed(3)
+    qkv = torch.randn(nw, N, 3, H, d, device=DEV, generator=g)
+    ramp = torch.linspace(0.2, 6.0, N, device=DEV).view(1, N, 1, 1)
+    qkv[:, :, 0] *= 3.0
+    qkv[:, :, 1] *= ramp                       # later keys score higher (and lower) than earlier ones
+    qkv = qkv.reshape(nw * N, 3 * H * d).bfloat16()
+    o, lse = A.attn_fwd(qkv, nw, N, H, d)
+    ref = A.attn_reference(qkv.float(), nw, N, H, d)
+    assert torch.isfinite(o.float()).all()
+    assert rel_err(o, ref) < 1.5e-2
+    q, k, _ = qkv.float().view(nw, N, 3, H, d).permute(2, 0, 3, 1, 4)
+    lref = torch.logsumexp((q @ k.transpose(-1, -2)) / math.sqrt(d), -1) / math.log(2)
+    assert (lse - lref).abs().max().item() < 2e-2
+
+
 @pytest.mark.parametrize("D", [128, 1536])
 @pytest.mark.parametrize("mode", [0, 1])
 def test_modnorm_fwd_bwd(D, mode):
