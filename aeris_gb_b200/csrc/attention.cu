@@ -238,34 +238,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free);
         if (warp_valid) {
-          float mx = max3(__uint_as_float(v0[0]), __uint_as_float(v0[1]), __uint_as_float(v1[0]));
+          // four independent chains of eight 3-input maxima instead of one chain of thirty-two
+          float mxc[4];
 #pragma unroll
-          for (int i = 1; i < 16; ++i) {
-            mx = max3(mx, __uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
-            mx = max3(mx, __uint_as_float(v1[2 * i - 1]), __uint_as_float(v1[2 * i]));
+          for (int c = 0; c < 4; ++c)
+            mxc[c] = fmaxf(__uint_as_float(v0[c]), __uint_as_float(v1[c]));
+#pragma unroll
+          for (int i = 1; i < 8; ++i) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              mxc[c] = max3(mxc[c], __uint_as_float(v0[4 * i + c]), __uint_as_float(v1[4 * i + c]));
           }
-          mx = fmaxf(mx, __uint_as_float(v1[31]));
+          const float mx = fmaxf(max3(mxc[0], mxc[1], mxc[2]), mxc[3]);
           const float m_new = fmaxf(m_ref, mx * sl2);
           if (__any_sync(0xffffffffu, m_new - m_ref > RESCALE_LOG2)) {
             if (!rescale(j, m_new, waited)) { ok = false; break; }
           }
           uint32_t pk[32];
-          float rs0 = 0.f, rs1 = 0.f;
+          float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(v0[2 * i]), sl2, -m_ref));
             const float p1 = fast_exp2(fmaf(__uint_as_float(v0[2 * i + 1]), sl2, -m_ref));
-            rs0 += p0; rs1 += p1;
+            rs[(2 * i) & 3] += p0; rs[(2 * i + 1) & 3] += p1;
             pk[i] = pack_bf16x2(p0, p1);
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(v1[2 * i]), sl2, -m_ref));
             const float p1 = fast_exp2(fmaf(__uint_as_float(v1[2 * i + 1]), sl2, -m_ref));
-            rs0 += p0; rs1 += p1;
+            rs[(2 * i) & 3] += p0; rs[(2 * i + 1) & 3] += p1;
             pk[16 + i] = pack_bf16x2(p0, p1);
           }
-          l += rs0 + rs1;
+          l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
           if (j > 0 && !waited && !mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
 #pragma unroll
           for (int g = 0; g < 8; ++g)

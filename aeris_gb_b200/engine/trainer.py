@@ -43,7 +43,7 @@ def wp_grid_for(n: int) -> tuple[int, int]:
 class Trainer:
     def __init__(self, model_cfg: AerisConfig, optim_cfg: OptimConfig, diff_cfg: DiffusionConfig, device,
                  seed: int = 1234, wp_group=None, dp_size: int = 1, dp_rank: int = 0, model: AerisModel | None = None,
-                 fused_dp: bool | None = None, use_multicast: bool = True, sp_group=None,
+                 fused_dp: bool | None = None, use_multicast: bool = False, sp_group=None,
                  fused_io: bool | None = None):
         self.cfg, self.ocfg, self.dcfg = model_cfg, optim_cfg, diff_cfg
         self.device = torch.device(device)

@@ -8,6 +8,27 @@ import torch
 from . import lib as _l
 
 
+def _kernel_dim(d: int) -> int:
+    """The kernels are built for 64- and 128-wide heads; other widths (for example 32) run zero-padded to the next one:
+    zero columns change neither Q K^T nor the valid columns of P V."""
+    if d in (64, 128):
+        return d
+    assert 0 < d < 128, f"head_dim {d} is not supported"
+    return 64 if d < 64 else 128
+
+
+def _pad_heads(t: torch.Tensor, parts: int, H: int, d: int, dp: int) -> torch.Tensor:
+    T = t.shape[0]
+    out = t.new_zeros((T, parts, H, dp))
+    out[..., :d] = t.reshape(T, parts, H, d)
+    return out.view(T, parts * H * dp)
+
+
+def _unpad_heads(t: torch.Tensor, parts: int, H: int, d: int, dp: int) -> torch.Tensor:
+    T = t.shape[0]
+    return t.view(T, parts, H, dp)[..., :d].reshape(T, parts * H * d)
+
+
 def attn_fwd(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int, *, out: torch.Tensor | None = None,
              lse: torch.Tensor | None = None, scale: float | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """softmax(Q K^T * scale) V for every (window, head).
@@ -17,6 +38,15 @@ def attn_fwd(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int, *, out: torc
     """
     T, C = qkv.shape
     assert T == n_win * N and C == 3 * H * d and qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
+    dp = _kernel_dim(d)
+    if dp != d:
+        o_p, lse = attn_fwd(_pad_heads(qkv, 3, H, d, dp), n_win, N, H, dp, lse=lse,
+                            scale=scale if scale is not None else 1.0 / math.sqrt(d))
+        o = _unpad_heads(o_p, 1, H, d, dp)
+        if out is not None:
+            out.copy_(o)
+            o = out
+        return o, lse
     if out is None:
         out = torch.empty((T, H * d), dtype=torch.bfloat16, device=qkv.device)
     if lse is None:
@@ -44,6 +74,15 @@ def attn_bwd(qkv: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor, lse: torch.T
     """Gradient of :func:`attn_fwd` with respect to the fused qkv tensor (same layout as ``qkv``)."""
     T, C = qkv.shape
     assert o.shape == (T, H * d) and d_o.shape == (T, H * d) and d_o.stride(1) == 1 and o.stride(0) == d_o.stride(0)
+    dp = _kernel_dim(d)
+    if dp != d:
+        g_p = attn_bwd(_pad_heads(qkv, 3, H, d, dp), _pad_heads(o, 1, H, d, dp), _pad_heads(d_o, 1, H, d, dp), lse,
+                       n_win, N, H, dp, delta=delta, scale=scale if scale is not None else 1.0 / math.sqrt(d))
+        g = _unpad_heads(g_p, 3, H, d, dp)
+        if dqkv is not None:
+            dqkv.copy_(g)
+            g = dqkv
+        return g
     if dqkv is None:
         dqkv = torch.empty_like(qkv)
     if delta is None:

@@ -61,7 +61,8 @@ def test_gemm_epilogues(M, N, K):
     assert rel_err(o, x.float() + g * ref) < TOL and rel_err(aux, ref) < TOL
 
 
-@pytest.mark.parametrize("nw,N,H,d", [(2, 64, 2, 64), (3, 256, 2, 64), (3, 900, 4, 64), (2, 900, 2, 128), (2, 100, 1, 64)])
+@pytest.mark.parametrize("nw,N,H,d", [(2, 64, 2, 64), (3, 256, 2, 64), (3, 900, 4, 64), (2, 900, 2, 128), (2, 100, 1, 64),
+                                        (2, 64, 4, 32), (2, 900, 2, 32)])
 def test_attention_fwd_bwd(nw, N, H, d):
     from aeris_gb_b200.ops import attention as A
     qkv = torch.randn(nw * N, 3 * H * d, device=DEV).bfloat16()
