@@ -70,7 +70,11 @@ class ParallelEngine:
             self.opt = DistOptimizer(self.module, optim_cfg, self.groups.get("weight"), rs_grads=ecfg.rs_grads)
         else:
             self.opt = FlatOptimizer(self.module, optim_cfg)
-        sched_cls = SCH.OverlappedTrainSchedule if ecfg.overlap_p2p else SCH.TrainSchedule
+        # The overlapped schedule posts receives a step early and sends right after compute; that needs a transport that
+        # accepts sends and receives in any order (gloo, MPI). NCCL p2p calls of a pair of ranks must be enqueued in
+        # matching order, so on CUDA the plain 1F1B order is used; its transfers still run on NCCL's own stream.
+        overlap = ecfg.overlap_p2p and self.device.type != "cuda"
+        sched_cls = SCH.OverlappedTrainSchedule if overlap else SCH.TrainSchedule
         self.schedule = sched_cls(self.GAS, self.PP, self.c.pp)
         nb = self.schedule.num_pipe_buffers()
         self.buf = {k: [None] * nb for k in ("inputs", "outputs", "dt_in", "dt_out", "x", "z", "t", "grad_x", "grad_dt")}

@@ -1,0 +1,87 @@
+"""Worker of the GPU pipeline-parallel test: the instruction-schedule engine with NCCL p2p between the stages (PP = 2,
+one GPU per stage group, CUDA kernels in every block) has to reproduce the losses and the updated weights of the same
+engine with every stage on one GPU. argv[1] = 1 uses the overlapped 1F1B schedule."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from aeris_gb_b200.engine.optim import OptimConfig  # noqa: E402
+from aeris_gb_b200.engine.pipeline import EngineConfig, ParallelEngine  # noqa: E402
+from aeris_gb_b200.engine.trainer import DiffusionConfig  # noqa: E402
+from aeris_gb_b200.models.aeris import AerisConfig  # noqa: E402
+from aeris_gb_b200.ops import lib as L  # noqa: E402
+from aeris_gb_b200.parallel.topology import ProcessGrid  # noqa: E402
+
+IMG, CH, CC = (32, 64), 6, 6
+
+
+def _field(seed, C):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(1, IMG[0], IMG[1], C, generator=g)
+
+
+def _idx(eng):
+    return eng.loads
+
+
+def build(grid, rank, dev, overlap, groups=None):
+    cfg = AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=128, heads=2, head_dim=64,
+                      mlp_dim=256, n_layers=4, sublayers=1, norm_eps=1e-3, chunk_windows=5)
+    ecfg = EngineConfig(gas=4, overlap_p2p=overlap, checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5)
+    eng = ParallelEngine(cfg, OptimConfig(lr=1e-2, lr_rampup_img=0, grad_clip_max_norm=1.0, weight_decay=0.0),
+                         DiffusionConfig(grad_scale_parity=False, cond_channels=CC), ecfg, grid, rank, dev,
+                         data_fn=lambda e: (_field(1000 + _idx(e), CC), _field(2000 + _idx(e), CH)), groups=groups)
+    for st, sd in eng.module.logical_state_dicts().items():     # identical weights for any split
+        g = torch.Generator().manual_seed(100 + st)
+        for k, v in sd.items():
+            if v.dtype.is_floating_point and "inv_freq" not in k:
+                v.copy_((torch.randn(v.shape, generator=g) * 0.05).to(v.dtype))
+    eng.opt = type(eng.opt)(eng.module, eng.ocfg)
+    eng.noise_fn = lambda e: _field(3000 + _idx(e), CH)
+    eng.t_fn = lambda e: torch.tensor([0.2 + 0.13 * (_idx(e) % 9)])
+    return eng
+
+
+def main():
+    overlap = bool(int(sys.argv[1])) if len(sys.argv) > 1 else False
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    iters = 2
+    # reference: all stages on this GPU, no communication
+    ref = build(ProcessGrid(1, PP=1), 0, dev, False, groups={})
+    ref_loss = []
+    for _ in range(iters):
+        ref.exec_schedule()
+        ref_loss.append(float(ref.tot_loss))
+    ref_sd = {st: {k: v.clone() for k, v in sd.items()} for st, sd in ref.module.logical_state_dicts().items()}
+    del ref
+    eng = build(ProcessGrid(world, PP=world), rank, dev, overlap)
+    loss = []
+    for _ in range(iters):
+        eng.exec_schedule()
+        loss.append(float(eng.tot_loss))
+    L.check_status()
+    worst = 0.0
+    for st, sd in eng.module.logical_state_dicts().items():
+        for k, v in sd.items():
+            if v.dtype.is_floating_point:
+                d = (v.float() - ref_sd[st][k].float()).abs().max().item()
+                worst = max(worst, d / max(ref_sd[st][k].float().abs().max().item(), 1e-3))
+    ok = worst < 3e-2
+    if eng.is_last_stage():
+        ok = ok and all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(loss, ref_loss))
+        print(f"pp{world} overlap={overlap}: losses {loss} vs single-GPU {ref_loss}; worst weight diff {worst:.2e}", flush=True)
+    flag = torch.tensor([0.0 if ok else 1.0], device=dev)
+    dist.all_reduce(flag)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -31,7 +31,7 @@ def test_fused_gradient_reduce_adamw_allgather(multicast):
     worker = os.path.join(os.path.dirname(__file__), "fused_dp_worker.py")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
                         "--master-addr", "127.0.0.1", "--master-port", str(29520 + multicast), worker, str(multicast)],
-                       capture_output=True, text=True, timeout=600)
+                       capture_output=True, text=True, timeout=240)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
 
 
@@ -44,5 +44,18 @@ def test_tensor_parallel_mlp(n):
     worker = os.path.join(os.path.dirname(__file__), "tp_worker.py")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
                         "--master-addr", "127.0.0.1", "--master-port", str(29540 + n), worker],
-                       capture_output=True, text=True, timeout=600)
+                       capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("overlap", [0])
+def test_pipeline_parallel_nccl(overlap):
+    """PP = 2 over NCCL p2p (1F1B) on the CUDA kernels against all stages on one GPU."""
+    n = 2
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    worker = os.path.join(os.path.dirname(__file__), "pp_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29560 + overlap), worker, str(overlap)],
+                       capture_output=True, text=True, timeout=240)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
