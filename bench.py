@@ -93,6 +93,70 @@ def flagship_config(n_gpus: int, scale: str, sp: int = 1):
                        head_dim=64, mlp_dim=512, n_layers=4, sublayers=1, wp=wp, sp=sp, chunk_windows=8)
 
 
+def infer_arm(args):
+    """WP-only ensemble forecast, one member per GPU: seconds per 6-hour forecast step (``--sampler-steps`` TrigFlow
+    steps, Heun on all but the last: 2 n - 1 network evaluations), device-timed, max over ranks. ``--steps`` forecast
+    steps are timed after one warm-up forecast step."""
+    import torch
+    import torch.distributed as dist
+    from aeris_gb_b200.diffusion.rollout import DeviceForecaster, SamplerConfig
+    from aeris_gb_b200.models.aeris import AerisModel, StreamContext
+    from aeris_gb_b200.ops import lib as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = flagship_config(1, args.scale)              # every GPU holds the whole image of its member
+    if args.layers:
+        cfg.n_layers = args.layers
+    torch.manual_seed(0)
+    model = AerisModel(cfg).to(dev).eval()
+    C = cfg.out_channels
+    stats = {"x_mean": torch.zeros(C, device=dev), "x_std": torch.ones(C, device=dev),
+             "t_mean": torch.zeros(C, device=dev), "t_std": torch.ones(C, device=dev)}
+    sampler = SamplerConfig(n_steps=args.sampler_steps, heun=True)
+    fc = DeviceForecaster(model, StreamContext(cfg, 1), stats, sampler, C, seed=1, member0=rank)
+    gen = torch.Generator().manual_seed(7)            # the same initial state for every member, noise differs
+    state = torch.randn(1, cfg.img[0], cfg.img[1], C, generator=gen).to(dev)
+    forcing = torch.randn(1, cfg.img[0], cfg.img[1], cfg.in_channels - 2 * C, generator=gen).to(dev)
+    state = fc.step(state, forcing)                   # warm-up forecast step
+    L.check_status()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clk = ClockSampler(local_rank)
+    clk.start()
+    l0 = L.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        state = fc.step(state, forcing)
+    e1.record()
+    torch.cuda.synchronize()
+    L.check_status(sync=False)
+    t = torch.tensor([e0.elapsed_time(e1) / 1e3 / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    clocks = clk.stop()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "WP-infer s/step (one member per GPU)", "value": t.item(), "unit": "s per forecast step",
+            "n_gpus": world, "steps": args.steps, "warmup": 1, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "members": world,
+            "member_forecast_steps_per_s": world / t.item(),
+            "config": {"model": f"AERIS Swin TrigFlow dim{cfg.dim} x{cfg.n_blocks} blocks ({cfg.param_count() / 1e9:.2f}B)",
+                       "sampler_steps": args.sampler_steps, "network_evals_per_step": fc.model_evals_per_forecast_step(),
+                       "scale": args.scale, "state_finite": bool(torch.isfinite(state).all().item())},
+            "clocks": clocks, "gpu_launches": L.launch_count() - l0, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9}))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -104,9 +168,14 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the number of Swin layers (development only)")
     ap.add_argument("--chunk-windows", type=int, default=0)
     ap.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel degree (WP = gpus / sp)")
+    ap.add_argument("--mode", default="train", choices=["train", "infer"],
+                    help="infer: one autoregressive forecast step per member, one member per GPU (s/step)")
+    ap.add_argument("--sampler-steps", type=int, default=10)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.mode == "infer":
+        return infer_arm(args)
 
     import torch
     import torch.distributed as dist
