@@ -91,10 +91,10 @@ def main(argv=None):
             wandb = None
 
     if PP == 1 and SP == 1:
-        groups = grid.build_groups(rank, kinds=("wp",)) if world > 1 else {}
+        groups = grid.build_groups(rank, kinds=("wp", "weight")) if world > 1 else {}
         trainer = Trainer(mcfg, ocfg, dcfg, device, seed=int(cfg.seed), wp_group=groups.get("wp"),
-                          dp_size=grid.DP, dp_rank=c.dp)
-        if cfg.model.get("load") and ckpt_dir and isinstance(trainer.opt, FlatOptimizer):
+                          dp_size=grid.DP, dp_rank=c.dp, weight_group=groups.get("weight"))
+        if cfg.model.get("load") and ckpt_dir:
             if load_stage_checkpoint(ckpt_dir, trainer.model, trainer.opt, device):
                 log0(f"loaded a checkpoint from {ckpt_dir} at {trainer.opt.cur_nimg} images")
         start = trainer.opt.cur_nimg // (gas * grid.DP)
@@ -112,10 +112,12 @@ def main(argv=None):
                  + (" SLOW STEP" if slow else ""))
             if wandb:
                 wandb.log(wandb_payload(it, trainer.opt.cur_nimg, tf, dt, loss, trainer.grad_norm(), trainer.opt.last_lr))
-            if ckpt_dir and not cfg.model.get("benchmark") and (it + 1) % 100 == 0 and rank == 0 \
-                    and isinstance(trainer.opt, FlatOptimizer):
-                save_stage_checkpoint(ckpt_dir, trainer.model, trainer.opt,
-                                      it=(it + 1) if (it + 1) % 1000 == 0 else None)
+            every = int(cfg.trainer.get("checkpoint_every", 100))
+            if ckpt_dir and not cfg.model.get("benchmark") and (it + 1) % every == 0:
+                # the sharded optimizer gathers its state over the group, so every rank calls; one rank writes
+                if rank == 0 or not isinstance(trainer.opt, FlatOptimizer):
+                    save_stage_checkpoint(ckpt_dir, trainer.model, trainer.opt,
+                                          it=(it + 1) if (it + 1) % 1000 == 0 else None, write=(rank == 0))
     else:
         ecfg = EngineConfig(gas=gas, overlap_p2p=bool(cfg.model.get("overlap_p2p_comms", False)),
                             dist_optimizer=bool(cfg.model.get("dist_optimizer", False)),

@@ -68,10 +68,12 @@ def _integrity(ckpt: dict) -> dict:
     return out
 
 
-def save_stage_checkpoint(directory: str, module, opt, it: int | None = None) -> list[str]:
-    """``module``: a PipelineStage or a whole AerisModel; ``opt``: FlatOptimizer built on it. Writes one file per
-    logical stage the module holds."""
-    os.makedirs(directory, exist_ok=True)
+def save_stage_checkpoint(directory: str, module, opt, it: int | None = None, write: bool = True) -> list[str]:
+    """``module``: a PipelineStage or a whole AerisModel; ``opt``: the optimizer built on it (FlatOptimizer, or the
+    sharded optimizer, whose state dicts are gathered collectively: then every rank of its group calls this function
+    and ``write`` is True on one of them). Writes one file per logical stage the module holds."""
+    if write:
+        os.makedirs(directory, exist_ok=True)
     model_sd = _logical(module, module.state_dict())
     master = _logical(module, dict(opt.master_state_dict()))
     ema = _logical(module, dict(opt.ema_state_dict())) if opt.cfg.use_ema else {}
@@ -79,6 +81,8 @@ def save_stage_checkpoint(directory: str, module, opt, it: int | None = None) ->
     exp_avg = _logical(module, osd["exp_avg"])
     exp_avg_sq = _logical(module, osd["exp_avg_sq"])
     written = []
+    if not write:
+        return written
     for stage, sd in model_sd.items():
         full_master = {k: v.detach().float().cpu().clone() for k, v in sd.items()}     # buffers and frozen params too
         full_master.update({k: v.detach().cpu().clone() for k, v in master.get(stage, {}).items()})

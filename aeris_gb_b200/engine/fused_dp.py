@@ -176,7 +176,63 @@ class FusedShardedOptimizer:
         self.last_lr = lr
         return self._sumsq
 
-    # ---- state ---------------------------------------------------------------------------------------------------
+    # ---- state in the layout of FlatOptimizer (collective: every rank of the group calls, all get the full dicts) ------
+    def _gather_full(self, s, shard: torch.Tensor) -> torch.Tensor:
+        if not s.low_precision:
+            return shard.detach().cpu().clone()
+        full = torch.empty(s.padded, dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+        out = full.cpu()
+        del full
+        return out
+
+    def _named(self, which: str) -> dict[str, torch.Tensor]:
+        out = {}
+        for s in self.segments:
+            shard = getattr(s, which)
+            if shard is None:
+                continue
+            full = self._gather_full(s, shard)
+            for name, p, off in zip(s.names, s.params, s.offs):
+                out[name] = full[off:off + p.numel()].view(p.shape)
+        return out
+
+    def master_state_dict(self) -> dict[str, torch.Tensor]:
+        return self._named("master")
+
+    def ema_state_dict(self) -> dict[str, torch.Tensor]:
+        return self._named("ema")
+
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "cur_nimg": self.cur_nimg, "exp_avg": self._named("m"),
+                "exp_avg_sq": self._named("v")}
+
+    def load_state_dict(self, sd: dict, master: dict | None = None, ema: dict | None = None):
+        """Inverse of the three dicts above: every rank takes its shard of each array; the bf16 model copy is rebuilt
+        from the masters on every rank."""
+        self.step_count, self.cur_nimg = int(sd["step"]), int(sd["cur_nimg"])
+        sources = {"m": sd.get("exp_avg"), "v": sd.get("exp_avg_sq"), "master": master, "ema": ema}
+        for s in self.segments:
+            for which, named in sources.items():
+                dst = getattr(s, which)
+                if named is None or dst is None:
+                    continue
+                for name, p, off in zip(s.names, s.params, s.offs):
+                    if name not in named:
+                        continue
+                    src = named[name].reshape(-1).float()
+                    n = p.numel()
+                    if s.low_precision:
+                        a, b = max(off, s.lo), min(off + n, s.lo + s.per)      # overlap with this rank's shard
+                        if a < b:
+                            dst[a - s.lo:b - s.lo].copy_(src[a - off:b - off])
+                        if which == "master":
+                            s.model_flat[off:off + n].copy_(src.to(s.model_flat.dtype))
+                    else:
+                        dst[off:off + n].copy_(src)
+        self.barrier()
+
+    # ---- per-rank shard state (no communication) ------------------------------------------------------------------
     def shard_state(self) -> dict:
         return {"step": self.step_count, "cur_nimg": self.cur_nimg, "rank": self.rank, "world": self.world,
                 "segments": [{"master": s.master.cpu(), "m": s.m.cpu(), "v": s.v.cpu(),

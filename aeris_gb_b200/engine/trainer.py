@@ -44,13 +44,15 @@ class Trainer:
     def __init__(self, model_cfg: AerisConfig, optim_cfg: OptimConfig, diff_cfg: DiffusionConfig, device,
                  seed: int = 1234, wp_group=None, dp_size: int = 1, dp_rank: int = 0, model: AerisModel | None = None,
                  fused_dp: bool | None = None, use_multicast: bool = False, sp_group=None,
-                 fused_io: bool | None = None):
+                 fused_io: bool | None = None, weight_group=None):
         self.cfg, self.ocfg, self.dcfg = model_cfg, optim_cfg, diff_cfg
         self.device = torch.device(device)
         # `wp_group`: every rank that shares a sample (WP grid x SP), ordered (wp_y, wp_x, sp); `sp_group`: the ranks that
         # share this rank's windows (Ulysses)
         self.wp_group = wp_group
         self.sp_group = sp_group
+        # `weight_group`: every rank that holds a replica of the weights (WP x SP x DP); gradients are reduced over it
+        self.weight_group = weight_group if weight_group is not None else wp_group
         self.wp_size = model_cfg.wp[0] * model_cfg.wp[1] * model_cfg.sp
         self.wp_rank = dist.get_rank(wp_group) if (self.wp_size > 1) else 0
         self.sp_rank = self.wp_rank % model_cfg.sp
@@ -58,10 +60,11 @@ class Trainer:
         torch.manual_seed(seed)   # identical initial weights on every rank
         self.model = (model or AerisModel(model_cfg)).to(self.device)
         # weight-group collectives: this library's peer-memory kernels (default on GPUs with > 1 rank) or NCCL
-        self.fused_dp = (self.wp_size > 1 and self.device.type == "cuda") if fused_dp is None else fused_dp
+        n_replicas = self.wp_size * dp_size
+        self.fused_dp = (n_replicas > 1 and self.device.type == "cuda") if fused_dp is None else fused_dp
         if self.fused_dp:
             from .fused_dp import FusedShardedOptimizer
-            self.opt = FusedShardedOptimizer(self.model, optim_cfg, wp_group, self.device, use_multicast)
+            self.opt = FusedShardedOptimizer(self.model, optim_cfg, self.weight_group, self.device, use_multicast)
         else:
             self.opt = FlatOptimizer(self.model, optim_cfg)
         self.grid = model_cfg.grid()
@@ -190,7 +193,7 @@ class Trainer:
             return
         if self.wp_size > 1 or self.dp_size > 1:
             for buf in self.opt.grad_buffers():
-                dist.all_reduce(buf, group=self.wp_group)
+                dist.all_reduce(buf, group=self.weight_group)
         nsq = self.opt.grad_norm_sq(scale) if self.ocfg.grad_clip else None
         self.opt.step(batch_img=gas * self.dp_size, grad_scale=scale, norm_sq=nsq)
         self._nsq = nsq

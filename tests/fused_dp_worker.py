@@ -45,6 +45,29 @@ def main():
         for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
             d = (p.float() - q.float()).abs().max().item()
             worst = max(worst, d / max(p.float().abs().max().item(), 1e-6))
+    if not use_mc:
+        # checkpoint round trip of the sharded optimizer: gathered into the per-stage file format by every rank, written
+        # by rank 0, loaded into a differently initialised trainer; weights and the next step must agree
+        import tempfile
+        from aeris_gb_b200.engine.checkpoint import load_stage_checkpoint, save_stage_checkpoint
+        box = [tempfile.mkdtemp() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        save_stage_checkpoint(box[0], b.model, b.opt, write=(rank == 0))
+        dist.barrier()
+        c = Trainer(cfg, ocfg, dcfg, dev, seed=999, wp_group=dist.group.WORLD, fused_dp=True, use_multicast=False)
+        assert load_stage_checkpoint(box[0], c.model, c.opt, dev)
+        c.seed, c.step_count = b.seed, b.step_count
+        for (n, p), (_, q) in zip(b.model.named_parameters(), c.model.named_parameters()):
+            assert torch.equal(p, q), n
+        x = torch.randn(2, hb, wb, 6, generator=g).pin_memory()
+        cc = torch.randn(2, hb, wb, 6, generator=g).pin_memory()
+        for t in (b, c):
+            t.nl_rng.manual_seed(777)
+        lb, lc = b.train_step(x, cc), c.train_step(x, cc)
+        assert abs(lb - lc) < 1e-4 * abs(lb), (lb, lc)
+        for (n, p), (_, q) in zip(b.model.named_parameters(), c.model.named_parameters()):
+            d = (p.float() - q.float()).abs().max().item()
+            worst = max(worst, d / max(p.float().abs().max().item(), 1e-6))
     L.check_status()
     flag = torch.tensor([worst], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MAX)
