@@ -5,8 +5,8 @@
 
 Same flow as the reference's Hydra main (src/aeris/train.py:66-358): bootstrap, seeds, dataset, channel wiring, engine,
 optimizer policy, warm-up probe, checkpoint load, data loader, main loop with TFLOP/s per GPU, periodic checkpoints.
-Overrides are ``key=value`` (dotted) like Hydra's. With ``model.PP = 1`` and ``model.SP = 1`` the single-node fused
-engine (:class:`Trainer`) runs the step; otherwise the pipeline engine (:class:`ParallelEngine`).
+Overrides are ``key=value`` (dotted) like Hydra's. With ``model.PP = 1`` the single-node fused engine (:class:`Trainer`:
+WP x SP x DP, every logical stage on every GPU) runs the step; otherwise the pipeline engine (:class:`ParallelEngine`).
 """
 from __future__ import annotations
 
@@ -90,10 +90,14 @@ def main(argv=None):
         except Exception:
             wandb = None
 
-    if PP == 1 and SP == 1:
-        groups = grid.build_groups(rank, kinds=("wp", "weight")) if world > 1 else {}
-        trainer = Trainer(mcfg, ocfg, dcfg, device, seed=int(cfg.seed), wp_group=groups.get("wp"),
-                          dp_size=grid.DP, dp_rank=c.dp, weight_group=groups.get("weight"))
+    if PP == 1 and (SP == 1 or device.type == "cuda"):
+        # one process group per sample (WP x SP ranks, ordered wp_y, wp_x, sp), its SP sub-groups, and the weight group
+        groups = grid.build_groups(rank, kinds=("replica", "sp", "weight")) if world > 1 else {}
+        mcfg.sp = SP
+        trainer = Trainer(mcfg, ocfg, dcfg, device, seed=int(cfg.seed), wp_group=groups.get("replica"),
+                          dp_size=grid.DP, dp_rank=c.dp, weight_group=groups.get("weight"),
+                          sp_group=groups.get("sp"))
+        trainer.timers.enabled = bool(cfg.trainer.get("report_timings", False))
         if cfg.model.get("load") and ckpt_dir:
             if load_stage_checkpoint(ckpt_dir, trainer.model, trainer.opt, device):
                 log0(f"loaded a checkpoint from {ckpt_dir} at {trainer.opt.cur_nimg} images")
@@ -110,6 +114,8 @@ def main(argv=None):
             slow = watchdog.observe(dt)
             log0(f"it {it} loss {loss:.5f} |g| {trainer.grad_norm():.4f} {dt:.3f} s/it {tf:.1f} TFLOP/s/GPU"
                  + (" SLOW STEP" if slow else ""))
+            if trainer.timers.enabled:
+                log0("   device ms: " + str({k: round(v, 1) for k, v in trainer.timers.resolve().items()}))
             if wandb:
                 wandb.log(wandb_payload(it, trainer.opt.cur_nimg, tf, dt, loss, trainer.grad_norm(), trainer.opt.last_lr))
             every = int(cfg.trainer.get("checkpoint_every", 100))

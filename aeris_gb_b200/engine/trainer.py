@@ -87,7 +87,9 @@ class Trainer:
         self.seed = seed
         self.step_count = 0
         self._io_tables = None
-        self.timers: dict[str, float] = {}
+        # device timers / NVTX ranges around the phases of a step (resolved lazily; enable with trainer.timers.enabled)
+        from ..utils.timers import DeviceTimers
+        self.timers = DeviceTimers(enabled=False)
         self.last_norm = 0.0
         self._sp_exchange = None
 
@@ -166,19 +168,23 @@ class Trainer:
         (standardised residual), cond_host: [B, H/wp_y, W/wp_x, C_cond] fp32; both pinned host tensors.
         Returns the loss averaged over the local batch (synchronises: the value is read back to the host)."""
         dev = self.device
-        x = target_host.to(dev, non_blocking=True)
-        c = cond_host.to(dev, non_blocking=True)
-        B = x.shape[0]
-        t = TF.sample_noise_level(B, self.dcfg.sigma_min, self.dcfg.sigma_max, self.dcfg.sigma_data,
-                                  generator=self.nl_rng, device=dev, law=self.dcfg.noise_law)
-        if self.fused_io:
-            loss = self.loss_images(x, c, t)
-        else:
-            x_tok, c_tok = self.block_to_tokens(x), self.block_to_tokens(c)
-            z = torch.randn(x_tok.shape, generator=self.rng, device=dev) * self.dcfg.sigma_data
-            loss = self.loss_tokens(x_tok, c_tok, t, z)
-        loss.backward()
-        self.reduce_and_step(B)
+        with self.timers.region("load"):
+            x = target_host.to(dev, non_blocking=True)
+            c = cond_host.to(dev, non_blocking=True)
+            B = x.shape[0]
+            t = TF.sample_noise_level(B, self.dcfg.sigma_min, self.dcfg.sigma_max, self.dcfg.sigma_data,
+                                      generator=self.nl_rng, device=dev, law=self.dcfg.noise_law)
+        with self.timers.region("fwd"):
+            if self.fused_io:
+                loss = self.loss_images(x, c, t)
+            else:
+                x_tok, c_tok = self.block_to_tokens(x), self.block_to_tokens(c)
+                z = torch.randn(x_tok.shape, generator=self.rng, device=dev) * self.dcfg.sigma_data
+                loss = self.loss_tokens(x_tok, c_tok, t, z)
+        with self.timers.region("bwd"):
+            loss.backward()
+        with self.timers.region("reduce_step"):
+            self.reduce_and_step(B)
         self.step_count += 1
         self.last_loss = loss.detach()
         return float(self.last_loss.item()) / B if read_loss else None
