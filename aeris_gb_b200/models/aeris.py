@@ -51,6 +51,7 @@ class AerisConfig:
     sp: int = 1                     # Ulysses sequence-parallel degree
     chunk_windows: int = 64
     shift_layers: str = "odd"       # which layers use the half-window shift: "odd" | "none"
+    oracle_checkpoint: bool = False  # PyTorch (oracle) path only: recompute every block in backward
 
     @property
     def n_blocks(self) -> int:
@@ -296,9 +297,13 @@ class SwinLayer(nn.Module):
                     from ..parallel.sequence import sp_window_attention
                     attn = lambda qkv, nw, nl, H, d: sp_window_attention(qkv, nw, nl, H, d, ctx.sp_group,
                                                                            O.window_attention)
-                x = O.block_forward(x, m, p, n_win_per_sample=ctx.grid.windows_per_rank, L=ctx.grid.n_local,
-                                    heads=cfg.heads, head_dim=cfg.head_dim, after_mod_norm=cfg.after_mod_norm,
-                                    eps=eps, attention=attn)
+                run = lambda xx, mm: O.block_forward(xx, mm, p, n_win_per_sample=ctx.grid.windows_per_rank,
+                                                     L=ctx.grid.n_local, heads=cfg.heads, head_dim=cfg.head_dim,
+                                                     after_mod_norm=cfg.after_mod_norm, eps=eps, attention=attn)
+                if cfg.oracle_checkpoint and torch.is_grad_enabled():
+                    x = torch.utils.checkpoint.checkpoint(run, x, m, use_reentrant=False)
+                else:
+                    x = run(x, m)
         return x
 
 

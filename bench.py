@@ -162,7 +162,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch-eager"],
+                    help="torch-eager: the same model through stock PyTorch ops (cuBLAS, SDPA) with per-block "
+                         "checkpointing: an informational same-math baseline, not the reference arm")
     ap.add_argument("--scale", default="full", choices=["full", "quarter", "tiny"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the number of Swin layers (development only)")
@@ -195,6 +197,10 @@ def main():
         group = dist.group.WORLD
 
     cfg = flagship_config(world, args.scale, args.sp)
+    eager = args.impl == "torch-eager"
+    if eager:
+        os.environ["AERIS_FORCE_ORACLE"] = "1"
+        cfg.oracle_checkpoint = True
     if args.layers:
         cfg.n_layers = args.layers
     if args.chunk_windows:
@@ -208,7 +214,8 @@ def main():
             g_ = dist.new_group(list(range(r0, r0 + args.sp)))
             if r0 <= rank < r0 + args.sp:
                 sp_group = g_
-    trainer = Trainer(cfg, OptimConfig(), DiffusionConfig(), dev, wp_group=group, sp_group=sp_group)
+    trainer = Trainer(cfg, OptimConfig(), DiffusionConfig(), dev, wp_group=group, sp_group=sp_group,
+                      **(dict(fused_io=False, fused_dp=False) if eager else {}))
     g = cfg.grid()
     hb, wb = cfg.img[0] // cfg.wp[0], cfg.img[1] // cfg.wp[1]
     gen = torch.Generator().manual_seed(100 + rank)
@@ -266,6 +273,7 @@ def main():
     flops = trainer.flops_per_step(B)
     if rank == 0:
         out = {
+            **({"impl": "torch-eager"} if eager else {}),
             "metric": "train samples/s (TrigFlow, 720x1440 Swin diffusion)", "value": B / (ms_dev / 1e3),
             "unit": "samples/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
