@@ -264,10 +264,12 @@ class SwinLayer(nn.Module):
             ]) for _ in range(cfg.sublayers)
         ])
 
-    def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext, regroup=None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext, regroup=None,
+                publish_out: bool = False) -> torch.Tensor:
         """``regroup = (src_shift, dst_shift)``: the stream arrives in the ``src`` window layout and this layer works
         in ``dst``. On the CUDA path the re-partition (with its halo exchange under WP) is fused into the first
-        block's modulate+norm kernel; the oracle path applies it as a separate gather."""
+        block's modulate+norm kernel; the oracle path applies it as a separate gather. ``publish_out``: the caller
+        re-partitions this layer's output next, so under WP the last block writes it into a peer-readable buffer."""
         cfg = self.cfg
         eps = cfg.eps(x.dtype)
         if regroup is not None and regroup[0] == regroup[1]:
@@ -284,8 +286,11 @@ class SwinLayer(nn.Module):
                 if j == 0 and regroup is not None:
                     rg = (ctx.table(regroup[0], regroup[1], x.device), ctx.table(regroup[1], regroup[0], x.device),
                           ctx.peer_fn)
+                alloc = None
+                if publish_out and j == len(self.modulelist) - 1:
+                    alloc = fused._pool_alloc(ctx.peer_fn)
                 x = fused.FusedBlock.apply(x, m, meta, n1.weight, attn.to_qkv.weight, attn.wo.weight, n2.weight,
-                                           ff.w1.weight, ff.w2.weight, rg)
+                                           ff.w1.weight, ff.w2.weight, rg, alloc)
             else:
                 m = mod(dt.to(mod.modulation[-1].weight.dtype))
                 if j == 0 and regroup is not None:
@@ -415,9 +420,11 @@ class AerisModel(nn.Module):
 
     def trunk(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
         cur = (0, 0)
+        n = len(self.layers)
         for i, layer in enumerate(self.layers):
             nxt = self.cfg.layer_shift(i)
-            x = layer(x, dt, ctx, regroup=(cur, nxt))
+            after = self.cfg.layer_shift(i + 1) if i + 1 < n else (0, 0)     # layout of whoever consumes the output
+            x = layer(x, dt, ctx, regroup=(cur, nxt), publish_out=(after != nxt))
             cur = nxt
         return ctx.regroup_unfused(x, cur, (0, 0))
 

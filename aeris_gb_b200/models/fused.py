@@ -294,25 +294,33 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
     return dx, dmod
 
 
+def _pool_alloc(peer_fn):
+    """The symmetric output-buffer allocator that belongs to a halo exchange's ``peer_fn`` (or None)."""
+    return getattr(getattr(peer_fn, "__self__", None), "output_buffer", None)
+
+
 class FusedBlock(torch.autograd.Function):
     """Autograd wrapper: saves only the block input; weight gradients go to ``param.main_grad`` (fp32) when the
     engine provides one, otherwise they are returned to autograd."""
 
     @staticmethod
-    def forward(ctx, x, mod, meta, wn1, wqkv, wo, wn2, w1, w2, regroup=None):
+    def forward(ctx, x, mod, meta, wn1, wqkv, wo, wn2, w1, w2, regroup=None, out_alloc=None):
         """``regroup = (table_fwd, table_bwd, peer_fn)`` fuses the preceding window re-partition into this block: the
         incoming stream ``x`` is in the previous layout (published to the WP peers when ``peer_fn`` is given) and the
-        first modulate+norm kernel gathers this block's rows from it."""
+        first modulate+norm kernel gathers this block's rows from it. ``out_alloc(rows, cols, dtype)``: where to put the
+        output when the caller knows that it will be re-partitioned next (a peer-readable buffer: no publish copy)."""
         ctx.meta = meta
         ctx.regroup = regroup
+        out = out_alloc(x.shape[0], x.shape[1], x.dtype) if out_alloc is not None else None
         if regroup is not None:
             table_fwd, _, peer_fn = regroup
             peers = peer_fn(x, "fwd") if peer_fn is not None else [x.data_ptr()]
             xg = torch.empty((table_fwd.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
-            y = block_forward(xg, mod.float(), meta, wn1, wqkv, wo, wn2, w1, w2, gather=(table_fwd, peers, x))
+            y = block_forward(xg, mod.float(), meta, wn1, wqkv, wo, wn2, w1, w2, out=out,
+                              gather=(table_fwd, peers, x))
             x = xg
         else:
-            y = block_forward(x, mod.float(), meta, wn1, wqkv, wo, wn2, w1, w2)
+            y = block_forward(x, mod.float(), meta, wn1, wqkv, wo, wn2, w1, w2, out=out)
         ctx.save_for_backward(x, mod, wn1, wqkv, wo, wn2, w1, w2)
         return y
 
@@ -334,12 +342,16 @@ class FusedBlock(torch.autograd.Function):
         if ctx.regroup is not None:
             _, table_bwd, peer_fn = ctx.regroup
             peers = peer_fn(dx, "bwd") if peer_fn is not None else [dx.data_ptr()]
-            back = torch.empty((table_bwd.numel(), dx.shape[1]), dtype=dx.dtype, device=dx.device)
+            # the gathered gradient is the next (earlier) layer's dy, which that layer turns into its dx in place and
+            # publishes in turn: put it into the other peer-readable buffer straight away
+            alloc = _pool_alloc(peer_fn)
+            back = (alloc(table_bwd.numel(), dx.shape[1], dx.dtype) if alloc is not None else
+                    torch.empty((table_bwd.numel(), dx.shape[1]), dtype=dx.dtype, device=dx.device))
             E.gather_rows(table_bwd, peers, back)
             dx = back
         out = [ret[k].to(params[k].dtype) if ret[k] is not None else None
                for k in ("n1", "to_qkv", "wo", "n2", "w1", "w2")]
-        return (dx, dmod.to(mod.dtype), None, *out, None)
+        return (dx, dmod.to(mod.dtype), None, *out, None, None)
 
 
 class GemvLinearFn(torch.autograd.Function):
@@ -401,7 +413,9 @@ class Regroup(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         dy = dy.contiguous()
-        out = torch.empty((ctx.table_bwd.numel(), dy.shape[1]), dtype=dy.dtype, device=dy.device)
         peers = ctx.peer_fn(dy, "bwd") if ctx.peer_fn is not None else [dy.data_ptr()]
+        alloc = _pool_alloc(ctx.peer_fn)      # the result is the previous layer's dy: see FusedBlock.backward
+        out = (alloc(ctx.table_bwd.numel(), dy.shape[1], dy.dtype) if alloc is not None else
+               torch.empty((ctx.table_bwd.numel(), dy.shape[1]), dtype=dy.dtype, device=dy.device))
         E.gather_rows(ctx.table_bwd, peers, out)
         return out, None, None, None

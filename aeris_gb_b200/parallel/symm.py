@@ -7,6 +7,12 @@ kernel pulls the rows it needs straight from the owners' buffers (local HBM or p
 done by the same row-gather kernels that do the local re-partition, so no send/recv buffers, packing kernels or
 rolls exist (reference: blocking send/recv of three strips + ``torch.roll`` per shift,
 src/aeris_wp_inference/model.py:72-114).
+
+Producers that know their output will be re-partitioned next (the last block of a Swin layer, the gradient gather of
+the layer after it) write it straight into one of two alternating symmetric buffers (:meth:`output_buffer`); publishing
+such a tensor needs no copy and a single barrier. Two buffers suffice: a rank can only overwrite buffer b two
+re-partitions later, and it passes the barrier of the re-partition in between only after every peer has finished
+reading buffer b.
 """
 from __future__ import annotations
 
@@ -23,6 +29,10 @@ class HaloExchange:
         self._buf = None
         self._hdl = None
         self._flag = torch.zeros(1, device=self.device)
+        self._pool: list[torch.Tensor] = []       # two alternating symmetric output buffers
+        self._pool_ptrs: list[list[int]] = []
+        self._pool_hdl: list = []
+        self._turn = 0
 
     def _ensure(self, numel: int, dtype: torch.dtype):
         if self._buf is not None and self._buf.numel() >= numel and self._buf.dtype == dtype:
@@ -36,9 +46,39 @@ class HaloExchange:
         # stream-ordered rank barrier (tiny NCCL all-reduce on the current stream)
         dist.all_reduce(self._flag, group=self.group)
 
+    def output_buffer(self, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """``[rows, cols]`` tensor inside the symmetric buffer whose turn it is (collective on first use and whenever a
+        larger size is asked for: every rank asks for the same sizes in the same order)."""
+        numel = rows * cols
+        if not self._pool or self._pool[0].numel() < numel or self._pool[0].dtype != dtype:
+            import torch.distributed._symmetric_memory as symm_mem
+            self._pool, self._pool_ptrs, self._pool_hdl = [], [], []
+            for _ in range(2):
+                t = symm_mem.empty(numel, dtype=dtype, device=self.device)
+                hdl = symm_mem.rendezvous(t, self.group)
+                self._pool.append(t)
+                self._pool_hdl.append(hdl)
+                self._pool_ptrs.append([int(p) for p in hdl.buffer_ptrs])
+        self._turn ^= 1
+        return self._pool[self._turn][:numel].view(rows, cols)
+
+    def _pool_slot(self, src: torch.Tensor):
+        p = src.data_ptr()
+        for b, t in enumerate(self._pool):
+            lo = t.data_ptr()
+            if lo <= p and p + src.numel() * src.element_size() <= lo + t.numel() * t.element_size():
+                return b, p - lo
+        return None
+
     def peer_fn(self, src: torch.Tensor, direction: str) -> list[int]:
-        """Publishes ``src`` (this rank's rows) and returns every rank's staging-buffer address. The caller launches
-        its gather right after; :meth:`release` must follow it before the next publish."""
+        """Publishes ``src`` (this rank's rows) and returns, for every rank, the address of its copy of those rows. The
+        caller launches its gather right after. A ``src`` that already lives in one of the :meth:`output_buffer`s is
+        published in place."""
+        slot = self._pool_slot(src) if src.is_contiguous() else None
+        if slot is not None:
+            b, off = slot
+            self._barrier()                  # every rank has finished writing its rows
+            return [p + off for p in self._pool_ptrs[b]]
         self._ensure(src.numel(), src.dtype)
         self._barrier()                      # peers finished reading the previous contents
         self._buf[:src.numel()].view_as(src).copy_(src)
