@@ -103,7 +103,9 @@ def bench_halo(a, dev, res):
     res["halo_fraction"] = frac
     res["halo_roofline_ms"] = max(hbm / (a.hbm_gbs * 1e6), link / (a.link_gbs * 1e6))
     res["halo_frac_of_roofline"] = res["halo_roofline_ms"] / res["halo_modnorm_gather_ms"]
-    res["halo_publish_copy_ms"] = _time(lambda: halo.peer_fn(x, "fwd"), a.iters)
+    res["halo_publish_copy_ms"] = _time(lambda: halo.peer_fn(x, "fwd"), a.iters)      # staged: copy + two barriers
+    xp = halo.output_buffer(rows, D, torch.bfloat16)
+    res["halo_publish_in_place_ms"] = _time(lambda: halo.peer_fn(xp, "fwd"), a.iters)   # producer wrote it there: one barrier
 
 
 def bench_dp(a, dev, res):
