@@ -52,6 +52,8 @@ class AerisConfig:
     chunk_windows: int = 64
     shift_layers: str = "odd"       # which layers use the half-window shift: "odd" | "none"
     oracle_checkpoint: bool = False  # PyTorch (oracle) path only: recompute every block in backward
+    use_rope: bool = False          # axial 2-D rotary embedding on q, k inside every window (the reference's is inert)
+    rope_base: float = 10_000.0
 
     @property
     def n_blocks(self) -> int:
@@ -94,6 +96,16 @@ class StreamContext:
         self.rank = rank
         self.peer_fn = peer_fn        # callable(tensor, direction) -> list of peer base addresses (WP) or None
         self._tables: dict = {}
+
+    def rope(self, device):
+        """(cos, sin) of the 2-D rotary embedding for one window, or None when the model does not use it."""
+        if not self.cfg.use_rope:
+            return None
+        key = ("rope", str(device))
+        if key not in self._tables:
+            self._tables[key] = O.rope_2d_cache(self.cfg.window[0], self.cfg.window[1], self.cfg.head_dim,
+                                                self.cfg.rope_base, device)
+        return self._tables[key]
 
     def table(self, src_shift, dst_shift, device) -> torch.Tensor:
         key = (src_shift, dst_shift, str(device))
@@ -281,7 +293,8 @@ class SwinLayer(nn.Module):
                 m = fused.modulation(mod.modulation, dt)
                 meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.n_local, cfg.heads, cfg.head_dim,
                                        E.MODE_MOD_THEN_NORM if cfg.after_mod_norm else E.MODE_NORM_THEN_MOD,
-                                       eps, cfg.chunk_windows, sp=ctx.sp_exchange if ctx.grid.sp > 1 else None)
+                                       eps, cfg.chunk_windows, sp=ctx.sp_exchange if ctx.grid.sp > 1 else None,
+                                       rope=ctx.rope(x.device))
                 rg = None
                 if j == 0 and regroup is not None:
                     rg = (ctx.table(regroup[0], regroup[1], x.device), ctx.table(regroup[1], regroup[0], x.device),
@@ -297,11 +310,13 @@ class SwinLayer(nn.Module):
                     x = ctx.regroup_unfused(x, regroup[0], regroup[1])
                 p = {"n1": n1.weight, "to_qkv": attn.to_qkv.weight, "wo": attn.wo.weight, "n2": n2.weight,
                      "w1": ff.w1.weight, "w2": ff.w2.weight}
-                attn = None
+                rope = ctx.rope(x.device)
+                inner = (lambda q_, nw, nl, H, d: O.window_attention(q_, nw, nl, H, d, rope=rope)) if rope else None
+                attn = inner
                 if ctx.sp_group is not None and ctx.grid.sp > 1:
                     from ..parallel.sequence import sp_window_attention
                     attn = lambda qkv, nw, nl, H, d: sp_window_attention(qkv, nw, nl, H, d, ctx.sp_group,
-                                                                           O.window_attention)
+                                                                           inner or O.window_attention)
                 run = lambda xx, mm: O.block_forward(xx, mm, p, n_win_per_sample=ctx.grid.windows_per_rank,
                                                      L=ctx.grid.n_local, heads=cfg.heads, head_dim=cfg.head_dim,
                                                      after_mod_norm=cfg.after_mod_norm, eps=eps, attention=attn)

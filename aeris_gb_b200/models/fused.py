@@ -30,6 +30,7 @@ class BlockMeta:
     eps: float
     chunk_windows: int = 64
     sp: "SPExchange | None" = None     # Ulysses sequence parallelism: L is then the LOCAL token count of a window
+    rope: tuple | None = None          # (cos, sin) [L, head_dim / 2]: optional 2-D rotary embedding of q and k
 
 
 class Workspace:
@@ -105,6 +106,18 @@ def _scatter_heads(a: torch.Tensor, w: torch.Tensor, sp: "SPExchange", peers: li
                                            sp.sp, sp.rank, n_local, L, sec_w, _l.ptr(_l.status_word()),
                                            _l.stream_ptr())
     _l.check(rc, "aeris_gemm_scatter_heads")
+
+
+def _rope_qk_(qkv: torch.Tensor, meta: BlockMeta, nw: int, inverse: bool = False) -> None:
+    """Rotates the q and k sections of a chunk's fused qkv tensor in place (optional feature, PyTorch element-wise
+    ops; ``inverse`` turns gradients with respect to the rotated q, k into gradients with respect to the projections)."""
+    from . import oracle as O
+    assert meta.sp is None, "the rotary embedding is not combined with sequence parallelism"
+    cos, sin = meta.rope
+    v = qkv.view(nw, meta.L, 3, meta.heads, meta.head_dim)
+    for i in (0, 1):
+        x = v[:, :, i].permute(0, 2, 1, 3)                              # [nw, H, L, d]
+        v[:, :, i] = O.apply_rope_2d(x, cos, sin, inverse).permute(0, 2, 1, 3)
 
 
 def _chunks(meta: BlockMeta):
@@ -201,6 +214,8 @@ def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv
                 E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h[:n])
             if meta.sp is None:
                 G.gemm(h[:n], wqkv, out=qkv[:n])
+                if meta.rope is not None:
+                    _rope_qk_(qkv[:n], meta, nw)
                 A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n],
                            lse=lse[:n * meta.heads].view(nw, meta.heads, meta.L))
                 oc = o[:n]
@@ -260,6 +275,8 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
             E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h1[:n])
             if meta.sp is None:
                 G.gemm(h1[:n], wqkv, out=qkv[:n])
+                if meta.rope is not None:
+                    _rope_qk_(qkv[:n], meta, nw)
                 A.attn_fwd(qkv[:n], nw, meta.L, meta.heads, meta.head_dim, out=o[:n], lse=lse_c)
                 oc = o[:n]
             else:
@@ -281,6 +298,8 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
                 G.gemm(dx1[:n], wog, b_t=True, out=d_o[:n])                            # do = (dx1 * g1) @ wo
                 A.attn_bwd(qkv[:n], o[:n], d_o[:n], lse_c, nw, meta.L, meta.heads, meta.head_dim, dqkv=dqkv[:n],
                            delta=delta[:n * meta.heads].view(nw, meta.heads, meta.L))
+                if meta.rope is not None:
+                    _rope_qk_(dqkv[:n], meta, nw, inverse=True)
                 dq_c = dqkv[:n]
             else:
                 dq_c = _sp_attention_bwd(meta, dx1[:n], wog, nw, sp_state)

@@ -74,10 +74,35 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
 
 
-def window_attention(qkv: torch.Tensor, n_win: int, L: int, heads: int, head_dim: int) -> torch.Tensor:
+def rope_2d_cache(ws_y: int, ws_x: int, head_dim: int, base: float = 10_000.0, device=None):
+    """(cos, sin), each ``[ws_y * ws_x, head_dim / 2]``, of the axial 2-D rotary embedding of
+    parallel_swin.py:158-218: with ``rope_dim = head_dim / 2`` frequencies ``theta_j = base^(-2j / rope_dim)``, the first
+    half of a head's (even, odd) channel pairs rotates by ``x * theta``, the second half by ``y * theta`` (x, y: column
+    and row of the token inside its window)."""
+    rope_dim = head_dim // 2
+    theta = 1.0 / (base ** (torch.arange(0, rope_dim, 2, device=device)[: rope_dim // 2].float() / rope_dim))
+    idx = torch.arange(ws_y * ws_x, dtype=torch.float32, device=device)
+    ang = torch.cat([torch.outer(idx % ws_x, theta), torch.outer(torch.div(idx, ws_x, rounding_mode="floor"), theta)], -1)
+    return ang.cos(), ang.sin()
+
+
+def apply_rope_2d(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+    """Rotates the (2i, 2i+1) channel pairs of ``x [..., L, d]`` by the cached angles (``inverse``: by their negatives,
+    which is also the transpose of the rotation, i.e. what its backward pass applies to the gradient)."""
+    xf = x.float().reshape(*x.shape[:-1], -1, 2)
+    s = -sin if inverse else sin
+    out = torch.stack([xf[..., 0] * cos - xf[..., 1] * s, xf[..., 1] * cos + xf[..., 0] * s], dim=-1)
+    return out.flatten(-2).to(x.dtype)
+
+
+def window_attention(qkv: torch.Tensor, n_win: int, L: int, heads: int, head_dim: int, rope=None) -> torch.Tensor:
     """softmax(q k^T / sqrt(d)) v per window and head, no mask (parallel_swin.py:257-258). qkv: [n_win*L, 3*h*d]
-    with columns ordered (q|k|v, head, d) as produced by ``to_qkv`` (model.py:300)."""
+    with columns ordered (q|k|v, head, d) as produced by ``to_qkv`` (model.py:300). ``rope = (cos, sin)`` applies the
+    2-D rotary embedding to q and k first (the reference computes it and then attends on the un-rotated tensors,
+    parallel_swin.py:292-294, so parity with it needs ``rope=None``)."""
     q, k, v = qkv.view(n_win, L, 3, heads, head_dim).permute(2, 0, 3, 1, 4)
+    if rope is not None:
+        q, k = apply_rope_2d(q, *rope), apply_rope_2d(k, *rope)
     o = F.scaled_dot_product_attention(q, k, v, is_causal=False)
     return o.permute(0, 2, 1, 3).reshape(n_win * L, heads * head_dim)
 

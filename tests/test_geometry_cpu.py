@@ -53,3 +53,24 @@ def test_gather_tables_are_permutations_of_the_other_layout():
         assert torch.equal(back[r], src[r])
     assert 0.0 < LY.halo_fraction(grid) < 0.5
     assert np.isclose(LY.halo_fraction(LY.Grid(32, 64, 8, 8)), 0.0)
+
+
+def test_rope_2d_is_a_relative_rotation():
+    """Rotating q at position a and k at position b leaves q.k a function of (a - b) per axis, and the inverse flag
+    undoes the rotation."""
+    from aeris_gb_b200.models import oracle as O
+    ws_y, ws_x, d = 4, 6, 16
+    cos, sin = O.rope_2d_cache(ws_y, ws_x, d)
+    assert cos.shape == (ws_y * ws_x, d // 2)
+    g = torch.Generator().manual_seed(0)
+    q, k = torch.randn(d, generator=g), torch.randn(d, generator=g)
+    L = ws_y * ws_x
+    Q = O.apply_rope_2d(q.expand(L, d), cos, sin)
+    K = O.apply_rope_2d(k.expand(L, d), cos, sin)
+    S = Q @ K.t()
+    pos = lambda y, x: y * ws_x + x
+    assert torch.allclose(S[pos(1, 2), pos(0, 1)], S[pos(3, 5), pos(2, 4)], atol=1e-5)     # same offset (1, 1)
+    assert torch.allclose(S[pos(0, 0), pos(0, 0)], q @ k, atol=1e-5)
+    assert not torch.allclose(S[pos(1, 2), pos(0, 1)], S[pos(1, 2), pos(0, 0)], atol=1e-4)
+    x = torch.randn(2, 3, L, d, generator=g)
+    assert torch.allclose(O.apply_rope_2d(O.apply_rope_2d(x, cos, sin), cos, sin, inverse=True), x, atol=1e-5)

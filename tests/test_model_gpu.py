@@ -51,3 +51,41 @@ def test_fused_model_matches_oracle(after_mod_norm):
             continue
         assert a is not None, n
         assert rel_err(a, b) < 8e-2, (n, rel_err(a, b))
+
+
+def test_fused_model_with_rope_matches_oracle():
+    """Optional 2-D rotary embedding: the CUDA path (rotation applied to the qkv chunks, inverse rotation of their
+    gradients) against the PyTorch formulation."""
+    from aeris_gb_b200.models.aeris import AerisModel
+    torch.manual_seed(2)
+    cfg = _small_cfg()
+    cfg.use_rope = True
+    model = AerisModel(cfg).cuda()
+    for n, p in model.named_parameters():
+        if "modulation" in n and p.dim() == 2:
+            torch.nn.init.normal_(p, std=0.05)
+    x = torch.randn(2, 32, 64, cfg.in_channels, device="cuda")
+    t = torch.tensor([0.3, 1.2], device="cuda")
+    params = [p for p in model.parameters() if p.requires_grad]
+
+    def run(force_oracle):
+        os.environ["AERIS_FORCE_ORACLE"] = "1" if force_oracle else "0"
+        for p in params:
+            p.grad = None
+        y = model(x, t)
+        (y * torch.linspace(-1, 1, y.numel(), device="cuda").view_as(y)).sum().backward()
+        return y.detach(), [p.grad.clone() if p.grad is not None else None for p in params]
+
+    try:
+        y0, g0 = run(True)
+        y1, g1 = run(False)
+        cfg.use_rope = False
+        y2, _ = run(True)
+    finally:
+        os.environ.pop("AERIS_FORCE_ORACLE", None)
+    assert rel_err(y1, y0) < 3e-2
+    assert rel_err(y2, y0) > 1e-3          # the embedding does change the result
+    for a, b in zip(g1, g0):
+        if b is None or b.float().norm() == 0:
+            continue
+        assert rel_err(a, b) < 8e-2
