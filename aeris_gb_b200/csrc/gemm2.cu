@@ -318,6 +318,12 @@ extern "C" int aeris_gemm_bf16_2cta(const void* A, const void* B, void* C, int M
   p.gate = gate; p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : M;
   p.aux = reinterpret_cast<__nv_bfloat16*>(aux); p.ld_aux = ld_aux;
   p.k_splits = k_splits; p.status = status; p.swiglu_f = swiglu_f;
+  {
+    // bf16-output epilogues write through the shared-memory stage as 256-byte row segments (measured 1-13 % faster
+    // than one 16-byte piece per row and instruction); AERIS_GEMM_STAGED_OUT=0 selects the direct stores
+    static const int staged = [] { const char* e = getenv("AERIS_GEMM_STAGED_OUT"); return e ? atoi(e) : 1; }();
+    p.staged_out = staged;
+  }
   if (swiglu_fwd) { p.b_tile_stride = G2_BN / 2; p.b_half_off = swiglu_f; }
   else            { p.b_tile_stride = G2_BN;     p.b_half_off = G2_BN / 2; }
   CUtensorMap ta, tb;

@@ -44,6 +44,7 @@ struct GemmParams {
   const unsigned* ag_count;
   unsigned ag_expect;
   int ag_world, ag_rank, ag_rows;
+  int staged_out;   // EPI_STORE / EPI_GATE_RESID: move rows through the warp's shared-memory stage (coalesced global I/O)
   int* status;
 };
 
@@ -70,6 +71,23 @@ __device__ __forceinline__ void push_stage_flush(uint8_t* stage, int lane, __nv_
     const unsigned long long d = __shfl_sync(0xffffffffu, mine, r);
     const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4));
     if (d) *reinterpret_cast<uint4*>(d + ch * 16) = v;
+  }
+  __syncwarp();
+}
+
+// Same, but the staged 128 columns are two 64-column halves with different destinations (two 128-byte segments per row).
+__device__ __forceinline__ void push_stage_flush2(uint8_t* stage, int lane, __nv_bfloat16* dst_a, __nv_bfloat16* dst_b) {
+  __syncwarp();
+  const unsigned long long ma = reinterpret_cast<unsigned long long>(dst_a);
+  const unsigned long long mb = reinterpret_cast<unsigned long long>(dst_b);
+  const int ch = lane & 15;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int r = 2 * i + (lane >> 4);
+    const unsigned long long da = __shfl_sync(0xffffffffu, ma, r), db = __shfl_sync(0xffffffffu, mb, r);
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4));
+    const unsigned long long d = (ch < 8) ? da + ch * 16 : db + (ch - 8) * 16;
+    if (da) *reinterpret_cast<uint4*>(d) = v;
   }
   __syncwarp();
 }
@@ -156,12 +174,58 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
             ou[4 * i + j] = pack_bf16x2(d0 * si0, d1 * si1);
           }
         }
+        if (stage != nullptr && p.staged_out) {
+          // 64 d(gate) columns and the matching 64 d(up) columns share one stage group
+          push_stage_put(stage, lane, (c & 32), og);
+          push_stage_put(stage, lane, 64 + (c & 32), ou);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(og[4 * i], og[4 * i + 1], og[4 * i + 2], og[4 * i + 3]);
-          *reinterpret_cast<uint4*>(dst + p.swiglu_f + c + 8 * i) =
-              make_uint4(ou[4 * i], ou[4 * i + 1], ou[4 * i + 2], ou[4 * i + 3]);
+          for (int i = 0; i < 4; ++i) {
+            *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(og[4 * i], og[4 * i + 1], og[4 * i + 2], og[4 * i + 3]);
+            *reinterpret_cast<uint4*>(dst + p.swiglu_f + c + 8 * i) =
+                make_uint4(ou[4 * i], ou[4 * i + 1], ou[4 * i + 2], ou[4 * i + 3]);
+          }
         }
+      }
+      if (stage != nullptr && p.staged_out && (c & 32))
+        push_stage_flush2(stage, lane, row_ok ? dst + (c - 32) : nullptr, row_ok ? dst + p.swiglu_f + (c - 32) : nullptr);
+    }
+  } else if ((p.epi == EPI_SWIGLU || p.epi == EPI_SWIGLU_BOTH) && stage != nullptr && p.staged_out && BN == 256) {
+    // staged stores: the 128 activation columns of the tile are one stage group; with EPI_SWIGLU_BOTH the raw gate
+    // and up columns follow as two more groups (second pass over the accumulator in TMEM)
+    constexpr int H = BN / 2;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * H;
+#pragma unroll 1
+    for (int c = 0; c < H; c += 32) {
+      uint32_t g[32], u[32];
+      tmem_ld32(taddr + c, g);
+      tmem_ld32(taddr + H + c, u);
+      tmem_wait_ld();
+      uint32_t o[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+        const float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+        const float s0 = g0 / (1.f + __expf(-g0)), s1 = g1 / (1.f + __expf(-g1));
+        o[i] = pack_bf16x2(s0 * u0, s1 * u1);
+      }
+      push_stage_put(stage, lane, c, o);
+    }
+    push_stage_flush(stage, lane, row_ok ? out : nullptr);
+    if (p.epi == EPI_SWIGLU_BOTH) {
+      __nv_bfloat16* raw = p.aux + static_cast<size_t>(row) * p.ld_aux + tn * H;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+        for (int c = 0; c < H; c += 32) {
+          uint32_t v[32], o[16];
+          tmem_ld32(taddr + half * H + c, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+          push_stage_put(stage, lane, c, o);
+        }
+        push_stage_flush(stage, lane, row_ok ? raw + half * p.swiglu_f : nullptr);
       }
     }
   } else if (p.epi == EPI_SWIGLU || p.epi == EPI_SWIGLU_BOTH) {
@@ -237,6 +301,47 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
           }
         }
       }
+    }
+  } else if (stage != nullptr && p.staged_out && p.aux == nullptr) {
+    // EPI_STORE / EPI_GATE_RESID with coalesced stores: every lane combines its own row (the residual is read
+    // directly: staging it too was measured slower), the packed results of a 128-column group go through the warp's
+    // stage and leave as 256-byte row segments.
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * BN;
+    const bool gated = (p.epi == EPI_GATE_RESID) && row_ok;
+    const __nv_bfloat16* res = p.resid ? p.resid + static_cast<size_t>(row) * p.ldr + tn * BN : nullptr;
+    const float* gate = nullptr;
+    if (gated) gate = p.gate + static_cast<size_t>(row / p.rows_per_gate) * p.N + tn * BN;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c, v);
+      uint4 r4[4];
+      if (gated) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r4[i] = reinterpret_cast<const uint4*>(res + c)[i];
+      }
+      tmem_wait_ld();
+      uint32_t o[16];
+      if (gated) {
+        const float4* gsrc = reinterpret_cast<const float4*>(gate + c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t rr[4] = {r4[i].x, r4[i].y, r4[i].z, r4[i].w};
+          const float4 ga = gsrc[2 * i], gb = gsrc[2 * i + 1];
+          const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 r2 = unpack_bf16x2(rr[j]);
+            const float a0 = __uint_as_float(v[8 * i + 2 * j]), a1 = __uint_as_float(v[8 * i + 2 * j + 1]);
+            o[4 * i + j] = pack_bf16x2(fmaf(gg[2 * j], a0, r2.x), fmaf(gg[2 * j + 1], a1, r2.y));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+      }
+      push_stage_put(stage, lane, c & 127, o);
+      if ((c & 127) == 96) push_stage_flush(stage, lane, row_ok ? out + (c - 96) : nullptr);
     }
   } else {
     // EPI_STORE / EPI_GATE_RESID : bf16 output
