@@ -28,7 +28,7 @@ def reference_arm(args):
     # interpreter and from the offline wheelhouse, it imports deepspeed/ezpz/mpi4py/hydra/h5py (all absent), its
     # engine asserts SP == 12 with >= 4 pipeline stages (>= 48 ranks) and calls torch.xpu.* unconditionally.
     print(json.dumps({"impl": "reference", "unavailable":
-                      "pip install of /root/reference fails offline (build backend hatchling missing; deps deepspeed, "
+                      "pip install of the reference fails offline (build backend hatchling missing; deps deepspeed, "
                       "ezpz, mpi4py, hydra, h5py missing) and its engine needs SP=12 x PP>=4 (>=48 ranks) on torch.xpu"}))
     return 0
 
