@@ -323,6 +323,8 @@ extern "C" int aeris_gemm_bf16_2cta(const void* A, const void* B, void* C, int M
     // than one 16-byte piece per row and instruction); AERIS_GEMM_STAGED_OUT=0 selects the direct stores
     static const int staged = [] { const char* e = getenv("AERIS_GEMM_STAGED_OUT"); return e ? atoi(e) : 1; }();
     p.staged_out = staged;
+    static const int staged_red = [] { const char* e = getenv("AERIS_GEMM_STAGED_RED"); return e ? atoi(e) : 0; }();
+    p.staged_red = staged_red;
   }
   if (swiglu_fwd) { p.b_tile_stride = G2_BN / 2; p.b_half_off = swiglu_f; }
   else            { p.b_tile_stride = G2_BN;     p.b_half_off = G2_BN / 2; }

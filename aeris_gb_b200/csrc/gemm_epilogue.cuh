@@ -44,7 +44,8 @@ struct GemmParams {
   const unsigned* ag_count;
   unsigned ag_expect;
   int ag_world, ag_rank, ag_rows;
-  int staged_out;   // EPI_STORE / EPI_GATE_RESID: move rows through the warp's shared-memory stage (coalesced global I/O)
+  int staged_out;   // bf16-output epilogues: move rows through the warp's shared-memory stage (coalesced global stores)
+  int staged_red;   // split-K fp32 accumulation: stage 32 rows x 64 columns and issue the reductions row-contiguously
   int* status;
 };
 
@@ -88,6 +89,31 @@ __device__ __forceinline__ void push_stage_flush2(uint8_t* stage, int lane, __nv
     const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4));
     const unsigned long long d = (ch < 8) ? da + ch * 16 : db + (ch - 8) * 16;
     if (da) *reinterpret_cast<uint4*>(d) = v;
+  }
+  __syncwarp();
+}
+
+// fp32 variant for the split-K reduction: the stage holds 32 rows x 64 fp32 columns; every flush instruction adds two
+// 256-byte row segments to global memory (red.add), so the atomics of one instruction fall into 16 sectors, not 32.
+__device__ __forceinline__ void push_stage_put_f32(uint8_t* stage, int lane, int col, const uint32_t (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    *reinterpret_cast<uint4*>(stage + lane * 256 + (((col / 4 + i) ^ (lane & 15)) << 4)) =
+        make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+__device__ __forceinline__ void push_stage_flush_red(uint8_t* stage, int lane, float* dst_row) {
+  __syncwarp();
+  const unsigned long long mine = reinterpret_cast<unsigned long long>(dst_row);
+  const int ch = lane & 15;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int r = 2 * i + (lane >> 4);
+    const unsigned long long d = __shfl_sync(0xffffffffu, mine, r);
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4));
+    if (d)
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d + ch * 16), "f"(__uint_as_float(v.x)),
+                   "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                   : "memory");
   }
   __syncwarp();
 }
@@ -265,6 +291,17 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
 #pragma unroll
         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
       }
+    }
+  } else if (p.epi == EPI_ACC_F32 && p.k_splits > 1 && stage != nullptr && p.staged_red) {
+    float* out = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * BN;
+    const bool live = row_ok && !kempty;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c, v);
+      tmem_wait_ld();
+      push_stage_put_f32(stage, lane, c & 32, v);
+      if (c & 32) push_stage_flush_red(stage, lane, live ? out + (c - 32) : nullptr);
     }
   } else if (p.epi == EPI_ACC_F32 || p.epi == EPI_STORE_F32) {
     float* out = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + tn * BN;

@@ -95,7 +95,7 @@ class ParallelEngine:
         halo = None
         if grid.WP_Y * grid.WP_X * grid.SP > 1 and self.device.type == "cuda":
             from ..parallel.symm import HaloExchange
-            halo = HaloExchange(self.groups["replica"], self.device)
+            halo = HaloExchange(self.groups["replica"], self.device, pool_gradients=False)
         self.ctx = StreamContext(model_cfg, 1, self.replica_rank, halo.peer_fn if halo else None,
                                  wp_group=self.groups.get("replica"), sp_group=self.groups.get("sp"))
         self.tokens = self.ctx.grid.tokens_per_rank

@@ -313,9 +313,9 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
     return dx, dmod
 
 
-def _pool_alloc(peer_fn):
-    """The symmetric output-buffer allocator that belongs to a halo exchange's ``peer_fn`` (or None)."""
-    return getattr(getattr(peer_fn, "__self__", None), "output_buffer", None)
+def _pool_alloc(peer_fn, gradient: bool = False):
+    """The peer-readable buffer allocator that belongs to a halo exchange's ``peer_fn`` (or None)."""
+    return getattr(getattr(peer_fn, "__self__", None), "gradient_buffer" if gradient else "output_buffer", None)
 
 
 class FusedBlock(torch.autograd.Function):
@@ -363,7 +363,7 @@ class FusedBlock(torch.autograd.Function):
             peers = peer_fn(dx, "bwd") if peer_fn is not None else [dx.data_ptr()]
             # the gathered gradient is the next (earlier) layer's dy, which that layer turns into its dx in place and
             # publishes in turn: put it into the other peer-readable buffer straight away
-            alloc = _pool_alloc(peer_fn)
+            alloc = _pool_alloc(peer_fn, gradient=True)
             back = (alloc(table_bwd.numel(), dx.shape[1], dx.dtype) if alloc is not None else
                     torch.empty((table_bwd.numel(), dx.shape[1]), dtype=dx.dtype, device=dx.device))
             E.gather_rows(table_bwd, peers, back)
@@ -433,7 +433,7 @@ class Regroup(torch.autograd.Function):
     def backward(ctx, dy):
         dy = dy.contiguous()
         peers = ctx.peer_fn(dy, "bwd") if ctx.peer_fn is not None else [dy.data_ptr()]
-        alloc = _pool_alloc(ctx.peer_fn)      # the result is the previous layer's dy: see FusedBlock.backward
+        alloc = _pool_alloc(ctx.peer_fn, gradient=True)      # the previous layer's dy: see FusedBlock.backward
         out = (alloc(ctx.table_bwd.numel(), dy.shape[1], dy.dtype) if alloc is not None else
                torch.empty((ctx.table_bwd.numel(), dy.shape[1]), dtype=dy.dtype, device=dy.device))
         E.gather_rows(ctx.table_bwd, peers, out)

@@ -21,7 +21,10 @@ import torch.distributed as dist
 
 
 class HaloExchange:
-    def __init__(self, group, device):
+    def __init__(self, group, device, pool_gradients: bool = True):
+        # pool_gradients=False: gathered gradients get ordinary buffers (for engines that hand them to asynchronous
+        # sends, which must not see the buffer recycled two re-partitions later)
+        self.pool_gradients = pool_gradients
         self.group = group
         self.device = torch.device(device)
         self.world = dist.get_world_size(group)
@@ -61,6 +64,12 @@ class HaloExchange:
                 self._pool_ptrs.append([int(p) for p in hdl.buffer_ptrs])
         self._turn ^= 1
         return self._pool[self._turn][:numel].view(rows, cols)
+
+    def gradient_buffer(self, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """Where a gathered gradient goes: a pooled peer-readable buffer, or an ordinary one (see ``pool_gradients``)."""
+        if self.pool_gradients:
+            return self.output_buffer(rows, cols, dtype)
+        return torch.empty((rows, cols), dtype=dtype, device=self.device)
 
     def _pool_slot(self, src: torch.Tensor):
         p = src.data_ptr()
