@@ -98,6 +98,9 @@ class ParallelEngine:
             halo = HaloExchange(self.groups["replica"], self.device, pool_gradients=False)
         self.ctx = StreamContext(model_cfg, 1, self.replica_rank, halo.peer_fn if halo else None,
                                  wp_group=self.groups.get("replica"), sp_group=self.groups.get("sp"))
+        if grid.SP > 1 and self.device.type == "cuda":
+            from ..models.fused import SPExchange
+            self.ctx.sp_exchange = SPExchange(self.groups["sp"], self.device)
         self.tokens = self.ctx.grid.tokens_per_rank
         self._w_var = TF.variable_weights(model_cfg.out_channels, self.device)
         w = TF.latitude_weights(model_cfg.img[0], diff_cfg.w_lat_add)

@@ -290,6 +290,8 @@ class SwinLayer(nn.Module):
             if use_fused(x):
                 from . import fused
                 from ..ops import elementwise as E
+                if ctx.grid.sp > 1 and ctx.sp_exchange is None:
+                    raise RuntimeError("sequence parallelism on CUDA needs StreamContext.sp_exchange (fused.SPExchange)")
                 m = fused.modulation(mod.modulation, dt)
                 meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.n_local, cfg.heads, cfg.head_dim,
                                        E.MODE_MOD_THEN_NORM if cfg.after_mod_norm else E.MODE_NORM_THEN_MOD,
