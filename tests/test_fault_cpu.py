@@ -15,21 +15,30 @@ from aeris_gb_b200.utils.fault import (FaultInjector, Heartbeat, NonFiniteError,
 
 def _worker(rank, world, port, out):
     store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=30))
-    hb = Heartbeat(store, rank, world, timeout_s=1.0)
+    hb = Heartbeat(store, rank, world, timeout_s=2.5)
     inj = FaultInjector("silent:rank=1:step=2")
     detected = None
-    for step in range(8):
+    store.add("ready", 1)                      # start together even when the machine is busy spawning the ranks
+    while int(store.add("ready", 0)) < world:
+        time.sleep(0.05)
+    for step in range(40):
         if not inj.silences(rank, step):
-            hb.beat()
-        time.sleep(0.4)
-        try:
-            hb.check()
-        except RankFailure as e:
-            detected = (step, str(e))
+            hb.beat()                          # ranks that have noticed the failure keep beating until all have
+        time.sleep(0.3)
+        if detected is None:
+            try:
+                hb.check()
+            except RankFailure as e:
+                detected = (step, str(e))
+                store.add("detected", 1)
+        if int(store.add("detected", 0)) >= world - 1:
             break
     with open(os.path.join(out, f"r{rank}.txt"), "w") as f:
         f.write(repr(detected))
-    time.sleep(1.0 if rank == 0 else 0.0)      # keep the store alive until the others are done
+    store.add("done", 1)                       # rank 0 owns the store: keep it alive until the others are done
+    t0 = time.time()
+    while rank == 0 and int(store.add("done", 0)) < world and time.time() - t0 < 30:
+        time.sleep(0.1)
 
 
 def test_heartbeat_detects_a_silent_rank_between_steps():
