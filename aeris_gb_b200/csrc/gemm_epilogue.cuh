@@ -348,14 +348,22 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
     const __nv_bfloat16* res = p.resid ? p.resid + static_cast<size_t>(row) * p.ldr + tn * BN : nullptr;
     const float* gate = nullptr;
     if (gated) gate = p.gate + static_cast<size_t>(row / p.rows_per_gate) * p.N + tn * BN;
+    uint4 r4[4], r4n[4];       // residual of this and of the next 32 columns (requested one step ahead)
+    if (gated) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) r4n[i] = reinterpret_cast<const uint4*>(res)[i];
+    }
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {
       uint32_t v[32];
       tmem_ld32(taddr + c, v);
-      uint4 r4[4];
       if (gated) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) r4[i] = reinterpret_cast<const uint4*>(res + c)[i];
+        for (int i = 0; i < 4; ++i) r4[i] = r4n[i];
+        if (c + 32 < BN) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) r4n[i] = reinterpret_cast<const uint4*>(res + c + 32)[i];
+        }
       }
       tmem_wait_ld();
       uint32_t o[16];
