@@ -168,7 +168,11 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
 
 // Backward of the above. dx = dres + d(norm path). Column sums are kept in registers over the CTA's rows and
 // flushed with atomics at the end: dscale, dshift (fp32 [D], one modulation vector per launch) and dw (fp32 [D]).
-__global__ void modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dh,
+// MAXT / MINB: launch bounds by row width: up to 1536 columns 192 threads and two CTAs per SM (three were measured slower: spills), up to 5120 columns
+// 640 threads, wider rows 1024 threads (register cap 64: spills, but it launches).
+template <int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB)
+modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dh,
                                    const __nv_bfloat16* __restrict__ dres, const float* __restrict__ scale,
                                    const float* __restrict__ shift, const __nv_bfloat16* __restrict__ w,
                                    __nv_bfloat16* __restrict__ dx, float* __restrict__ dscale,
@@ -545,7 +549,10 @@ extern "C" int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres
   int rpc = pick_rows_per_cta(rows);
   if (rpc < 16) rpc = rows < 16 ? rows : 16;  // amortise the atomic flush of the column sums
   const int grid = (rows + rpc - 1) / rpc;    // every CTA takes about rpc rows, interleaved with the others
-  modnorm_bwd_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  const int nt = row_threads(D);
+  auto kern = (nt <= 192) ? modnorm_bwd_kernel<192, 2> : (nt <= 640) ? modnorm_bwd_kernel<640, 1>
+                                                                      : modnorm_bwd_kernel<1024, 1>;
+  kern<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(dh),
       reinterpret_cast<const __nv_bfloat16*>(dres), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
       reinterpret_cast<__nv_bfloat16*>(dx), dscale, dshift, dw, rows, D, mode, eps, rpc, w_f32);
