@@ -89,3 +89,35 @@ def test_fused_model_with_rope_matches_oracle():
         if b is None or b.float().norm() == 0:
             continue
         assert rel_err(a, b) < 8e-2
+
+
+def test_wide_block_dim5120_matches_oracle():
+    """The block dimensions of the 13 B-class configuration (dim 5120, 40 heads x 128, 30 x 30 windows) on a small
+    image: forward and input gradient of the CUDA path against the PyTorch formulation."""
+    from aeris_gb_b200.models.aeris import AerisConfig, AerisModel
+    torch.manual_seed(4)
+    cfg = AerisConfig(img=(60, 120), window=(30, 30), in_channels=20, out_channels=8, dim=5120, heads=40, head_dim=128,
+                      mlp_dim=13824, n_layers=2, sublayers=1, norm_eps=1e-3, chunk_windows=3)
+    model = AerisModel(cfg).cuda()
+    for n, p in model.named_parameters():
+        if "modulation" in n and p.dim() == 2:
+            torch.nn.init.normal_(p, std=0.02)
+    x = torch.randn(1, 60, 120, cfg.in_channels, device="cuda")
+    t = torch.tensor([0.7], device="cuda")
+
+    def run(force_oracle):
+        os.environ["AERIS_FORCE_ORACLE"] = "1" if force_oracle else "0"
+        model.zero_grad(set_to_none=True)
+        xin = x.clone().requires_grad_(True)
+        y = model(xin, t)
+        (y * torch.linspace(-1, 1, y.numel(), device="cuda").view_as(y)).sum().backward()
+        return y.detach(), xin.grad, model.layers[0].modulelist[0][3].w2.weight.grad.clone()
+
+    try:
+        y0, gx0, gw0 = run(True)
+        y1, gx1, gw1 = run(False)
+    finally:
+        os.environ.pop("AERIS_FORCE_ORACLE", None)
+    assert rel_err(y1, y0) < 3e-2
+    assert rel_err(gx1, gx0) < 6e-2
+    assert rel_err(gw1, gw0) < 8e-2
