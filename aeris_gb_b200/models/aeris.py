@@ -356,25 +356,19 @@ class OutputStage(nn.Module):
         shift, scale = self.modulation(dt.to(cfg.data_dtype)).chunk(2, dim=1)
         return _HeadFn.apply(x, shift, scale, self.norm.weight, self.head.weight, self)
 
-
-def _out_loss_images(self, x, dt, x_img, cs, plan):
-    """TrigFlow loss of the output stage straight from the stream (CUDA path; see :mod:`.fused_io`)."""
-    from . import fused, fused_io
-    shift, scale = fused.modulation(self.modulation, dt).chunk(2, dim=1)
-    return fused_io.HeadLossFn.apply(x, shift, scale, self.norm.weight, self.head.weight, x_img, cs, plan)
-
-
-def _out_predict_tokens(self, x, dt):
-    """Network output in token order, fp32 ``[T, 128]`` (channels past ``out_channels`` are zero); no autograd."""
-    from . import fused, fused_io
-    with torch.no_grad():
+    def loss_images(self, x, dt, x_img, cs, plan):
+        """TrigFlow loss of the output stage straight from the stream (CUDA path; see :mod:`.fused_io`)."""
+        from . import fused, fused_io
         shift, scale = fused.modulation(self.modulation, dt).chunk(2, dim=1)
-        return fused_io.head_forward(x, shift, scale, self.norm.weight, self.head.weight,
-                                     self.cfg.eps(self.cfg.data_dtype))
+        return fused_io.HeadLossFn.apply(x, shift, scale, self.norm.weight, self.head.weight, x_img, cs, plan)
 
-
-OutputStage.loss_images = _out_loss_images
-OutputStage.predict_tokens = _out_predict_tokens
+    def predict_tokens(self, x, dt):
+        """Network output in token order, fp32 ``[T, 128]`` (channels past ``out_channels`` are zero); no autograd."""
+        from . import fused, fused_io
+        with torch.no_grad():
+            shift, scale = fused.modulation(self.modulation, dt).chunk(2, dim=1)
+            return fused_io.head_forward(x, shift, scale, self.norm.weight, self.head.weight,
+                                         self.cfg.eps(self.cfg.data_dtype))
 
 
 class _HeadFn(torch.autograd.Function):
