@@ -6,6 +6,10 @@
 Weak scaling: the global batch is N samples; every sample is window-parallel over all N GPUs (WP = N), so each GPU
 always holds 1,036,800 tokens per step. Synthetic N(0,1) fields, random-init weights, bf16 compute with fp32 master
 weights, full optimizer step inside the timed region. Prints ONE JSON line on rank 0.
+
+Other arms: ``--impl reference`` (prints why the reference cannot run here), ``--impl torch-eager`` (the same model
+through stock PyTorch ops, an informational same-math baseline), ``--mode infer`` (seconds per autoregressive forecast
+step, one ensemble member per GPU), ``--sp S`` (WP = N / S with Ulysses sequence parallelism S).
 """
 from __future__ import annotations
 
