@@ -33,6 +33,8 @@ class InferenceEngine(ParallelEngine):
         self._ret = 0
         self.first_rank = self.grid.rank_of(self.c.dp, self.c.wp_y, self.c.wp_x, 0, self.c.sp)
         self.last_rank = self.grid.rank_of(self.c.dp, self.c.wp_y, self.c.wp_x, self.PP - 1, self.c.sp)
+        if self.PP > 1:
+            self.links.peer["result"] = self.last_rank if self.is_first_stage() else self.first_rank
         self._imap.update({SCH.SendResult: self.send_result, SCH.ReturnResult: self.return_result})
 
     def load(self, buffer_id):
@@ -51,8 +53,8 @@ class InferenceEngine(ParallelEngine):
         self.buf["outputs"][buffer_id], self.buf["dt_out"][buffer_id] = y, dt
 
     def process_recv(self, buffer_id):
-        hx, hd, x, dt = self._pending.pop(("act", buffer_id))
-        hx.wait(); hd.wait()
+        works, x, dt = self._pending.pop(("act", buffer_id))
+        self.links.wait(works)
         self.buf["inputs"][buffer_id], self.buf["dt_in"][buffer_id] = x, dt
 
     def send_result(self, buffer_id):
@@ -60,15 +62,14 @@ class InferenceEngine(ParallelEngine):
         if self.PP == 1:
             self._local_result = y
             return
-        self._wait_sends()
-        self._isend(y.float(), self.first_rank, 4)
+        self.links.send("result", [y.float()])
 
     def return_result(self, buffer_id):
         if self.PP == 1:
             out = self._local_result
         else:
             out = torch.empty((self.tokens, self.cfg.out_channels), dtype=torch.float32, device=self.device)
-            dist.recv(out, self.last_rank, tag=4)
+            self.links.wait(self.links.post_recv("result", [out]))
         self.results[self._ret] = out
         self._ret += 1
 
@@ -82,4 +83,5 @@ class InferenceEngine(ParallelEngine):
             for cmd in cmds:
                 self._imap[type(cmd)](**cmd.kwargs)
         self._wait_sends()
+        self.check_device()
         return self.results if self.is_first_stage() else None

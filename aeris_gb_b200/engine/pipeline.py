@@ -31,6 +31,7 @@ from ..parallel.topology import ProcessGrid
 from .checkpoint import load_stage_checkpoint, save_stage_checkpoint
 from .init import init_params
 from .optim import FlatOptimizer, OptimConfig
+from .p2p import PipeLinks
 from .trainer import DiffusionConfig
 
 
@@ -70,16 +71,18 @@ class ParallelEngine:
             self.opt = DistOptimizer(self.module, optim_cfg, self.groups.get("weight"), rs_grads=ecfg.rs_grads)
         else:
             self.opt = FlatOptimizer(self.module, optim_cfg)
-        # The overlapped schedule posts receives a step early and sends right after compute; that needs a transport that
-        # accepts sends and receives in any order (gloo, MPI). NCCL p2p calls of a pair of ranks must be enqueued in
-        # matching order, so on CUDA the plain 1F1B order is used; its transfers still run on NCCL's own stream.
-        overlap = ecfg.overlap_p2p and self.device.type != "cuda"
-        sched_cls = SCH.OverlappedTrainSchedule if overlap else SCH.TrainSchedule
+        # The overlapped schedule posts receives a step early and sends right after compute (NCCL and gloo alike:
+        # the links have one communicator per direction, see engine/p2p.py).
+        sched_cls = SCH.OverlappedTrainSchedule if ecfg.overlap_p2p else SCH.TrainSchedule
         self.schedule = sched_cls(self.GAS, self.PP, self.c.pp)
         nb = self.schedule.num_pipe_buffers()
         self.buf = {k: [None] * nb for k in ("inputs", "outputs", "dt_in", "dt_out", "x", "z", "t", "grad_x", "grad_dt")}
         self.prev_rank = grid.rank_of(self.c.dp, self.c.wp_y, self.c.wp_x, self.c.pp - 1, self.c.sp) if self.c.pp > 0 else None
         self.next_rank = grid.rank_of(self.c.dp, self.c.wp_y, self.c.wp_x, self.c.pp + 1, self.c.sp) if self.c.pp < self.PP - 1 else None
+        self.links = PipeLinks(self.groups, self.prev_rank, self.next_rank, self.device)
+        if self.PP > 1:
+            self.links.warm()
+        self.dt_grad = self.PP > 1 and not model_cfg.layerwise_t_emb
         # noise: per (wp, dp, sp), NOT per pp, so the first and last stage regenerate identical z without talking
         # (:119, :667); noise level: per dp replica (:120)
         base = ecfg.seed
@@ -197,19 +200,21 @@ class ParallelEngine:
             loss = err.sum(dim=-1).mean()
             self.loss_acc += loss.detach()
             loss.backward()
+        elif self.dt_grad:
+            # dt leaves this stage unchanged: on the first stage it is the embedding network's output, elsewhere the
+            # received leaf, so the gradient from below is added to what this stage's own layers contribute
+            torch.autograd.backward([out, self.buf["dt_out"][buffer_id]],
+                                    [self.buf["grad_x"][buffer_id], self.buf["grad_dt"][buffer_id]])
         else:
             torch.autograd.backward(out, self.buf["grad_x"][buffer_id])
-        for k in ("outputs", "x", "z"):
+        for k in ("outputs", "x", "z", "grad_x", "grad_dt", "dt_out"):
             self.buf[k][buffer_id] = None
 
     # p2p ---------------------------------------------------------------------------------------------------------
-    def _isend(self, t: torch.Tensor, dst: int, tag: int):
-        h = dist.isend(t.detach().contiguous(), dst, tag=tag)
-        self._pending.setdefault("send", []).append((h, t))
-
+    # One grouped transfer per instruction on the channel that :func:`schedule.p2p_op` names; x travels before dt and
+    # the gradient of x before that of dt on both ends. Nothing here blocks the host on NCCL.
     def _wait_sends(self):
-        for h, _ in self._pending.pop("send", []):
-            h.wait()
+        self.links.wait_sends()
 
     def _act_buffers(self):
         B = 1
@@ -218,38 +223,45 @@ class ParallelEngine:
         return x, dt
 
     def send(self, buffer_id):
-        self._wait_sends()
-        self._isend(self.buf["outputs"][buffer_id], self.next_rank, 1)
-        self._isend(self.buf["dt_out"][buffer_id], self.next_rank, 2)
+        self.links.send("down_next", [self.buf["outputs"][buffer_id], self.buf["dt_out"][buffer_id]])
 
     def submit_recv(self, buffer_id):
         x, dt = self._act_buffers()
-        self._pending[("act", buffer_id)] = (dist.irecv(x, self.prev_rank, tag=1), dist.irecv(dt, self.prev_rank, tag=2), x, dt)
+        self._pending[("act", buffer_id)] = (self.links.post_recv("down_prev", [x, dt]), x, dt)
 
     def process_recv(self, buffer_id):
-        hx, hd, x, dt = self._pending.pop(("act", buffer_id))
-        hx.wait(); hd.wait()
+        works, x, dt = self._pending.pop(("act", buffer_id))
+        self.links.wait(works)
         self.buf["inputs"][buffer_id] = x.requires_grad_(True)   # leaf: its .grad is what goes back upstream
-        self.buf["dt_in"][buffer_id] = dt
+        # with one embedding network on the first stage (layerwise_t_emb off) dt is trainable upstream: a leaf too,
+        # whose gradient (this stage's layers plus what the stages below send up) returns with that of x (:1052-1068)
+        self.buf["dt_in"][buffer_id] = dt.requires_grad_(True) if self.dt_grad else dt
 
     def recv(self, buffer_id):
         self.submit_recv(buffer_id)
         self.process_recv(buffer_id)
 
     def send_grad(self, buffer_id):
-        self._wait_sends()
-        g = self.buf["inputs"][buffer_id].grad
-        self._isend(g, self.prev_rank, 3)
+        out = [self.buf["inputs"][buffer_id].grad]
+        if self.dt_grad:
+            g = self.buf["dt_in"][buffer_id].grad
+            out.append(g if g is not None else torch.zeros_like(self.buf["dt_in"][buffer_id]))
+        self.links.send("up_prev", out)
         self.buf["inputs"][buffer_id] = None
+        self.buf["dt_in"][buffer_id] = None
 
     def submit_recv_grad(self, buffer_id):
         g = torch.empty((self.tokens, self.cfg.dim), dtype=self.cfg.model_dtype, device=self.device)
-        self._pending[("grad", buffer_id)] = (dist.irecv(g, self.next_rank, tag=3), g)
+        bufs = [g]
+        if self.dt_grad:
+            bufs.append(torch.empty((1, self.cfg.dim), dtype=self.cfg.model_dtype, device=self.device))
+        self._pending[("grad", buffer_id)] = (self.links.post_recv("up_next", bufs), bufs)
 
     def process_grad(self, buffer_id):
-        h, g = self._pending.pop(("grad", buffer_id))
-        h.wait()
-        self.buf["grad_x"][buffer_id] = g
+        works, bufs = self._pending.pop(("grad", buffer_id))
+        self.links.wait(works)
+        self.buf["grad_x"][buffer_id] = bufs[0]
+        self.buf["grad_dt"][buffer_id] = bufs[1] if self.dt_grad else None
 
     def recv_grad(self, buffer_id):
         self.submit_recv_grad(buffer_id)
@@ -266,9 +278,17 @@ class ParallelEngine:
             self.tot_loss = float(lt.item())
             self.loss_acc.zero_()
 
+    def check_device(self):
+        """Raise ``KernelError`` if a kernel recorded a device-side error (a bounded wait that ran out, a failed bounds
+        check) since the last check; reads one word from the device."""
+        if self.device.type == "cuda":
+            from ..ops import lib as L
+            L.check_status(sync=False)
+
     def reduce_grads(self):
         self._wait_sends()
         self.reduce_loss()
+        self.check_device()       # before the gradients of an incomplete exchange reach the optimizer and the peers
         scale = 1.0 / (self.grid.DP * self.GAS)
         if not self.dcfg.grad_scale_parity:
             scale /= self.grid.WP_Y * self.grid.WP_X * self.grid.SP
@@ -308,6 +328,7 @@ class ParallelEngine:
         self._wait_sends()
         if self.device.type == "cuda":
             torch.cuda.synchronize()
+            self.check_device()
         self.timers = timers
         e = self.ecfg
         if e.checkpoint_dir and not e.benchmark and self.cur_it % e.checkpoint_every == 0:

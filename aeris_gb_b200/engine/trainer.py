@@ -183,11 +183,26 @@ class Trainer:
                 loss = self.loss_tokens(x_tok, c_tok, t, z)
         with self.timers.region("bwd"):
             loss.backward()
+        if read_loss:
+            # a bounded device wait that ran out (a peer that never signalled) leaves incomplete activations or
+            # gradients behind: raise before the optimizer applies them and the all-gather spreads them
+            self.check_device()
         with self.timers.region("reduce_step"):
             self.reduce_and_step(B)
         self.step_count += 1
         self.last_loss = loss.detach()
-        return float(self.last_loss.item()) / B if read_loss else None
+        if not read_loss:
+            return None
+        value = float(self.last_loss.item()) / B
+        self.check_device()
+        return value
+
+    def check_device(self) -> None:
+        """Raise ``KernelError`` if a kernel of this library recorded a device-side error (time-out of a bounded wait,
+        failed bounds check) since the last check. Reads one word from the device, so it synchronises."""
+        if self.device.type == "cuda":
+            from ..ops import lib as L
+            L.check_status(sync=False)
 
     def reduce_and_step(self, local_batch: int):
         gas = local_batch

@@ -50,6 +50,23 @@ class SendResult(Instruction): pass
 class ReturnResult(Instruction): pass
 
 
+# Point-to-point traffic of the training instructions. Every link between two neighbouring stages has two channels,
+# one per direction of travel: "down" carries activations (x, then the noise-level embedding dt) from stage s to s + 1,
+# "up" carries gradients (of x, then of dt where dt is trainable upstream) from s + 1 to s. A channel is a communicator
+# of its own, so its operations all flow one way and the k-th send meets the k-th receive whatever the two ranks do on
+# other channels in between. (With one communicator per pair, as NCCL orders the operations of a communicator by issue
+# order, the overlapped schedule stalls: stage s issues recv(grad) then send(x), stage s + 1 recv(x) then send(grad),
+# and each receive waits for a send queued behind the peer's receive.)
+# instruction type -> (channel as seen from the issuing stage, "send" | "recv", "act" | "grad")
+def p2p_op(cmd: Instruction) -> tuple[str, str, str] | None:
+    return {
+        SendActivation: ("down_next", "send", "act"), RecvActivation: ("down_prev", "recv", "act"),
+        SubmitRecvActivation: ("down_prev", "recv", "act"),
+        SendGrad: ("up_prev", "send", "grad"), RecvGrad: ("up_next", "recv", "grad"),
+        SubmitRecvGrad: ("up_next", "recv", "grad"),
+    }.get(type(cmd))
+
+
 class PipeSchedule:
     def __init__(self, micro_batches: int, stages: int, stage_id: int):
         assert 0 <= stage_id < stages and micro_batches >= 1

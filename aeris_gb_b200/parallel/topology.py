@@ -5,7 +5,10 @@ as plain rank lists (testable without any process group); :meth:`ProcessGrid.bui
 
 Groups (reference lines in parentheses): ``sp`` = same (dp, wp, pp) (:379); ``pp`` = same (dp, wp, sp) (:391);
 ``weight`` = every rank of one pipeline stage, i.e. all of DP x WP x SP (:400-402), the group gradients are reduced
-over; ``wp`` = same (dp, pp, sp) (window-parallel peers, used by the halo exchange and result gathers); ``dp``.
+over; ``wp`` = same (dp, pp, sp) (window-parallel peers, used by the halo exchange and result gathers); ``dp``;
+``pipe`` = for every pair of neighbouring pipeline stages two 2-rank groups, one per direction of travel (the reference
+creates pairwise ``pp_comm_group_{prev,next}`` groups, :425-451): activations go down one, gradients come up the other,
+so the point-to-point operations of each communicator all flow one way and match in issue order.
 """
 from __future__ import annotations
 
@@ -80,6 +83,15 @@ class ProcessGrid:
         """One rank per pipeline stage (dp = wp = sp = 0): the ranks that write checkpoints (:1229)."""
         return self.grid[0, 0, 0, :, 0].flatten().tolist()
 
+    def pipe_pairs(self) -> list[tuple[int, int]]:
+        """(rank of stage s, rank of stage s + 1) for every pipeline link of the grid, in a fixed global order."""
+        out = []
+        for r in range(self.used):
+            c = self.coords(r)
+            if c.pp + 1 < self.PP:
+                out.append((r, self.rank_of(c.dp, c.wp_y, c.wp_x, c.pp + 1, c.sp)))
+        return out
+
     def all_group_lists(self, kind: str) -> list[list[int]]:
         fn = {"sp": self.sp_ranks, "pp": self.pp_ranks, "wp": self.wp_ranks, "dp": self.dp_ranks,
               "weight": self.weight_ranks, "replica": self.replica_ranks}[kind]
@@ -92,13 +104,32 @@ class ProcessGrid:
         return out
 
     # ---- torch.distributed groups -----------------------------------------------------------------------------
-    def build_groups(self, rank: int, kinds=("sp", "pp", "wp", "dp", "weight", "replica"),
+    def build_groups(self, rank: int, kinds=("sp", "pp", "wp", "dp", "weight", "replica", "pipe"),
                      backend: str | None = None) -> dict:
         """Creates every group of the requested kinds on every rank (``new_group`` is collective over the world) and
-        returns this rank's group of each kind. Groups of size 1 are returned as ``None``."""
+        returns this rank's group of each kind. Groups of size 1 are returned as ``None``. Kind ``pipe`` yields the
+        keys ``down_next`` / ``up_next`` (links to the next stage), ``down_prev`` / ``up_prev`` and ``result`` (last
+        stage to first stage)."""
         import torch.distributed as dist
         mine = {}
         for kind in kinds:
+            if kind == "pipe":
+                for lo, hi in self.pipe_pairs():
+                    for direction in ("down", "up"):
+                        g = dist.new_group([lo, hi], backend=backend)
+                        if rank == lo:
+                            mine[f"{direction}_next"] = g
+                        elif rank == hi:
+                            mine[f"{direction}_prev"] = g
+                if self.PP > 1:      # last stage -> first stage: results of the inference schedule
+                    for r in range(self.used):
+                        c = self.coords(r)
+                        if c.pp == 0:
+                            last = self.rank_of(c.dp, c.wp_y, c.wp_x, self.PP - 1, c.sp)
+                            g = dist.new_group([r, last], backend=backend)
+                            if rank in (r, last):
+                                mine["result"] = g
+                continue
             for ranks in self.all_group_lists(kind):
                 if len(ranks) == 1:
                     if rank in ranks:

@@ -7,7 +7,7 @@ Weak scaling: the global batch is N samples; every sample is window-parallel ove
 always holds 1,036,800 tokens per step. Synthetic N(0,1) fields, random-init weights, bf16 compute with fp32 master
 weights, full optimizer step inside the timed region. Prints ONE JSON line on rank 0.
 
-Other arms: ``--impl reference`` (prints why the reference cannot run here), ``--impl torch-eager`` (the same model
+Other arms: ``--impl reference`` (the unmodified reference modules on stock PyTorch kernels, data parallel), ``--impl torch-eager`` (the same model
 through stock PyTorch ops, an informational same-math baseline), ``--mode infer`` (seconds per autoregressive forecast
 step, one ensemble member per GPU), ``--sp S`` (WP = N / S with Ulysses sequence parallelism S).
 """
@@ -27,13 +27,131 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 
+FLAGSHIP = {   # plain numbers shared by both arms (no package import needed to read them)
+    "full": dict(img=(720, 1440), window=(30, 30), dim=1536, heads=24, head_dim=64, mlp_dim=4096, n_layers=40,
+                 in_ch=144, out_ch=70, chunk_windows=72),
+    "quarter": dict(img=(360, 720), window=(30, 30), dim=1536, heads=24, head_dim=64, mlp_dim=4096, n_layers=10,
+                    in_ch=144, out_ch=70, chunk_windows=72),
+    "tiny": dict(img=(120, 240), window=(30, 30), dim=256, heads=4, head_dim=64, mlp_dim=512, n_layers=4,
+                 in_ch=144, out_ch=70, chunk_windows=8),
+}
+METRIC_TRAIN = "train samples/s (TrigFlow, 720x1440 Swin diffusion)"
+METRIC_INFER = "WP-infer s/step (one member per GPU)"
+
+
+def model_label(d: dict) -> str:
+    return (f"AERIS Swin TrigFlow dim{d['dim']} x{d['n_layers']} blocks heads{d['heads']}x{d['head_dim']} "
+            f"mlp{d['mlp_dim']} window{d['window'][0]}x{d['window'][1]} channels{d['in_ch']}->{d['out_ch']}")
+
+
 def reference_arm(args):
-    # The reference cannot be installed or imported in this image: its build backend (hatchling) is absent from the
-    # interpreter and from the offline wheelhouse, it imports deepspeed/ezpz/mpi4py/hydra/h5py (all absent), its
-    # engine asserts SP == 12 with >= 4 pipeline stages (>= 48 ranks) and calls torch.xpu.* unconditionally.
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "pip install of the reference fails offline (build backend hatchling missing; deps deepspeed, "
-                      "ezpz, mpi4py, hydra, h5py missing) and its engine needs SP=12 x PP>=4 (>=48 ranks) on torch.xpu"}))
+    """The unmodified reference modules (a copy of the reference's ``src/`` under ``baseline/_ref``) driven by
+    ``baseline/harness.py`` on stock PyTorch kernels: data parallel over the N GPUs, one full sample per GPU, so global
+    batch and tokens per GPU equal the framework's run. Nothing of ``aeris_gb_b200`` is imported on this path.
+    One pass of K steps gives both numbers: every step copies its inputs from pinned host memory and reads the loss
+    back (end to end); CUDA events after the copy and before the read-back give the device-only time."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from baseline import harness as HN
+    why = HN.reference_available()
+    if why:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29517")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    d = dict(FLAGSHIP[args.scale])
+    if args.layers:
+        d["n_layers"] = args.layers
+    if args.chunk_windows:
+        d["chunk_windows"] = args.chunk_windows
+    H, Wd = d["img"]
+    W, K = max(args.warmup, 3), args.steps
+    gen = torch.Generator().manual_seed(100 + rank)
+
+    def sync_all():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    if args.mode == "infer":
+        fc = HN.ReferenceForecaster(d, dev, sampler_steps=args.sampler_steps, seed=rank)
+        g7 = torch.Generator().manual_seed(7)
+        state = torch.randn(1, H * Wd, d["out_ch"], generator=g7).to(dev)
+        forcing = torch.randn(1, H * Wd, d["in_ch"] - 2 * d["out_ch"], generator=g7).to(dev)
+        state = fc.step(state, forcing)
+        sync_all()
+        clk = ClockSampler(local_rank)
+        clk.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            state = fc.step(state, forcing)
+        e1.record()
+        sync_all()
+        t = torch.tensor([e0.elapsed_time(e1) / 1e3 / K], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        clocks = clk.stop()
+        if rank == 0:
+            n_par = sum(p.numel() for p in fc.model.parameters())
+            print(json.dumps({
+                "impl": "reference", "metric": METRIC_INFER, "value": t.item(), "unit": "s per forecast step",
+                "n_gpus": world, "steps": K, "warmup": 1, "higher_is_better": False, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "members": world,
+                "config": {"model": model_label(d), "params": n_par, "sampler_steps": args.sampler_steps,
+                           "network_evals_per_step": 2 * args.sampler_steps - 1, "scale": args.scale,
+                           "state_finite": bool(torch.isfinite(state).all().item())},
+                "clocks": clocks, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9}))
+        dist.destroy_process_group()
+        return 0
+
+    tr = HN.ReferenceTrainer(d, dev, group=dist.group.WORLD)
+    host = [(torch.randn(1, H, Wd, d["out_ch"], generator=gen).pin_memory(),
+             torch.randn(1, H, Wd, d["in_ch"] - d["out_ch"], generator=gen).pin_memory()) for _ in range(2)]
+    h2d = sum(t_.numel() * 4 for t_ in host[0])
+    for i in range(W):
+        tr.train_step(*host[i % 2])
+    sync_all()
+    clk = ClockSampler(local_rank)
+    clk.start()
+    marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    loss = None
+    for i in range(K):
+        loss = tr.train_step(*host[i % 2], marks=marks[i])
+    e1.record()
+    sync_all()
+    wall = (time.perf_counter() - t0) * 1e3
+    ms_dev = sum(a.elapsed_time(b) for a, b in marks)
+    tt = torch.tensor([ms_dev, max(e0.elapsed_time(e1), wall)], device=dev, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    clocks = clk.stop()
+    ms_dev, ms_e = tt[0].item() / K, tt[1].item() / K
+    B = world
+    if rank == 0:
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC_TRAIN, "value": B / (ms_dev / 1e3), "unit": "samples/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_dev, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "tflops_per_gpu": tr.flops_per_step(B) / (ms_dev / 1e3) / 1e12 / world,
+            "config": {"model": model_label(d), "params": tr.param_count, "global_batch": B, "seq_len": H * Wd,
+                       "parallelism": f"dp{world}", "scale": args.scale,
+                       "activation_checkpointing": "per layer and window chunk (harness glue)",
+                       "l2": "inputs (597 MB/step/GPU) and activations are far larger than L2",
+                       "timing": "one pass: device time between events after the H2D copy and before the loss read"},
+            "clocks": clocks,
+            "e2e": {"value": B / (ms_e / 1e3), "unit": "samples/s", "ms_per_step": ms_e, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 4, "last_loss": loss},
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9}))
+    dist.destroy_process_group()
     return 0
 
 
@@ -83,18 +201,13 @@ class ClockSampler:
 
 
 def flagship_config(n_gpus: int, scale: str, sp: int = 1):
-    import torch
     from aeris_gb_b200.engine.trainer import wp_grid_for
     from aeris_gb_b200.models.aeris import AerisConfig
-    wp = wp_grid_for(n_gpus // sp)
-    if scale == "full":
-        return AerisConfig(img=(720, 1440), window=(30, 30), in_channels=144, out_channels=70, dim=1536, heads=24,
-                           head_dim=64, mlp_dim=4096, n_layers=40, sublayers=1, wp=wp, sp=sp, chunk_windows=72)
-    if scale == "quarter":   # development size: a quarter of the pixels, a quarter of the depth
-        return AerisConfig(img=(360, 720), window=(30, 30), in_channels=144, out_channels=70, dim=1536, heads=24,
-                           head_dim=64, mlp_dim=4096, n_layers=10, sublayers=1, wp=wp, sp=sp, chunk_windows=72)
-    return AerisConfig(img=(120, 240), window=(30, 30), in_channels=144, out_channels=70, dim=256, heads=4,
-                       head_dim=64, mlp_dim=512, n_layers=4, sublayers=1, wp=wp, sp=sp, chunk_windows=8)
+    d = FLAGSHIP[scale]
+    return AerisConfig(img=d["img"], window=d["window"], in_channels=d["in_ch"], out_channels=d["out_ch"],
+                       dim=d["dim"], heads=d["heads"], head_dim=d["head_dim"], mlp_dim=d["mlp_dim"],
+                       n_layers=d["n_layers"], sublayers=1, wp=wp_grid_for(n_gpus // sp), sp=sp,
+                       chunk_windows=d["chunk_windows"])
 
 
 def infer_arm(args):
@@ -148,12 +261,12 @@ def infer_arm(args):
     clocks = clk.stop()
     if rank == 0:
         print(json.dumps({
-            "metric": "WP-infer s/step (one member per GPU)", "value": t.item(), "unit": "s per forecast step",
+            "metric": METRIC_INFER, "value": t.item(), "unit": "s per forecast step",
             "n_gpus": world, "steps": args.steps, "warmup": 1, "higher_is_better": False, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "members": world,
             "member_forecast_steps_per_s": world / t.item(),
-            "config": {"model": f"AERIS Swin TrigFlow dim{cfg.dim} x{cfg.n_blocks} blocks ({cfg.param_count() / 1e9:.2f}B)",
-                       "sampler_steps": args.sampler_steps, "network_evals_per_step": fc.model_evals_per_forecast_step(),
+            "config": {"model": model_label({**FLAGSHIP[args.scale], "n_layers": cfg.n_layers}),
+                       "params": cfg.param_count(), "sampler_steps": args.sampler_steps, "network_evals_per_step": fc.model_evals_per_forecast_step(),
                        "scale": args.scale, "state_finite": bool(torch.isfinite(state).all().item())},
             "clocks": clocks, "gpu_launches": L.launch_count() - l0, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9}))
     if world > 1:
@@ -200,8 +313,15 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
 
-    cfg = flagship_config(world, args.scale, args.sp)
     eager = args.impl == "torch-eager"
+    parity = None
+    if world > 1 and not eager:
+        # outside the timed region: the multi-GPU kernels of this run against one GPU on a small model
+        from aeris_gb_b200.parallel.parity import wp_parity
+        parity = wp_parity(dev, args.sp)
+        if parity["max_rel_err"] > 3e-2:
+            raise SystemExit(f"multi-GPU parity check failed: {parity}")
+    cfg = flagship_config(world, args.scale, args.sp)
     if eager:
         os.environ["AERIS_FORCE_ORACLE"] = "1"
         cfg.oracle_checkpoint = True
@@ -278,17 +398,15 @@ def main():
     if rank == 0:
         out = {
             **({"impl": "torch-eager"} if eager else {}),
-            "metric": "train samples/s (TrigFlow, 720x1440 Swin diffusion)", "value": B / (ms_dev / 1e3),
+            "metric": METRIC_TRAIN, "value": B / (ms_dev / 1e3),
             "unit": "samples/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "tflops_per_gpu": flops / (ms_dev / 1e3) / 1e12 / world,
-            "config": {"model": f"AERIS Swin TrigFlow dim{cfg.dim} x{cfg.n_blocks} blocks heads{cfg.heads} "
-                                f"mlp{cfg.mlp_dim} window{cfg.window[0]}x{cfg.window[1]} "
-                                f"({cfg.param_count() / 1e9:.2f}B params)",
-                       "global_batch": B, "seq_len": cfg.img[0] * cfg.img[1], "parallelism": f"wp{world // args.sp}" + (f"xsp{args.sp}" if args.sp > 1 else ""),
+            "config": {"model": model_label({**FLAGSHIP[args.scale], "n_layers": cfg.n_layers}),
+                       "params": cfg.param_count(), "global_batch": B, "seq_len": cfg.img[0] * cfg.img[1], "parallelism": f"wp{world // args.sp}" + (f"xsp{args.sp}" if args.sp > 1 else ""),
                        "scale": args.scale, "activation_checkpointing": "per block",
                        "l2": "inputs (597 MB/step/GPU) and activations are far larger than L2"},
-            "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+            "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "parity": parity,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
         }
         print(json.dumps(out))

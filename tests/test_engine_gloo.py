@@ -17,9 +17,10 @@ from aeris_gb_b200.parallel.topology import ProcessGrid
 IMG, CH, CC = (16, 32), 6, 4
 
 
-def _cfg(wp=(1, 1), sp=1):
+def _cfg(wp=(1, 1), sp=1, layerwise=True):
     return AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=32, heads=2, head_dim=16,
-                       mlp_dim=64, n_layers=4, sublayers=1, model_dtype=torch.float32, wp=wp, sp=sp, norm_eps=1e-5)
+                       mlp_dim=64, n_layers=4, sublayers=1, model_dtype=torch.float32, wp=wp, sp=sp, norm_eps=1e-5,
+                       layerwise_t_emb=layerwise)
 
 
 def _field(seed, C):
@@ -46,7 +47,7 @@ def _noise_fn(eng):
     return _block(_field(3000 + _sample_index(eng), CH), eng)
 
 
-def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_dir, resume, SP=1):
+def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_dir, resume, SP=1, layerwise=True):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     if world > 1:
         dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -54,7 +55,7 @@ def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_
     ecfg = EngineConfig(gas=gas, overlap_p2p=overlap, dist_optimizer=distopt, checkpoint_dir=ckpt_dir,
                         checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5)
     torch.manual_seed(0)
-    eng = ParallelEngine(_cfg(WP, SP), OptimConfig(lr=0.5, eps=1.0, lr_rampup_img=0, grad_clip_max_norm=0.5, weight_decay=0.0),
+    eng = ParallelEngine(_cfg(WP, SP, layerwise), OptimConfig(lr=0.5, eps=1.0, lr_rampup_img=0, grad_clip_max_norm=0.5, weight_decay=0.0),
                          DiffusionConfig(grad_scale_parity=False, cond_channels=CC), ecfg, grid, rank, "cpu",
                          data_fn=_data_fn, groups={} if world == 1 else None)
     # identical initial weights regardless of the split: every logical stage is seeded by its own index
@@ -90,7 +91,7 @@ def _launch(world, **kw):
     from conftest import free_port
     port = free_port()
     args = (world, port, kw["PP"], kw["WP"], kw["gas"], kw.get("overlap", False), kw.get("distopt", False),
-            kw["iters"], out, kw.get("ckpt_dir"), kw.get("resume", False), kw.get("SP", 1))
+            kw["iters"], out, kw.get("ckpt_dir"), kw.get("resume", False), kw.get("SP", 1), kw.get("layerwise", True))
     if world == 1:
         _run(0, *args)
     else:
@@ -125,6 +126,20 @@ def test_pp3_matches_single_process(single):
     _assert_same(sd, single[0])
     assert loss == pytest.approx(single[1], rel=1e-4)
     assert norm == pytest.approx(single[2], rel=1e-4)
+
+
+def test_pp3_shared_noise_embedding_gets_its_gradient_from_every_stage():
+    """One embedding network on the first stage (layerwise_t_emb off): its output dt feeds every stage, so its
+    gradient has to travel back up the pipeline with that of the activations (parallel_engine.py:1052-1068)."""
+    ref = _launch(1, PP=1, WP=(1, 1), gas=4, iters=2, layerwise=False)
+    ref_grads = _launch.last_grads
+    sd, loss, norm = _launch(3, PP=3, WP=(1, 1), gas=4, iters=2, overlap=True, layerwise=False)
+    g = _launch.last_grads
+    k = "latent_embed.w1.weight"
+    assert ref_grads[0][k].abs().max() > 0
+    assert torch.allclose(g[0][k], ref_grads[0][k], atol=1e-6, rtol=1e-4)
+    _assert_same(sd, ref[0])
+    assert norm == pytest.approx(ref[2], rel=1e-4)
 
 
 def test_pp2_overlapped_wp2_matches_single_process(single):

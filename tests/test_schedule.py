@@ -100,3 +100,85 @@ def test_ensemble_inference_schedule(M, P):
         sent = [c for c in seq[P - 1][k] if c.name == "SendResult"]
         ret = [c for c in seq[0][k] if c.name == "ReturnResult"]
         assert len(sent) == len(ret)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Stream-level replay of the point-to-point traffic the way NCCL executes it: the host enqueues everything without
+# blocking; every communicator runs its operations in issue order on a stream of its own; an operation starts once
+# the compute kernels queued before it have finished and completes only together with the complementary operation at
+# the head of the peer's stream of the same communicator; a compute kernel waits for the receives it consumes.
+def _enqueue(cls, M, P, s, directional):
+    sched = cls(M, P, s)
+    comm, compute, pending, wait_list = {}, [], {}, []
+    buf_mb = {}
+    for k, cmds in enumerate(sched.steps()):
+        for c in cmds:
+            op = S.p2p_op(c)
+            if op is not None:
+                channel, kind, what = op
+                lo = s if channel.endswith("next") else s - 1
+                key = (lo, channel.split("_")[0]) if directional else (lo,)
+                item = dict(kind=kind, what=what, after=len(compute), done=False, rank=s)
+                comm.setdefault(key, []).append(item)
+                if isinstance(c, (S.RecvActivation, S.RecvGrad)):
+                    wait_list.append(item)
+                elif kind == "recv":
+                    pending[(what, c.buffer_id)] = item
+            elif isinstance(c, S.ProcessActivation):
+                wait_list.append(pending.pop(("act", c.buffer_id)))
+            elif isinstance(c, S.ProcessGrad):
+                wait_list.append(pending.pop(("grad", c.buffer_id)))
+            elif isinstance(c, (S.ForwardPass, S.BackwardPass)):
+                compute.append(dict(needs=wait_list, done=False))
+                wait_list = []
+    assert not pending
+    return comm, compute
+
+
+def _run_streams(cls, M, P, directional):
+    ranks = [_enqueue(cls, M, P, s, directional) for s in range(P)]
+    heads = [{k: 0 for k in comm} for comm, _ in ranks]
+    chead = [0] * P
+    progress = True
+    while progress:
+        progress = False
+        for s, (comm, compute) in enumerate(ranks):
+            while chead[s] < len(compute) and all(n["done"] for n in compute[chead[s]]["needs"]):
+                compute[chead[s]]["done"] = True
+                chead[s] += 1
+                progress = True
+        for s, (comm, compute) in enumerate(ranks):
+            for key, q in comm.items():
+                i = heads[s][key]
+                if i >= len(q) or chead[s] < q[i]["after"]:
+                    continue
+                peer = key[0] + 1 if key[0] == s else key[0]
+                pq = ranks[peer][0].get(key, [])
+                j = heads[peer][key] if key in heads[peer] else 0
+                if j >= len(pq) or chead[peer] < pq[j]["after"]:
+                    continue
+                a, b = q[i], pq[j]
+                if {a["kind"], b["kind"]} != {"send", "recv"}:
+                    continue                      # two receives (or two sends) face each other: neither can move
+                assert a["what"] == b["what"], f"{a} meets {b} on {key}"
+                a["done"] = b["done"] = True
+                heads[s][key] += 1
+                heads[peer][key] += 1
+                progress = True
+    finished = all(chead[s] == len(ranks[s][1]) for s in range(P)) and \
+        all(heads[s][k] == len(q) for s in range(P) for k, q in ranks[s][0].items())
+    return finished
+
+
+@settings(max_examples=80, deadline=None)
+@given(M=st.integers(1, 9), P=st.integers(2, 7), overlapped=st.booleans())
+def test_one_communicator_per_direction_never_stalls_on_ordered_streams(M, P, overlapped):
+    cls = S.OverlappedTrainSchedule if overlapped else S.TrainSchedule
+    assert _run_streams(cls, M, P, directional=True)
+
+
+def test_one_communicator_per_pair_stalls_under_the_overlapped_schedule():
+    """Why the links are split by direction: with a single communicator per pair the early receive of stage s
+    (gradient) and that of stage s + 1 (activation) face each other at the heads of the two streams."""
+    assert _run_streams(S.TrainSchedule, 4, 2, directional=False)
+    assert not _run_streams(S.OverlappedTrainSchedule, 4, 2, directional=False)

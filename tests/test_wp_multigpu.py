@@ -9,7 +9,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("n,sp", [(2, 1), (4, 1), (2, 2), (4, 2)])
+@pytest.mark.parametrize("n,sp", [(2, 1), (4, 1), (2, 2), (4, 2), (8, 1), (8, 2)])
 def test_wp_parity(n, sp):
     """Window parallelism (halo pulled from peer memory) and Ulysses sequence parallelism (head<->sequence exchange
     fused into the QKV GEMM epilogue and the attention epilogues) against the single-GPU result."""
@@ -48,9 +48,11 @@ def test_tensor_parallel_mlp(n):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
 
 
-@pytest.mark.parametrize("overlap", [0])
+@pytest.mark.parametrize("overlap", [0, 1])
 def test_pipeline_parallel_nccl(overlap):
-    """PP = 2 over NCCL p2p (1F1B) on the CUDA kernels against all stages on one GPU."""
+    """PP = 2 over NCCL p2p on the CUDA kernels against all stages on one GPU: plain 1F1B and the overlapped schedule
+    (receives posted a step early on per-direction communicators). The worker's process group has a short time-out,
+    so a transfer that never meets its counterpart ends the run with an error instead of waiting."""
     n = 2
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
