@@ -6,6 +6,13 @@ Training writes one file per *logical* pipeline stage, ``checkpoint_PP{stage}.pt
 (src/aeris/parallelism/parallel_engine.py:1119-1160). Files are loaded with ``weights_only=True``. Because files are
 per logical stage they do not depend on how many physical pipeline ranks wrote them.
 
+``optimizer_state_dict`` has the layout of ``torch.optim.AdamW.state_dict()``, which is what the reference stores
+(:1131): ``state`` maps the index of a parameter to ``{"step", "exp_avg", "exp_avg_sq"}`` and ``param_groups`` lists
+the indices with the hyper-parameters. Indices count the stage's parameters in ``named_parameters()`` order (the order
+of ``main_model.parameters()`` the reference builds its optimizer from, src/aeris/train.py:194-223), one group, or the
+reference's (decay, no-decay) pair of groups. Files written here also carry ``param_names`` so that loading does not
+depend on the order; a file without it (written by the reference) is mapped by position.
+
 Inference reads the per-stage files into one monolithic model (``input_stage.* / layers.{i}.* / output_stage.*``),
 always from ``ema_state_dict`` (src/aeris_wp_inference/model.py:479-495).
 """
@@ -58,13 +65,62 @@ def _integrity(ckpt: dict) -> dict:
     lets :func:`load_stage_checkpoint` reject a file whose payload was damaged (torch.load does not verify it)."""
     out = {}
     sections = {n: ckpt.get(n, {}) for n in ("model_state_dict", "main_model_state_dict", "ema_state_dict")}
-    osd = ckpt.get("optimizer_state_dict", {})
-    sections["optimizer/exp_avg"] = osd.get("exp_avg", {})
-    sections["optimizer/exp_avg_sq"] = osd.get("exp_avg_sq", {})
+    state = ckpt.get("optimizer_state_dict", {}).get("state", {})
+    sections["optimizer/exp_avg"] = {str(i): st["exp_avg"] for i, st in state.items() if "exp_avg" in st}
+    sections["optimizer/exp_avg_sq"] = {str(i): st["exp_avg_sq"] for i, st in state.items() if "exp_avg_sq" in st}
     for section, sd in sections.items():
         for k, t in sd.items():
             if torch.is_tensor(t) and t.dtype.is_floating_point:
                 out[f"{section}/{k}"] = float(torch.nan_to_num(t.double()).sum())
+    return out
+
+
+def _torch_optim_state(names: list[str], exp_avg: dict, exp_avg_sq: dict, opt) -> dict:
+    """``torch.optim.AdamW.state_dict()`` for one logical stage: ``names`` are all its parameters in order."""
+    c = opt.cfg
+    state = {}
+    for i, n in enumerate(names):
+        if n in exp_avg:
+            state[i] = {"step": torch.tensor(float(opt.step_count)), "exp_avg": exp_avg[n].cpu(),
+                        "exp_avg_sq": exp_avg_sq[n].cpu()}
+    group = {"lr": float(getattr(opt, "last_lr", c.lr)), "betas": tuple(c.betas), "eps": c.eps,
+             "weight_decay": c.weight_decay, "amsgrad": False, "maximize": False, "foreach": None, "capturable": False,
+             "differentiable": False, "fused": None, "params": list(range(len(names)))}
+    return {"state": state, "param_groups": [group], "param_names": list(names)}
+
+
+def _read_optim_state(osd: dict, names: list[str]) -> tuple[int, dict, dict]:
+    """(step, exp_avg by name, exp_avg_sq by name) from a ``torch.optim`` state dict of one stage. ``names``: the
+    stage's parameters in ``named_parameters()`` order, used when the file does not name them itself."""
+    if "state" not in osd or "param_groups" not in osd:
+        raise ValueError("optimizer_state_dict is not a torch.optim state dict")
+    order = [i for g in osd["param_groups"] for i in g["params"]]
+    file_names = osd.get("param_names")
+    if file_names is None:
+        if len(order) != len(names):
+            raise ValueError(f"optimizer state covers {len(order)} parameters, the stage has {len(names)}")
+        file_names = names
+    by_index = {i: file_names[pos] for pos, i in enumerate(order)}
+    m, v, step = {}, {}, 0
+    for i, st in osd["state"].items():
+        name = by_index[int(i)]
+        m[name], v[name] = st["exp_avg"], st["exp_avg_sq"]
+        step = max(step, int(float(st["step"])))
+    return step, m, v
+
+
+def _stage_param_names(module) -> dict[int, list[str]]:
+    """Per logical stage, the reference-style names of all parameters in registration order."""
+    out: dict[int, list[str]] = {}
+    last = _n_logical(module) - 1
+    for k, _ in module.named_parameters():
+        if k.startswith("input_stage."):
+            out.setdefault(0, []).append(k[len("input_stage."):])
+        elif k.startswith("output_stage."):
+            out.setdefault(last, []).append(k[len("output_stage."):])
+        elif k.startswith("layers."):
+            _, idx, rest = k.split(".", 2)
+            out.setdefault(int(idx) + 1, []).append(rest)
     return out
 
 
@@ -75,11 +131,16 @@ def save_stage_checkpoint(directory: str, module, opt, it: int | None = None, wr
     if write:
         os.makedirs(directory, exist_ok=True)
     model_sd = _logical(module, module.state_dict())
+    if hasattr(opt, "host_copies"):
+        opt.host_copies = write        # a sharded optimizer gathers collectively; only the writer copies to the host
     master = _logical(module, dict(opt.master_state_dict()))
     ema = _logical(module, dict(opt.ema_state_dict())) if opt.cfg.use_ema else {}
     osd = opt.state_dict()
+    if hasattr(opt, "host_copies"):
+        opt.host_copies = True
     exp_avg = _logical(module, osd["exp_avg"])
     exp_avg_sq = _logical(module, osd["exp_avg_sq"])
+    names = _stage_param_names(module)
     written = []
     if not write:
         return written
@@ -90,9 +151,8 @@ def save_stage_checkpoint(directory: str, module, opt, it: int | None = None, wr
             "cur_nimg": int(opt.cur_nimg),
             "model_state_dict": {k: v.detach().cpu().clone() for k, v in sd.items()},
             "main_model_state_dict": full_master,
-            "optimizer_state_dict": {"step": int(opt.step_count),
-                                     "exp_avg": {k: v.cpu() for k, v in exp_avg.get(stage, {}).items()},
-                                     "exp_avg_sq": {k: v.cpu() for k, v in exp_avg_sq.get(stage, {}).items()}},
+            "optimizer_state_dict": _torch_optim_state(names.get(stage, []), exp_avg.get(stage, {}),
+                                                       exp_avg_sq.get(stage, {}), opt),
         }
         if opt.cfg.use_ema:
             full_ema = dict(full_master)
@@ -113,29 +173,34 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     if not directory:
         return False
     loaded = {}
+    names = _stage_param_names(module)
+    model_sd, master, ema, m, v = {}, {}, {}, {}, {}
+    step = 0
     for stage in _stage_ids(module):
         try:
             ck = torch.load(_fname(directory, stage), map_location="cpu", weights_only=True)
             if "integrity" in ck:
                 now = _integrity(ck)
-                for k, v in ck["integrity"].items():
-                    if not (abs(now.get(k, float("nan")) - v) <= 1e-9 * max(1.0, abs(v))):
+                for k, val in ck["integrity"].items():
+                    if not (abs(now.get(k, float("nan")) - val) <= 1e-9 * max(1.0, abs(val))):
                         raise ValueError(f"checkpoint payload damaged: {k}")
+            st_step, st_m, st_v = _read_optim_state(ck["optimizer_state_dict"], names.get(stage, []))
+            for k, t in ck["model_state_dict"].items():
+                model_sd[_key_for(module, stage, k)] = t
+            for k, t in ck["main_model_state_dict"].items():
+                master[_key_for(module, stage, k)] = t
+            for k, t in ck.get("ema_state_dict", {}).items():
+                ema[_key_for(module, stage, k)] = t
+            for k, t in st_m.items():
+                m[_key_for(module, stage, k)] = t
+            for k, t in st_v.items():
+                v[_key_for(module, stage, k)] = t
+            step = max(step, st_step)
             loaded[stage] = ck
-        except Exception:
+        except Exception as e:      # missing, unreadable, damaged or foreign file: nothing has been touched yet
+            import logging
+            logging.getLogger(__name__).warning("checkpoint of stage %d in %s not loaded: %s", stage, directory, e)
             return False
-    model_sd, master, ema, m, v = {}, {}, {}, {}, {}
-    for stage, ck in loaded.items():
-        for k, t in ck["model_state_dict"].items():
-            model_sd[_key_for(module, stage, k)] = t
-        for k, t in ck["main_model_state_dict"].items():
-            master[_key_for(module, stage, k)] = t
-        for k, t in ck.get("ema_state_dict", {}).items():
-            ema[_key_for(module, stage, k)] = t
-        for k, t in ck["optimizer_state_dict"]["exp_avg"].items():
-            m[_key_for(module, stage, k)] = t
-        for k, t in ck["optimizer_state_dict"]["exp_avg_sq"].items():
-            v[_key_for(module, stage, k)] = t
     first = next(iter(loaded.values()))
     # parameters are views of the optimizer's flat buffers, so loading the masters refreshes the model copies too;
     # buffers and frozen parameters come from the model state dict
@@ -144,8 +209,8 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     for k, t in model_sd.items():
         if k in own and k not in managed:
             own[k].copy_(t)
-    opt.load_state_dict({"step": first["optimizer_state_dict"]["step"], "cur_nimg": first["cur_nimg"],
-                         "exp_avg": m, "exp_avg_sq": v}, master=master, ema=ema or None)
+    opt.load_state_dict({"step": step, "cur_nimg": first["cur_nimg"], "exp_avg": m, "exp_avg_sq": v},
+                        master=master, ema=ema or None)
     return True
 
 

@@ -110,23 +110,56 @@ class DistOptimizer(FlatOptimizer):
         dist.all_gather(parts, src, group=self.group)
         target.copy_(torch.cat(parts))
 
-    def save_shard(self, directory: str, pp: int, sp: int):
-        os.makedirs(directory, exist_ok=True)
-        sd = {"step": self.step_count, "cur_nimg": self.cur_nimg, "group_rank": self.grank, "world": self.world,
-              "segments": [{"name": s.name, "master": s.master_shard.cpu(), "m": s.m.cpu(), "v": s.v.cpu(),
-                            "ema": None if s.ema is None else s.ema.cpu()} for s in self.segments]}
-        torch.save(sd, os.path.join(directory, f"distopt_PP{pp}_shard{self.grank}.pth"))
+    # ---- state for checkpoints: gathered over the group (collective), in the layout of FlatOptimizer ----------------
+    host_copies = True      # False on ranks that only take part in the gathers of a checkpoint another rank writes
 
-    def load_shard(self, directory: str, pp: int) -> bool:
-        try:
-            sd = torch.load(os.path.join(directory, f"distopt_PP{pp}_shard{self.grank}.pth"), map_location="cpu",
-                            weights_only=True)
-        except Exception:
-            return False
-        assert sd["world"] == self.world, "sharded optimizer state was written by a different group size"
-        self.step_count, self.cur_nimg = sd["step"], sd["cur_nimg"]
-        for s, d in zip(self.segments, sd["segments"]):
-            s.master_shard.copy_(d["master"]); s.m.copy_(d["m"]); s.v.copy_(d["v"])
-            if s.ema is not None and d["ema"] is not None:
-                s.ema.copy_(d["ema"])
-        return True
+    def _gather_full(self, s, which: str) -> torch.Tensor | None:
+        shard = {"m": s.m, "v": s.v, "master": s.master_shard, "ema": s.ema}[which]
+        if shard is None:
+            return None
+        if self.world == 1:
+            return shard
+        if dist.get_backend(self.group) == "nccl":
+            full = torch.empty(s.shard * self.world, dtype=shard.dtype, device=shard.device)
+            dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+        else:
+            parts = [torch.empty_like(shard) for _ in range(self.world)]
+            dist.all_gather(parts, shard.contiguous(), group=self.group)
+            full = torch.cat(parts)
+        return full.cpu() if self.host_copies else None
+
+    def _named_views(self, which: str) -> dict[str, torch.Tensor]:
+        out = {}
+        for s in self.segments:
+            full = self._gather_full(s, which)
+            if full is None:
+                continue
+            off = 0
+            for n, p in zip(s.names, s.params):
+                out[n] = full[off:off + p.numel()].view(p.shape)
+                off += (p.numel() + 15) // 16 * 16
+        return out
+
+    def load_state_dict(self, sd: dict, master: dict | None = None, ema: dict | None = None):
+        """Every rank reads the full named arrays and keeps its shard; the working copy of the weights is rebuilt from
+        the masters on every rank."""
+        self.step_count, self.cur_nimg = int(sd["step"]), int(sd["cur_nimg"])
+        sources = {"m": sd.get("exp_avg"), "v": sd.get("exp_avg_sq"), "master": master, "ema": ema}
+        for s in self.segments:
+            for which, named in sources.items():
+                dst = {"m": s.m, "v": s.v, "master": s.master_shard, "ema": s.ema}[which]
+                if named is None or dst is None:
+                    continue
+                off = 0
+                for n, p in zip(s.names, s.params):
+                    cnt = p.numel()
+                    if n in named:
+                        src = named[n].reshape(-1).to(dst.device, torch.float32)
+                        a, b = max(off, s.lo), min(off + cnt, s.lo + s.shard)      # overlap with this rank's shard
+                        if a < b:
+                            dst[a - s.lo:b - s.lo].copy_(src[a - off:b - off])
+                        if which == "master":
+                            s.master[off:off + cnt].copy_(src)
+                            if s.model_flat is not None:
+                                s.model_flat[off:off + cnt].copy_(src.to(s.model_flat.dtype))
+                    off += (cnt + 15) // 16 * 16

@@ -177,12 +177,14 @@ class FusedShardedOptimizer:
         return self._sumsq
 
     # ---- state in the layout of FlatOptimizer (collective: every rank of the group calls, all get the full dicts) ------
-    def _gather_full(self, s, shard: torch.Tensor) -> torch.Tensor:
+    host_copies = True      # False on ranks that only take part in the gathers of a checkpoint another rank writes
+
+    def _gather_full(self, s, shard: torch.Tensor) -> torch.Tensor | None:
         if not s.low_precision:
-            return shard.detach().cpu().clone()
+            return shard.detach().cpu().clone() if self.host_copies else None
         full = torch.empty(s.padded, dtype=torch.float32, device=self.device)
         dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
-        out = full.cpu()
+        out = full.cpu() if self.host_copies else None
         del full
         return out
 
@@ -193,6 +195,8 @@ class FusedShardedOptimizer:
             if shard is None:
                 continue
             full = self._gather_full(s, shard)
+            if full is None:
+                continue
             for name, p, off in zip(s.names, s.params, s.offs):
                 out[name] = full[off:off + p.numel()].view(p.shape)
         return out

@@ -337,12 +337,15 @@ class ParallelEngine:
 
     # checkpoints ---------------------------------------------------------------------------------------------------
     def save_checkpoint(self):
+        """One file per logical stage, written by the head rank of each pipeline stage between two barriers (:1225-1234).
+        With the distributed optimizer the state is sharded over the weight group: every rank takes part in the gathers
+        and the head rank writes the same files (the reference cannot checkpoint in that mode, :1120-1122)."""
         dist.barrier() if dist.is_initialized() else None
-        if self.rank in self.grid.stage_heads() and not self.ecfg.dist_optimizer:
+        head = self.rank in self.grid.stage_heads()
+        if head or self.ecfg.dist_optimizer:
             numbered = self.cur_it % self.ecfg.checkpoint_keep_every == 0 and self.cur_it > 0
-            save_stage_checkpoint(self.ecfg.checkpoint_dir, self.module, self.opt, it=self.cur_it if numbered else None)
-        elif self.ecfg.dist_optimizer and self.c.dp == 0 and self.c.wp_y == 0 and self.c.wp_x == 0:
-            self.opt.save_shard(self.ecfg.checkpoint_dir, self.c.pp, self.c.sp)
+            save_stage_checkpoint(self.ecfg.checkpoint_dir, self.module, self.opt, it=self.cur_it if numbered else None,
+                                  write=head)
         dist.barrier() if dist.is_initialized() else None
 
     def load_checkpoint(self) -> bool:

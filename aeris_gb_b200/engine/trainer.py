@@ -186,7 +186,12 @@ class Trainer:
         if read_loss:
             # a bounded device wait that ran out (a peer that never signalled) leaves incomplete activations or
             # gradients behind: raise before the optimizer applies them and the all-gather spreads them
-            self.check_device()
+            try:
+                self.check_device()
+            except Exception:
+                for buf in self.opt.grad_buffers():
+                    buf.zero_()
+                raise
         with self.timers.region("reduce_step"):
             self.reduce_and_step(B)
         self.step_count += 1
@@ -196,6 +201,14 @@ class Trainer:
         value = float(self.last_loss.item()) / B
         self.check_device()
         return value
+
+    def resume(self, cur_nimg: int, gas: int = 1) -> None:
+        """After a checkpoint load: continue the step counter (it seeds the counter-based noise of the fused input
+        kernels) and the noise / noise-level generators where a run of ``cur_nimg`` images would be, instead of
+        replaying the draws of step 0 (parallel_engine.py:1155-1156)."""
+        self.step_count = cur_nimg // max(1, gas * self.dp_size)
+        self.rng.manual_seed(self.seed + 1000 * self.dp_rank + self.wp_rank + cur_nimg)
+        self.nl_rng.manual_seed(self.seed + self.dp_rank + cur_nimg)
 
     def check_device(self) -> None:
         """Raise ``KernelError`` if a kernel of this library recorded a device-side error (time-out of a bounded wait,

@@ -43,3 +43,45 @@ def test_pp_generate_cli_two_stage_pipeline():
                 "--rollout-steps", "1", "--sampler-steps", "2"], nproc=2)
     rec = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
     assert rec["PP"] == 2 and rec["network_evaluations"] == 3
+
+
+def test_resumed_trainer_does_not_replay_the_first_noise_draws(tmp_path):
+    """step, save, reload into a fresh trainer, resume: the next noise level and noise differ from those of step 0,
+    the step counter that seeds the fused input kernels continues (parallel_engine.py:1155-1156, train.py:247)."""
+    import torch
+    from aeris_gb_b200.engine.checkpoint import load_stage_checkpoint, save_stage_checkpoint
+    from aeris_gb_b200.engine.optim import OptimConfig
+    from aeris_gb_b200.engine.trainer import DiffusionConfig, Trainer
+    from aeris_gb_b200.models.aeris import AerisConfig
+    from aeris_gb_b200.diffusion import trigflow as TF
+    cfg = AerisConfig(img=(16, 32), window=(8, 8), in_channels=10, out_channels=4, dim=32, heads=2, head_dim=16,
+                      mlp_dim=64, n_layers=2, sublayers=1, model_dtype=torch.float32)
+    dc = DiffusionConfig(cond_channels=6)
+
+    def draws(tr):
+        t = TF.sample_noise_level(1, dc.sigma_min, dc.sigma_max, dc.sigma_data, generator=tr.nl_rng, device="cpu")
+        return t, torch.randn(8, generator=tr.rng)
+    fresh = Trainer(cfg, OptimConfig(), dc, "cpu", seed=3)
+    t0, z0 = draws(fresh)
+    tr = Trainer(cfg, OptimConfig(), dc, "cpu", seed=3)
+    g = torch.Generator().manual_seed(0)
+    x, c = torch.randn(2, 16, 32, 4, generator=g), torch.randn(2, 16, 32, 6, generator=g)
+    tr.train_step(x, c)
+    save_stage_checkpoint(str(tmp_path), tr.model, tr.opt)
+    tr2 = Trainer(cfg, OptimConfig(), dc, "cpu", seed=3)
+    assert load_stage_checkpoint(str(tmp_path), tr2.model, tr2.opt, "cpu")
+    tr2.resume(tr2.opt.cur_nimg, gas=2)
+    assert tr2.step_count == 1 and tr2.opt.cur_nimg == 2
+    t1, z1 = draws(tr2)
+    assert not torch.equal(t1, t0) and not torch.equal(z1, z0)
+
+
+def test_stage_metric_names_follow_the_reference():
+    import torch
+    from aeris_gb_b200.cli.train import stage_metrics
+    from aeris_gb_b200.models.aeris import AerisConfig, SwinLayer
+    cfg = AerisConfig(img=(16, 32), window=(8, 8), in_channels=10, out_channels=4, dim=32, heads=2, head_dim=16,
+                      mlp_dim=64, n_layers=2, sublayers=1, model_dtype=torch.float32)
+    m = stage_metrics({1: SwinLayer(cfg)}, 2.5, 1, 4, {"ForwardPass": 0.1})
+    assert set(m) == {"train/stage_norm/stage_norm_1", "train/weight_norm/stage_1/0_modulation_0",
+                      "train/weight_norm/stage_1/0_modulation_2", "train/pp_timers/ForwardPass/rank_1"}

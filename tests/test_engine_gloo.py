@@ -170,3 +170,66 @@ def test_checkpoint_roundtrip_across_pipeline_splits(single):
     # resume the second iteration on a 2-stage pipeline: must land on the single-process 2-iteration weights
     sd, _, _ = _launch(2, PP=2, WP=(1, 1), gas=4, iters=1, ckpt_dir=ck, resume=True)
     _assert_same(sd, single[0])
+
+
+def test_dp2_distributed_optimizer_checkpoint_resumes(single):
+    """The sharded optimizer state is gathered into the per-stage files and scattered back: one iteration, save,
+    reload on two ranks, second iteration lands on the single-process two-iteration weights."""
+    ck = tempfile.mkdtemp()
+    _launch(2, PP=1, WP=(1, 1), gas=2, iters=1, distopt=True, ckpt_dir=ck)
+    assert sorted(os.listdir(ck)) == [f"checkpoint_PP{i}.pth" for i in range(6)]
+    sd, _, _ = _launch(2, PP=1, WP=(1, 1), gas=2, iters=1, distopt=True, ckpt_dir=ck, resume=True)
+    _assert_same(sd, single[0])
+
+
+def test_checkpoint_with_the_references_optimizer_layout_loads(tmp_path):
+    """A file whose ``optimizer_state_dict`` is what ``torch.optim.AdamW.state_dict()`` returns for the stage's
+    parameter list (no names, positions only: parallel_engine.py:1128-1137) resumes; a foreign layout is refused
+    without touching the model."""
+    from aeris_gb_b200.engine.checkpoint import load_stage_checkpoint, save_stage_checkpoint
+    from aeris_gb_b200.engine.optim import FlatOptimizer
+    from aeris_gb_b200.models.aeris import AerisModel
+    torch.manual_seed(0)
+    model = AerisModel(_cfg())
+    opt = FlatOptimizer(model, OptimConfig())
+    for s in opt.segments:
+        s.m.normal_(); s.v.uniform_()
+    opt.step_count, opt.cur_nimg = 7, 28
+    save_stage_checkpoint(str(tmp_path), model, opt)
+    m_ref = {k: v.clone() for k, v in opt.state_dict()["exp_avg"].items()}
+    # rewrite stage 1 the way torch would: state keyed by position, parameters without names
+    f = os.path.join(tmp_path, "checkpoint_PP1.pth")
+    ck = torch.load(f, weights_only=True)
+    layer = torch.nn.ModuleList([p for p in [model.layers[0]]])[0]
+    plist = [torch.nn.Parameter(p.detach().float().clone()) for _, p in layer.named_parameters()]
+    ref_opt = torch.optim.AdamW(plist, lr=1e-3)
+    for p in plist:
+        p.grad = torch.zeros_like(p)
+    ref_opt.step()
+    tsd = ref_opt.state_dict()
+    own = ck["optimizer_state_dict"]
+    for i, name in enumerate(own["param_names"]):
+        if i in own["state"]:
+            tsd["state"][i]["exp_avg"] = own["state"][i]["exp_avg"]
+            tsd["state"][i]["exp_avg_sq"] = own["state"][i]["exp_avg_sq"]
+            tsd["state"][i]["step"] = torch.tensor(7.0)
+        else:
+            tsd["state"].pop(i, None)
+    assert "param_names" not in tsd
+    ck["optimizer_state_dict"] = tsd
+    ck.pop("integrity")
+    torch.save(ck, f)
+    model2 = AerisModel(_cfg())
+    opt2 = FlatOptimizer(model2, OptimConfig())
+    assert load_stage_checkpoint(str(tmp_path), model2, opt2, "cpu")
+    assert opt2.step_count == 7 and opt2.cur_nimg == 28
+    got = opt2.state_dict()["exp_avg"]
+    for k in m_ref:
+        assert torch.equal(got[k], m_ref[k]), k
+    # an optimizer section in some other layout: refused, nothing loaded
+    ck["optimizer_state_dict"] = {"step": 7, "moments": {}}
+    torch.save(ck, f)
+    model3 = AerisModel(_cfg())
+    before = {k: v.clone() for k, v in model3.state_dict().items()}
+    assert not load_stage_checkpoint(str(tmp_path), model3, FlatOptimizer(model3, OptimConfig()), "cpu")
+    assert all(torch.equal(v, before[k]) for k, v in model3.state_dict().items())

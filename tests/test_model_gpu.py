@@ -121,3 +121,30 @@ def test_wide_block_dim5120_matches_oracle():
     assert rel_err(y1, y0) < 3e-2
     assert rel_err(gx1, gx0) < 6e-2
     assert rel_err(gw1, gw0) < 8e-2
+
+
+def test_train_step_raises_on_a_device_timeout_instead_of_stepping():
+    """A bounded device wait that runs out (here: a wait on a flag that nothing sets, queued ahead of the step) must
+    surface as KernelError from train_step before the optimizer touches the weights; the trainer stays usable."""
+    import ctypes
+    from aeris_gb_b200.engine.optim import OptimConfig
+    from aeris_gb_b200.engine.trainer import DiffusionConfig, Trainer
+    from aeris_gb_b200.ops import lib as L
+    cfg = _small_cfg()
+    tr = Trainer(cfg, OptimConfig(), DiffusionConfig(cond_channels=cfg.in_channels - cfg.out_channels), "cuda:0")
+    x = torch.randn(1, 32, 64, cfg.out_channels).pin_memory()
+    c = torch.randn(1, 32, 64, cfg.in_channels - cfg.out_channels).pin_memory()
+    tr.train_step(x, c)
+    before = [p.detach().clone() for p in tr.model.parameters()]
+    steps = tr.opt.step_count
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = L.lib().aeris_wait_flag(L.ptr(flag), ctypes.c_uint(1), L.ptr(L.status_word()), ctypes.c_double(0.3),
+                                 L.stream_ptr())
+    assert rc == 0
+    with pytest.raises(L.KernelError, match="peer signal"):
+        tr.train_step(x, c)
+    assert tr.opt.step_count == steps
+    assert all(torch.equal(a, b.detach()) for a, b in zip(before, tr.model.parameters()))
+    assert all(float(g.abs().max()) == 0.0 for g in tr.opt.grad_buffers())
+    loss = tr.train_step(x, c)              # status cleared, gradients dropped: the next step runs normally
+    assert loss == loss and tr.opt.step_count == steps + 1
