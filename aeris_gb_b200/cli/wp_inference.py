@@ -6,8 +6,11 @@
 Reference: src/aeris_wp_inference/inference.py (argparse CLI :24-41, rollout :43-198, mesh [DP, SP=WP] :215-231,
 checkpoint conversion :281, strided initial conditions :302-314). Two layouts: every member window-parallel over all
 GPUs (the reference's), or one member per GPU (``--member-parallel``: no halo traffic at all, members are independent
-until the metrics). The state stays on the device for the whole rollout. Without ``--data`` synthetic N(0,1) initial
-states and forcings are used, and with ``--random-init`` random weights (benchmarking without a checkpoint).
+until the metrics). The state stays on the device for the whole rollout. ``--data FILE`` (``--data-root`` = folder of
+the statistics files) reads initial conditions every ``--stride-ic`` samples, split over the data-parallel replicas,
+with forcings and verification fields from the file, dataset statistics for the (un)standardisation and, with
+``--out``, the rollout of every window-parallel tile written per forecast step. Without ``--data`` synthetic N(0,1)
+initial states and forcings are used, and with ``--random-init`` random weights (benchmarking without a checkpoint).
 """
 from __future__ import annotations
 
@@ -106,8 +109,21 @@ def main(argv=None):
         out = out.view(B, g.nwy_loc, g.nwx_loc, g.ws_y, g.ws_x, -1).permute(0, 1, 3, 2, 4, 5)
         return out.reshape(B, hb, wb, -1).float()
 
-    stats = {k: torch.zeros(C_out, device=device) if "mean" in k else torch.ones(C_out, device=device)
-             for k in ("x_mean", "x_std", "t_mean", "t_std")}
+    wp_yx = (wp_rank // wp[1], wp_rank % wp[1])
+    data = None
+    if a.data:
+        from ..data.inference_data import InferenceData, RolloutWriter, strided_indices
+        data = InferenceData(a.data, a.data_root, (H, W), wp, wp_yx, interval=int(cfg.model.get("interval", 6)),
+                             rollout_steps=steps, out_channels=C_out,
+                             channels=73 if C_f > 0 else 69)
+        stats = data.stats(device)
+        # window-parallel: the replicas share the initial conditions out; member-parallel: every rank sees all of them
+        all_ic, my_ic = strided_indices(data.ds.ds.shape[0], steps, data.dt, a.stride_ic,
+                                        0 if a.member_parallel else dp_rank, 1 if a.member_parallel else dp)
+    else:
+        stats = {k: torch.zeros(C_out, device=device) if "mean" in k else torch.ones(C_out, device=device)
+                 for k in ("x_mean", "x_std", "t_mean", "t_std")}
+        all_ic = my_ic = [0]
     gen = torch.Generator(device=device).manual_seed(a.seed * 1000 + rank)
     if device.type == "cuda":     # sampler, (un)standardisation, embedding and head on the CUDA kernels
         fc = DeviceForecaster(model, ctx, stats, sampler, C_out, seed=a.seed,
@@ -120,30 +136,60 @@ def main(argv=None):
     g0 = torch.Generator().manual_seed(a.seed)
     state_full = torch.randn(H, W, C_out, generator=g0)
     truth_full = [torch.randn(H, W, C_out, generator=g0) for _ in range(steps)] if a.debug else None
-    state = shard_block(state_full.unsqueeze(0), wp, (wp_rank // wp[1], wp_rank % wp[1])).to(device).repeat(max(M, 1), 1, 1, 1)
-    forcing = torch.randn(max(M, 1), hb, wb, C_f, generator=gen, device=device) if C_f > 0 else None
+    syn_forcing = torch.randn(max(M, 1), hb, wb, C_f, generator=gen, device=device) if C_f > 0 else None
+    writer = None
+    if a.out and data is not None and M > 0:
+        stem = f"rollout-{len(all_ic)}i-{steps}s-{a.members}m" + (f"_dp{dp_rank}" if dp > 1 else "")
+        writer = RolloutWriter(a.out, stem, wp_yx, len(my_ic), steps, M, C_out, hb, wb)
     times = []
+    cur = {}
 
     def on_step(k, x):
         if device.type == "cuda":
             torch.cuda.synchronize()
+            from ..ops import lib as L
+            L.check_status(sync=False)         # a bounded device wait that ran out ends the rollout here
         times.append(time.perf_counter())
+        if writer is not None:
+            writer.put(cur["ic"], k + 1, x)
         if a.member_parallel and world > 1:
             allm = [torch.empty_like(x) for _ in range(world)]
             dist.all_gather(allm, x)
             mem = torch.cat(allm).permute(0, 3, 1, 2)
         else:
             mem = x.permute(0, 3, 1, 2)
-        label = (truth_full[k] if truth_full is not None else state_full)
-        label = shard_block(label.unsqueeze(0), wp, (wp_rank // wp[1], wp_rank % wp[1]))[0].to(device).permute(2, 0, 1)
-        metrics.update(k, mem, label, w_lat_blk)
+        metrics.update(k, mem, cur["truth"](k), w_lat_blk)
 
     t_start = time.perf_counter()
     times.append(t_start)
-    if M > 0:
-        fc.rollout(state, (lambda k: forcing), steps, generator=gen, on_step=on_step)
-    metrics.end_initial_condition()
+    for n, idx in enumerate(my_ic):
+        if data is not None:
+            smp = data.sample(idx)
+            state = smp["state"].to(device).unsqueeze(0).repeat(max(M, 1), 1, 1, 1)
+            f_all = smp["forcing"].to(device) if smp["forcing"] is not None else None
+            forcings = (lambda k: f_all[k].unsqueeze(0).expand(max(M, 1), -1, -1, -1)) if f_all is not None else None
+            truth = smp["truth"].to(device)
+            cur.update(ic=n, truth=lambda k: truth[k].permute(2, 0, 1))
+        else:
+            state = shard_block(state_full.unsqueeze(0), wp, wp_yx).to(device).repeat(max(M, 1), 1, 1, 1)
+            forcings = (lambda k: syn_forcing) if syn_forcing is not None else None
+            label = lambda k: shard_block((truth_full[k] if truth_full is not None else state_full).unsqueeze(0), wp,
+                                          wp_yx)[0].to(device).permute(2, 0, 1)
+            cur.update(ic=n, truth=label)
+        if writer is not None:
+            writer.put(n, 0, state)
+        if M > 0:
+            fc.rollout(state, forcings, steps, generator=gen, on_step=on_step)
+        metrics.end_initial_condition()
+    if dp > 1 and not a.member_parallel:        # scores of the replicas' initial conditions in one packed reduction
+        packed = torch.cat([metrics.err.reshape(-1), torch.tensor([float(metrics.count)], device=device,
+                                                                  dtype=torch.float64)])
+        dist.all_reduce(packed)
+        metrics.err = packed[:-1].view_as(metrics.err) / n_wp       # every WP rank of a replica holds the same sums
+        metrics.count = int(round(packed[-1].item() / n_wp))
     agg, scores = metrics.finalize()
+    if writer is not None:
+        writer.close()
     per_step = float(np.mean(np.diff(times))) if len(times) > 1 else float("nan")
     if a.out and rank == 0:
         os.makedirs(a.out, exist_ok=True)
