@@ -214,6 +214,28 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     return True
 
 
+def load_stage_weights(directory: str, module, use_ema: bool = True) -> bool:
+    """Inference: only the weights of the module's logical stages, from ``ema_state_dict`` (or ``model_state_dict``),
+    as the reference's inference engine does (src/aeris/parallelism/sp_inference_engine.py:552-573)."""
+    which = "ema_state_dict" if use_ema else "model_state_dict"
+    new = {}
+    try:
+        for stage in _stage_ids(module):
+            ck = torch.load(_fname(directory, stage), map_location="cpu", weights_only=True)
+            for k, t in (ck[which] if which in ck else ck["model_state_dict"]).items():
+                new[_key_for(module, stage, k)] = t
+    except Exception as e:
+        import logging
+        logging.getLogger(__name__).warning("weights in %s not loaded: %s", directory, e)
+        return False
+    own = module.state_dict()
+    with torch.no_grad():
+        for k, t in new.items():
+            if k in own:
+                own[k].copy_(t.to(own[k].dtype))
+    return True
+
+
 def convert_inference_checkpoint(path: str, n_logical: int, model, map_location="cpu", use_ema: bool = True,
                                  strict: bool = True) -> dict:
     """Per-stage files -> one state dict for :class:`AerisModel`, then ``model.load_state_dict``. Takes

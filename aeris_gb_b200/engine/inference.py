@@ -37,6 +37,14 @@ class InferenceEngine(ParallelEngine):
             self.links.peer["result"] = self.last_rank if self.is_first_stage() else self.first_rank
         self._imap.update({SCH.SendResult: self.send_result, SCH.ReturnResult: self.return_result})
 
+    def load_checkpoint(self, load_ema: bool = True) -> bool:
+        """Weights only, the EMA copy by default (sp_inference_engine.py:552-573)."""
+        from .checkpoint import load_stage_weights
+        ok = load_stage_weights(self.ecfg.checkpoint_dir, self.module, use_ema=load_ema)
+        if dist.is_initialized():
+            dist.barrier()
+        return ok
+
     def load(self, buffer_id):
         """Micro-batch = member: the caller's model input rows for member ``_mb`` and the shared noise level."""
         self.buf["inputs"][buffer_id] = self._model_in[self._mb]
