@@ -32,9 +32,18 @@ from ..utils.timers import tflops_per_gpu, wandb_payload
 
 
 def build_dataset(cfg, mcfg, wp_rank, channels):
+    rti = mcfg.rit and not mcfg.diffusion
     if cfg.data.get("synthetic", False) or not cfg.data.get("root"):
-        return SyntheticERA5(img=mcfg.img, cond_channels=channels["condition"], target_channels=channels["label"],
-                             wp=mcfg.wp, wp_rank=wp_rank, seed=int(cfg.seed))
+        cond = channels["condition"] if mcfg.diffusion else channels["model_in"]
+        return SyntheticERA5(img=mcfg.img, cond_channels=cond, target_channels=channels["label"],
+                             wp=mcfg.wp, wp_rank=wp_rank, seed=int(cfg.seed), intervals=(6, 12, 24) if rti else None)
+    if rti:
+        from ..data.era5 import ERA5NRMRTIDataset
+        ds = ERA5NRMRTIDataset(cfg.data.dataset.root, cfg.data.root, interval=int(cfg.model.interval),
+                               channels=channels["dataset"], seed=int(cfg.seed))
+        ds.open_file(wp_rank[0], wp_rank[1], benchmark=bool(cfg.model.get("benchmark", False)),
+                     data_shape=(30, channels["dataset"], mcfg.img[0] // mcfg.wp[0], mcfg.img[1] // mcfg.wp[1]))
+        return _ChannelsLast(ds)
     from ..data.era5 import ERA5NRMDataset
     ds = ERA5NRMDataset(cfg.data.dataset.root, cfg.data.root, interval=int(cfg.model.interval),
                         channels=channels["dataset"])
@@ -52,8 +61,8 @@ class _ChannelsLast(torch.utils.data.Dataset):
         return len(self.ds)
 
     def __getitem__(self, i):
-        x, t = self.ds[i]
-        return x.permute(1, 2, 0).contiguous(), t.permute(1, 2, 0).contiguous()
+        x, t, *rest = self.ds[i]
+        return (x.permute(1, 2, 0).contiguous(), t.permute(1, 2, 0).contiguous(), *rest)
 
 
 def _module_norm(module) -> float:
@@ -151,8 +160,9 @@ def main(argv=None):
             cond = torch.cat([b[0] for b in batch]).pin_memory() if device.type == "cuda" else torch.cat([b[0] for b in batch])
             tgt = torch.cat([b[1] for b in batch]).pin_memory() if device.type == "cuda" else torch.cat([b[1] for b in batch])
             tgt = injector.poison(tgt, rank, it)
+            interval = torch.cat([b[2] for b in batch]).reshape(-1) if len(batch[0]) > 2 else None
             t0 = time.perf_counter()
-            loss = trainer.train_step(tgt, cond)
+            loss = trainer.train_step(tgt, cond, interval=interval)
             dt = time.perf_counter() - t0
             check_finite("loss", loss)
             tf = tflops_per_gpu(mcfg.flops_per_sample(), gas * grid.DP, dt, world)
@@ -188,8 +198,7 @@ def main(argv=None):
         holder = {}
 
         def data_fn(_eng):
-            cnd, tg = next(holder["loader"])
-            return cnd, tg
+            return next(holder["loader"])        # (condition, target[, interval])
         eng = ParallelEngine(mcfg, ocfg, dcfg, ecfg, grid, rank, device, data_fn=data_fn)
         eng.warmup()
         if cfg.model.get("load"):

@@ -9,11 +9,15 @@ from torch.utils.data import Dataset
 
 class SyntheticERA5(Dataset):
     def __init__(self, img=(720, 1440), cond_channels=74, target_channels=70, wp=(1, 1), wp_rank=(0, 0),
-                 length: int = 4096, seed: int = 0, pool: int = 4, channels_last: bool = True):
+                 length: int = 4096, seed: int = 0, pool: int = 4, channels_last: bool = True,
+                 intervals: tuple | None = None):
         self.hb, self.wb = img[0] // wp[0], img[1] // wp[1]
         self.cc, self.ct, self.length, self.seed, self.pool = cond_channels, target_channels, length, seed, pool
         self.rank_id = wp_rank[0] * wp[1] + wp_rank[1]
         self.channels_last = channels_last
+        # random-time-interval training (reference ERA5NRMRTIDataset): every item also carries its forecast interval in
+        # hours, a function of (seed, index) only so that every rank sharing a sample agrees on it
+        self.intervals = tuple(intervals) if intervals else None
         self._cache: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
 
     def __len__(self):
@@ -26,4 +30,7 @@ class SyntheticERA5(Dataset):
             shape_c = (self.hb, self.wb, self.cc) if self.channels_last else (self.cc, self.hb, self.wb)
             shape_t = (self.hb, self.wb, self.ct) if self.channels_last else (self.ct, self.hb, self.wb)
             self._cache[k] = (torch.randn(shape_c, generator=g), torch.randn(shape_t, generator=g))
+        if self.intervals:
+            pick = (self.seed * 7919 + idx * 104729) % len(self.intervals)
+            return (*self._cache[k], torch.tensor([float(self.intervals[pick])]))
         return self._cache[k]

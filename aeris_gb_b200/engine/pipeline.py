@@ -82,7 +82,10 @@ class ParallelEngine:
         self.links = PipeLinks(self.groups, self.prev_rank, self.next_rank, self.device)
         if self.PP > 1:
             self.links.warm()
-        self.dt_grad = self.PP > 1 and not model_cfg.layerwise_t_emb
+        # the conditioning vector is trainable upstream when one embedding network on the first stage feeds every
+        # stage: the shared noise-level MLP (layerwise_t_emb off) or the interval embedding (rit)
+        self.dt_grad = self.PP > 1 and model_cfg.conditioned and (model_cfg.rit and not model_cfg.diffusion
+                                                                  or not model_cfg.layerwise_t_emb)
         # noise: per (wp, dp, sp), NOT per pp, so the first and last stage regenerate identical z without talking
         # (:119, :667); noise level: per dp replica (:120)
         base = ecfg.seed
@@ -158,7 +161,8 @@ class ParallelEngine:
     def load(self, buffer_id):
         if not (self.is_first_stage() or self.is_last_stage()):
             return
-        cond_blk, tgt_blk = self.data_fn(self)       # [1, H/wp_y, W/wp_x, C] blocks of this WP rank
+        item = self.data_fn(self)                    # [1, H/wp_y, W/wp_x, C] blocks of this WP rank (+ interval, rit)
+        cond_blk, tgt_blk = item[0], item[1]
         g = self.ctx.grid
 
         def to_tok(blk):
@@ -166,6 +170,20 @@ class ParallelEngine:
             x = blk.to(self.device).view(B, g.nwy_loc, g.ws_y, g.nwx_loc, g.ws_x, C).permute(0, 1, 3, 2, 4, 5)
             return self._sp_slice(x.reshape(B * g.windows_per_rank * g.L, C).float())
         x = to_tok(tgt_blk)
+        if not self.cfg.diffusion:
+            # deterministic modes: the condition is the model input, the target the state to predict; the forecast
+            # interval (rit) is the same on every rank that shares the sample (:286)
+            t = None
+            if self.cfg.rit:
+                t = item[2].reshape(-1).float().to(self.device)
+                rg = self.groups.get("replica")
+                if rg is not None:
+                    dist.broadcast(t, src=self.grid.replica_ranks(self.rank)[0], group=rg)
+            self.buf["x"][buffer_id], self.buf["z"][buffer_id], self.buf["t"][buffer_id] = x, None, t
+            self.loads += 1
+            if self.is_first_stage():
+                self.buf["inputs"][buffer_id] = to_tok(cond_blk)
+            return
         if self.t_fn is not None:
             t = self.t_fn(self).to(self.device)
         else:
@@ -194,9 +212,12 @@ class ParallelEngine:
         out = self.buf["outputs"][buffer_id]
         if self.is_last_stage():
             x, z, t = self.buf["x"][buffer_id], self.buf["z"][buffer_id], self.buf["t"][buffer_id]
-            tr = t.repeat_interleave(x.shape[0])
-            sd = self.dcfg.sigma_data
-            err = (sd * out - TF.v_target(x, z, tr)) ** 2 * self._w_var * self._w_lat
+            if self.cfg.diffusion:
+                tr = t.repeat_interleave(x.shape[0])
+                sd = self.dcfg.sigma_data
+                err = (sd * out - TF.v_target(x, z, tr)) ** 2 * self._w_var * self._w_lat
+            else:
+                err = (out - x) ** 2 * self._w_var * self._w_lat              # (:998)
             loss = err.sum(dim=-1).mean()
             self.loss_acc += loss.detach()
             loss.backward()

@@ -143,6 +143,16 @@ class Trainer:
         err = (sd * pred - TF.v_target(x_tok, z, tr)) ** 2 * self._w_var * w_lat
         return err.sum(dim=-1).view(B, rows).mean(dim=1).sum()
 
+    def loss_regression(self, in_tok: torch.Tensor, target_tok: torch.Tensor, interval: torch.Tensor | None) -> torch.Tensor:
+        """Non-diffusion modes (``rit`` / plain): weighted squared error of the model's output against the target
+        state, mean over the local tokens, summed over the local batch (parallel_engine.py:998)."""
+        B = in_tok.shape[0] // self.grid.tokens_per_rank
+        rows = in_tok.shape[0] // B
+        pred = self.model.forward_tokens(in_tok, interval, self.context(B))
+        w_lat = self.w_lat_tokens().repeat(B, 1)
+        err = (pred - target_tok) ** 2 * self._w_var * w_lat
+        return err.sum(dim=-1).view(B, rows).mean(dim=1).sum()
+
     def io_plan(self, batch: int, noise: bool = True, seed: int | None = None):
         from ..models import fused_io
         from ..ops import diffusion as DF
@@ -163,19 +173,26 @@ class Trainer:
         cs = torch.stack([torch.cos(t), torch.sin(t)], dim=1).float().contiguous()
         return self.model.loss_images(x.contiguous(), c.contiguous(), cs, t, self.context(B), self.io_plan(B, seed=seed))
 
-    def train_step(self, target_host: torch.Tensor, cond_host: torch.Tensor, read_loss: bool = True):
+    def train_step(self, target_host: torch.Tensor, cond_host: torch.Tensor, read_loss: bool = True,
+                   interval: torch.Tensor | None = None):
         """One optimizer step on this rank's blocks of ``B`` samples. target_host: [B, H/wp_y, W/wp_x, C_out] fp32
         (standardised residual), cond_host: [B, H/wp_y, W/wp_x, C_cond] fp32; both pinned host tensors.
-        Returns the loss averaged over the local batch (synchronises: the value is read back to the host)."""
+        Non-diffusion modes: ``cond_host`` is the model input, ``target_host`` the state to predict and ``interval``
+        [B] the forecast interval (rit). Returns the loss averaged over the local batch (synchronises: the value is
+        read back to the host)."""
         dev = self.device
         with self.timers.region("load"):
             x = target_host.to(dev, non_blocking=True)
             c = cond_host.to(dev, non_blocking=True)
             B = x.shape[0]
-            t = TF.sample_noise_level(B, self.dcfg.sigma_min, self.dcfg.sigma_max, self.dcfg.sigma_data,
-                                      generator=self.nl_rng, device=dev, law=self.dcfg.noise_law)
+            if self.cfg.diffusion:
+                t = TF.sample_noise_level(B, self.dcfg.sigma_min, self.dcfg.sigma_max, self.dcfg.sigma_data,
+                                          generator=self.nl_rng, device=dev, law=self.dcfg.noise_law)
         with self.timers.region("fwd"):
-            if self.fused_io:
+            if not self.cfg.diffusion:
+                iv = interval.to(dev).float() if interval is not None else None
+                loss = self.loss_regression(self.block_to_tokens(c), self.block_to_tokens(x), iv)
+            elif self.fused_io:
                 loss = self.loss_images(x, c, t)
             else:
                 x_tok, c_tok = self.block_to_tokens(x), self.block_to_tokens(c)

@@ -54,6 +54,16 @@ class AerisConfig:
     oracle_checkpoint: bool = False  # PyTorch (oracle) path only: recompute every block in backward
     use_rope: bool = False          # axial 2-D rotary embedding on q, k inside every window (the reference's is inert)
     rope_base: float = 10_000.0
+    # model mode (parallel_swin.py:367-376, 394-397, 474-486): ``diffusion`` conditions every block on the noise level,
+    # ``rit`` (random time interval) on an embedding of the forecast interval; with neither the blocks are plain
+    # pre-norm transformer blocks and the model is a deterministic regressor
+    diffusion: bool = True
+    rit: bool = False
+    emb_norm: bool = False          # rit: RMSNorm after the interval embedding
+
+    @property
+    def conditioned(self) -> bool:
+        return self.diffusion or self.rit
 
     @property
     def n_blocks(self) -> int:
@@ -72,7 +82,7 @@ class AerisConfig:
 
     def param_count(self) -> int:
         d, hd, f = self.dim, self.heads * self.head_dim, self.mlp_dim
-        mod = (d * d + d if self.layerwise_t_emb else 0) + d * 6 * d + 6 * d
+        mod = ((d * d + d if self.layerwise_t_emb else 0) + d * 6 * d + 6 * d) if self.conditioned else 0
         block = 2 * d + hd + 3 * hd * d + d * hd + 3 * d * f + mod
         inp = self.in_channels * d + d + 2 * (d * d + d)
         outp = d + (d * d + d if self.layerwise_t_emb else 0) + d * 2 * d + 2 * d + d * self.out_channels
@@ -178,17 +188,25 @@ class ApeBuffer(nn.Module):
 
 
 class AttentionParams(nn.Module):
-    def __init__(self, dim, heads, head_dim):
+    """``norm``: ``"unused"`` = present in the reference's diffusion checkpoints but never applied (kept frozen for
+    key parity, parallel_swin.py:231-232, 265-266), ``"own"`` = the block's pre-norm in the plain mode, ``None`` = absent
+    (rit)."""
+
+    def __init__(self, dim, heads, head_dim, norm: str | None = "unused"):
         super().__init__()
-        self.norm = nn.RMSNorm(dim)       # present in reference checkpoints, never applied in diffusion mode
-        self.norm.weight.requires_grad_(False)
+        if norm is not None:
+            self.norm = nn.RMSNorm(dim)
+            if norm == "unused":
+                self.norm.weight.requires_grad_(False)
         self.to_qkv = nn.Linear(dim, 3 * heads * head_dim, bias=False)
         self.wo = nn.Linear(heads * head_dim, dim, bias=False)
 
 
 class FeedForwardParams(nn.Module):
-    def __init__(self, dim, hidden):
+    def __init__(self, dim, hidden, own_norm: bool = False):
         super().__init__()
+        if own_norm:                       # plain mode: the MLP normalises its own input (parallel_swin.py:88-96)
+            self.norm = nn.RMSNorm(dim)
         self.w1 = nn.Linear(dim, 2 * hidden, bias=False)
         self.w2 = nn.Linear(hidden, dim, bias=False)
 
@@ -216,6 +234,10 @@ class InputStage(nn.Module):
         self.proj = nn.Linear(cfg.in_channels, cfg.dim).to(cfg.data_dtype)
         self.proj.is_emb = True
         self.latent_embed = LatentEmbedding(cfg.dim).to(cfg.data_dtype)
+        if cfg.rit and not cfg.diffusion:          # scalar forecast interval -> conditioning vector (:367-376)
+            lin = nn.Linear(1, cfg.dim)
+            lin.is_emb = lin.is_time_emb = True
+            self.interval_embed = (nn.Sequential(lin, nn.RMSNorm(cfg.dim)) if cfg.emb_norm else lin).to(cfg.data_dtype)
         self.ape = ApeBuffer(cfg.in_channels)
         self._ape_tok: dict = {}
 
@@ -232,9 +254,9 @@ class InputStage(nn.Module):
     def forward(self, x_tok: torch.Tensor, t: torch.Tensor, ctx: StreamContext):
         """x_tok: [B * tokens_per_rank, in_channels] fp32 in the unshifted layout; t: [B] noise level (radians)."""
         cfg = self.cfg
-        B = t.shape[0]
         ape = self.ape_tokens(ctx, x_tok.device)
         rows = ape.shape[0]
+        B = x_tok.shape[0] // rows
         out = torch.empty((x_tok.shape[0], cfg.dim), dtype=cfg.model_dtype, device=x_tok.device)
         step = 1 << 16
         for b in range(B):
@@ -243,8 +265,15 @@ class InputStage(nn.Module):
                 out[sl] = self.proj(x_tok[sl].to(cfg.data_dtype) + ape[r:r + step]).to(cfg.model_dtype)
         return out, self.noise_embedding(t)
 
-    def noise_embedding(self, t: torch.Tensor) -> torch.Tensor:
+    def noise_embedding(self, t: torch.Tensor | None) -> torch.Tensor:
+        """Conditioning vector [B, dim]: the noise-level embedding (diffusion), the embedded forecast interval (rit,
+        ``t`` = interval per sample), or zeros that nothing reads (plain mode)."""
         cfg = self.cfg
+        if not cfg.diffusion:
+            if cfg.rit:
+                return self.interval_embed(t.reshape(-1, 1).to(cfg.data_dtype)).to(cfg.model_dtype)
+            n = 1 if t is None else t.reshape(-1).shape[0]
+            return torch.zeros((n, cfg.dim), dtype=cfg.model_dtype, device=self.proj.weight.device)
         emb = O.timestep_embedding(t.to(cfg.data_dtype), cfg.dim, cfg.max_period)
         if not cfg.layerwise_t_emb:
             emb = self.latent_embed(emb)
@@ -266,15 +295,38 @@ class SwinLayer(nn.Module):
         super().__init__()
         self.cfg = cfg
         d = cfg.dim
-        self.modulelist = nn.ModuleList([
-            nn.ModuleList([
-                nn.RMSNorm(d),
-                AttentionParams(d, cfg.heads, cfg.head_dim),
-                nn.RMSNorm(d),
-                FeedForwardParams(d, cfg.mlp_dim),
-                ModulationLinear(d, 6 * d, cfg.layerwise_t_emb),
-            ]) for _ in range(cfg.sublayers)
-        ])
+        if cfg.conditioned:
+            self.modulelist = nn.ModuleList([
+                nn.ModuleList([
+                    nn.RMSNorm(d),
+                    AttentionParams(d, cfg.heads, cfg.head_dim, None if cfg.rit else "unused"),
+                    nn.RMSNorm(d),
+                    FeedForwardParams(d, cfg.mlp_dim),
+                    ModulationLinear(d, 6 * d, cfg.layerwise_t_emb),
+                ]) for _ in range(cfg.sublayers)
+            ])
+        elif cfg.sublayers > 1:         # plain pre-norm blocks, module names as in parallel_swin.py:446-451
+            self.modulelist = nn.ModuleList([
+                nn.ModuleList([AttentionParams(d, cfg.heads, cfg.head_dim, "own"),
+                               FeedForwardParams(d, cfg.mlp_dim, own_norm=True)]) for _ in range(cfg.sublayers)])
+        else:
+            self.attn = AttentionParams(d, cfg.heads, cfg.head_dim, "own")
+            self.ff = FeedForwardParams(d, cfg.mlp_dim, own_norm=True)
+
+    def blocks(self):
+        """(norm1 weight, attention parameters, norm2 weight, MLP parameters, modulation module or None) per block."""
+        if self.cfg.conditioned:
+            return [(n1.weight, attn, n2.weight, ff, mod) for n1, attn, n2, ff, mod in self.modulelist]
+        pairs = list(self.modulelist) if self.cfg.sublayers > 1 else [(self.attn, self.ff)]
+        return [(attn.norm.weight, attn, ff.norm.weight, ff, None) for attn, ff in pairs]
+
+    def _plain_modulation(self, batch: int, device, dtype) -> torch.Tensor:
+        """shift = scale = 0, gate = 1: the modulated block then IS the plain block x + f(norm(x))."""
+        d = self.cfg.dim
+        m = torch.zeros((batch, 6 * d), device=device, dtype=dtype)
+        m[:, 2 * d:3 * d] = 1.0
+        m[:, 5 * d:] = 1.0
+        return m
 
     def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext, regroup=None,
                 publish_out: bool = False) -> torch.Tensor:
@@ -286,15 +338,19 @@ class SwinLayer(nn.Module):
         eps = cfg.eps(x.dtype)
         if regroup is not None and regroup[0] == regroup[1]:
             regroup = None
-        for j, (n1, attn, n2, ff, mod) in enumerate(self.modulelist):
+        blocks = self.blocks()
+        # plain blocks normalise first (there is nothing to modulate before the norm)
+        after_mod_norm = cfg.after_mod_norm and cfg.conditioned
+        for j, (n1w, attn, n2w, ff, mod) in enumerate(blocks):
             if use_fused(x):
                 from . import fused
                 from ..ops import elementwise as E
                 if ctx.grid.sp > 1 and ctx.sp_exchange is None:
                     raise RuntimeError("sequence parallelism on CUDA needs StreamContext.sp_exchange (fused.SPExchange)")
-                m = fused.modulation(mod.modulation, dt)
+                m = fused.modulation(mod.modulation, dt) if mod is not None else \
+                    self._plain_modulation(ctx.batch, x.device, torch.float32)
                 meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.n_local, cfg.heads, cfg.head_dim,
-                                       E.MODE_MOD_THEN_NORM if cfg.after_mod_norm else E.MODE_NORM_THEN_MOD,
+                                       E.MODE_MOD_THEN_NORM if after_mod_norm else E.MODE_NORM_THEN_MOD,
                                        eps, cfg.chunk_windows, sp=ctx.sp_exchange if ctx.grid.sp > 1 else None,
                                        rope=ctx.rope(x.device))
                 rg = None
@@ -302,15 +358,16 @@ class SwinLayer(nn.Module):
                     rg = (ctx.table(regroup[0], regroup[1], x.device), ctx.table(regroup[1], regroup[0], x.device),
                           ctx.peer_fn)
                 alloc = None
-                if publish_out and j == len(self.modulelist) - 1:
+                if publish_out and j == len(blocks) - 1:
                     alloc = fused._pool_alloc(ctx.peer_fn)
-                x = fused.FusedBlock.apply(x, m, meta, n1.weight, attn.to_qkv.weight, attn.wo.weight, n2.weight,
+                x = fused.FusedBlock.apply(x, m, meta, n1w, attn.to_qkv.weight, attn.wo.weight, n2w,
                                            ff.w1.weight, ff.w2.weight, rg, alloc)
             else:
-                m = mod(dt.to(mod.modulation[-1].weight.dtype))
+                m = mod(dt.to(mod.modulation[-1].weight.dtype)) if mod is not None else \
+                    self._plain_modulation(ctx.batch, x.device, x.dtype)
                 if j == 0 and regroup is not None:
                     x = ctx.regroup_unfused(x, regroup[0], regroup[1])
-                p = {"n1": n1.weight, "to_qkv": attn.to_qkv.weight, "wo": attn.wo.weight, "n2": n2.weight,
+                p = {"n1": n1w, "to_qkv": attn.to_qkv.weight, "wo": attn.wo.weight, "n2": n2w,
                      "w1": ff.w1.weight, "w2": ff.w2.weight}
                 rope = ctx.rope(x.device)
                 inner = (lambda q_, nw, nl, H, d: O.window_attention(q_, nw, nl, H, d, rope=rope)) if rope else None
@@ -321,7 +378,7 @@ class SwinLayer(nn.Module):
                                                                            inner or O.window_attention)
                 run = lambda xx, mm: O.block_forward(xx, mm, p, n_win_per_sample=ctx.grid.windows_per_rank,
                                                      L=ctx.grid.n_local, heads=cfg.heads, head_dim=cfg.head_dim,
-                                                     after_mod_norm=cfg.after_mod_norm, eps=eps, attention=attn)
+                                                     after_mod_norm=after_mod_norm, eps=eps, attention=attn)
                 if cfg.oracle_checkpoint and torch.is_grad_enabled():
                     x = torch.utils.checkpoint.checkpoint(run, x, m, use_reentrant=False)
                 else:
@@ -338,11 +395,12 @@ class OutputStage(nn.Module):
         d = cfg.dim
         self.norm = nn.RMSNorm(d).to(cfg.data_dtype)
         self.norm.is_head = True
-        if cfg.layerwise_t_emb:
-            self.modulation = nn.Sequential(nn.Linear(d, d, bias=True), nn.SiLU(), nn.Linear(d, 2 * d, bias=True))
-        else:
-            self.modulation = nn.Sequential(nn.SiLU(), nn.Linear(d, 2 * d, bias=True))
-        self.modulation.to(cfg.data_dtype)
+        if cfg.conditioned:
+            if cfg.layerwise_t_emb:
+                self.modulation = nn.Sequential(nn.Linear(d, d, bias=True), nn.SiLU(), nn.Linear(d, 2 * d, bias=True))
+            else:
+                self.modulation = nn.Sequential(nn.SiLU(), nn.Linear(d, 2 * d, bias=True))
+            self.modulation.to(cfg.data_dtype)
         self.head = nn.Linear(d, cfg.out_channels, bias=False).to(cfg.data_dtype)
 
     def forward_rows(self, x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
@@ -353,7 +411,10 @@ class OutputStage(nn.Module):
 
     def forward(self, x: torch.Tensor, dt: torch.Tensor, ctx: StreamContext) -> torch.Tensor:
         cfg = self.cfg
-        shift, scale = self.modulation(dt.to(cfg.data_dtype)).chunk(2, dim=1)
+        if cfg.conditioned:
+            shift, scale = self.modulation(dt.to(cfg.data_dtype)).chunk(2, dim=1)
+        else:                               # plain mode: norm -> head (parallel_swin.py:526-528)
+            shift = scale = torch.zeros((ctx.batch, cfg.dim), dtype=cfg.data_dtype, device=x.device)
         return _HeadFn.apply(x, shift, scale, self.norm.weight, self.head.weight, self)
 
     def loss_images(self, x, dt, x_img, cs, plan):

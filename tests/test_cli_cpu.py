@@ -85,3 +85,15 @@ def test_stage_metric_names_follow_the_reference():
     m = stage_metrics({1: SwinLayer(cfg)}, 2.5, 1, 4, {"ForwardPass": 0.1})
     assert set(m) == {"train/stage_norm/stage_norm_1", "train/weight_norm/stage_1/0_modulation_0",
                       "train/weight_norm/stage_1/0_modulation_2", "train/pp_timers/ForwardPass/rank_1"}
+
+
+def test_reference_benchmark_experiment_trains_at_toy_size():
+    """``experiment=benchmark`` (the reference's own benchmark config: random-time-interval regression, overlapped
+    pipeline p2p, distributed optimizer) composes and trains with its sizes overridden, PP 2 x WP 2 on four ranks."""
+    out = _run(["aeris_gb_b200.cli.train", "experiment=benchmark", "data.synthetic=true", "data.gas=3",
+                "trainer.benchmark_steps=3", "model.PP=2", "model.SP=1", "model.WP_X=2", "model.WP_Y=1", "model.dim=32",
+                "model.heads=2", "model.head_dim=16", "model.mlp_dim=64", "model.PP_stages=4", "model.window_size=[8,8]",
+                "model.img=[16,32]", "model.checkpoint_dir=null", "model.dtype=float32", "model.channels=6",
+                "optimizer.lr=0.01", "trainer.lr_rampup_kimg=0"], nproc=4, port=29763)
+    losses = [float(l.split("loss ")[1].split()[0]) for l in out.splitlines() if " loss " in l]
+    assert len(losses) == 3 and all(l == l for l in losses) and losses[-1] < losses[0]

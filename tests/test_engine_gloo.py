@@ -18,9 +18,13 @@ IMG, CH, CC = (16, 32), 6, 4
 
 
 def _cfg(wp=(1, 1), sp=1, layerwise=True):
-    return AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=32, heads=2, head_dim=16,
-                       mlp_dim=64, n_layers=4, sublayers=1, model_dtype=torch.float32, wp=wp, sp=sp, norm_eps=1e-5,
-                       layerwise_t_emb=layerwise)
+    """``layerwise``: True / False = diffusion with per-layer / shared noise embedding; "rit" = random-time-interval
+    regression (no noise, the condition is the model input)."""
+    rit = layerwise == "rit"
+    return AerisConfig(img=IMG, window=(8, 8), in_channels=CC if rit else CH + CC, out_channels=CH, dim=32, heads=2,
+                       head_dim=16, mlp_dim=64, n_layers=4, sublayers=1, model_dtype=torch.float32, wp=wp, sp=sp,
+                       norm_eps=1e-5, layerwise_t_emb=layerwise is True, after_mod_norm=not rit, diffusion=not rit,
+                       rit=rit)
 
 
 def _field(seed, C):
@@ -40,7 +44,10 @@ def _sample_index(eng):
 
 def _data_fn(eng):
     i = _sample_index(eng)
-    return _block(_field(1000 + i, CC), eng), _block(_field(2000 + i, CH), eng)
+    item = (_block(_field(1000 + i, CC), eng), _block(_field(2000 + i, CH), eng))
+    if eng.cfg.rit and not eng.cfg.diffusion:
+        item += (torch.tensor([float((6, 12, 24)[i % 3])]),)
+    return item
 
 
 def _noise_fn(eng):
@@ -140,6 +147,19 @@ def test_pp3_shared_noise_embedding_gets_its_gradient_from_every_stage():
     assert torch.allclose(g[0][k], ref_grads[0][k], atol=1e-6, rtol=1e-4)
     _assert_same(sd, ref[0])
     assert norm == pytest.approx(ref[2], rel=1e-4)
+
+
+def test_pp2_wp2_random_time_interval_mode_matches_single_process():
+    """Deterministic regression conditioned on the embedded forecast interval (rit): the interval embedding on the
+    first stage is trained through every stage of the pipeline."""
+    ref = _launch(1, PP=1, WP=(1, 1), gas=3, iters=2, layerwise="rit")
+    ref_grads = _launch.last_grads
+    sd, loss, norm = _launch(4, PP=2, WP=(1, 2), gas=3, iters=2, overlap=True, layerwise="rit")
+    assert ref_grads[0]["interval_embed.weight"].abs().max() > 0
+    assert torch.allclose(_launch.last_grads[0]["interval_embed.weight"], ref_grads[0]["interval_embed.weight"],
+                          atol=1e-6, rtol=1e-4)
+    _assert_same(sd, ref[0])
+    assert loss == pytest.approx(ref[1], rel=1e-4)
 
 
 def test_pp2_overlapped_wp2_matches_single_process(single):
