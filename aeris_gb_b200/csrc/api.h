@@ -28,6 +28,12 @@ int aeris_attn_bwd(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0,
 int aeris_gemm_scatter_heads(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int b_mn,
                              const void* const* peers, int sp, int sp_rank, int n_local, int L, int sec_w, int* status,
                              void* stream);
+// Softmax arithmetic of the head_dim-64 forward kernel (-1 scalar; 0, 2, 3, 4 two-wide with that many of every eight
+// score pairs on the polynomial exp2). Returns non-zero for an unknown variant.
+int aeris_attn_set_fwd_variant(int poly);
+// Checking build (-DAERIS_BOUNDS_CHECK) only: status word and source rows for the gathers launched next; returns 1 when
+// the library validates gather codes, 0 when it was built without the checks.
+int aeris_debug_set_gather_bounds(int* status, unsigned src_rows);
 int aeris_attn_fwd_push(const void* qkv, int ld, int H_local, void* o, int ldo, float* lse, int n_win, int N,
                         int head_dim, float scale, const void* const* o_peers, int sp, int n_local, int push_ld,
                         int push_col0, int* status, void* stream);

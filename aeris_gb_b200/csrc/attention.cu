@@ -41,6 +41,84 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Packed two-wide fp32 arithmetic (sm_100 f32x2 instructions): one issue slot per two scores.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float mufu_exp2(float x) {   // not volatile: the scheduler may interleave it freely
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x for a pair of exponents on the FMA pipe instead of the exp unit (which limits attention at head_dim 64):
+// x = r + f with r = round(x), f in [-0.5, 0.5]; 2^f by a cubic (relative error 7.5e-5, far below bf16 resolution),
+// 2^r by adding r to the exponent field. x is clamped at -125 so the exponent field cannot wrap; callers keep x <= 8.
+__device__ __forceinline__ void poly_exp2_pair(uint64_t t2, float& p0, float& p1) {
+  float t0, t1;
+  f2_unpack(t2, t0, t1);
+  t2 = f2_pack(fmaxf(t0, -125.f), fmaxf(t1, -125.f));
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f);     // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
+  const uint64_t tm = f2_add(t2, magic);
+  const uint64_t f = f2_sub(t2, f2_sub(tm, magic));
+  uint64_t q = f2_fma(f2_pack(0.0551716574f, 0.0551716574f), f, f2_pack(0.2426111251f, 0.2426111251f));
+  q = f2_fma(q, f, f2_pack(0.6932609677f, 0.6932609677f));
+  q = f2_fma(q, f, f2_pack(0.9999280572f, 0.9999280572f));
+  float q0, q1, m0, m1;
+  f2_unpack(q, q0, q1);
+  f2_unpack(tm, m0, m1);
+  p0 = __uint_as_float(__float_as_uint(m0) * 0x00800000u + __float_as_uint(q0));
+  p1 = __uint_as_float(__float_as_uint(m1) * 0x00800000u + __float_as_uint(q1));
+}
+
+// Probabilities of one 64-score row segment (raw scores in v0 | v1) against the reference maximum m_ref: bf16 pairs
+// into pk, their sum returned. POLY of every eight pairs take the polynomial path, the rest the exp unit, interleaved
+// so that both pipes stay busy.
+template <int POLY>
+__device__ __forceinline__ float softmax_row64(const uint32_t (&v0)[32], const uint32_t (&v1)[32], float sl2,
+                                               float m_ref, uint32_t (&pk)[32]) {
+  const uint64_t sl = f2_pack(sl2, sl2), nm = f2_pack(-m_ref, -m_ref);
+  uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};      // bit pattern of (0.f, 0.f)
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const uint32_t a = (i < 16) ? v0[2 * i] : v1[2 * i - 32], b = (i < 16) ? v0[2 * i + 1] : v1[2 * i - 31];
+    const uint64_t t = f2_fma(f2_pack(__uint_as_float(a), __uint_as_float(b)), sl, nm);
+    float p0, p1;
+    if ((i & 7) < POLY) {
+      poly_exp2_pair(t, p0, p1);
+    } else {
+      float t0, t1;
+      f2_unpack(t, t0, t1);
+      p0 = mufu_exp2(t0);
+      p1 = mufu_exp2(t1);
+    }
+    acc[i & 3] = f2_add(acc[i & 3], f2_pack(p0, p1));
+    pk[i] = pack_bf16x2(p0, p1);
+  }
+  float s0, s1;
+  f2_unpack(f2_add(f2_add(acc[0], acc[1]), f2_add(acc[2], acc[3])), s0, s1);
+  return s0 + s1;
+}
+
 // -------------------------------------------------------------------------------------------------------- forward
 // grid = (q_tiles, H, n_win). One CTA owns a 128-row Q tile and streams the window's K/V in 64-row tiles through a
 // two-stage TMA ring. Per tile: S = Q K^T lands in TMEM, the four softmax warps (one thread per query row) read its 64
@@ -74,7 +152,9 @@ __device__ __forceinline__ void rescale_tmem_rows(uint32_t taddr, int cols, floa
   tmem_wait_st();
 }
 
-template <int DCH>
+// POLY < 0: scalar softmax arithmetic, every exponential on the exp unit; POLY >= 0: two-wide fp32 arithmetic with POLY of
+// every eight score pairs exponentiated by the polynomial.
+template <int DCH, int POLY>
 __global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 3 : 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
@@ -255,22 +335,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (!rescale(j, m_new, waited)) { ok = false; break; }
           }
           uint32_t pk[32];
-          float rs[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(v0[2 * i]), sl2, -m_ref));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(v0[2 * i + 1]), sl2, -m_ref));
-            rs[(2 * i) & 3] += p0; rs[(2 * i + 1) & 3] += p1;
-            pk[i] = pack_bf16x2(p0, p1);
+          if constexpr (POLY >= 0) {
+            l += softmax_row64<POLY>(v0, v1, sl2, m_ref, pk);
+          } else {
+            float rs[4] = {0.f, 0.f, 0.f, 0.f};
+  #pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(v0[2 * i]), sl2, -m_ref));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(v0[2 * i + 1]), sl2, -m_ref));
+              rs[(2 * i) & 3] += p0; rs[(2 * i + 1) & 3] += p1;
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+  #pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(v1[2 * i]), sl2, -m_ref));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(v1[2 * i + 1]), sl2, -m_ref));
+              rs[(2 * i) & 3] += p0; rs[(2 * i + 1) & 3] += p1;
+              pk[16 + i] = pack_bf16x2(p0, p1);
+            }
+            l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
           }
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(v1[2 * i]), sl2, -m_ref));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(v1[2 * i + 1]), sl2, -m_ref));
-            rs[(2 * i) & 3] += p0; rs[(2 * i + 1) & 3] += p1;
-            pk[16 + i] = pack_bf16x2(p0, p1);
-          }
-          l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
           if (j > 0 && !waited && !mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
 #pragma unroll
           for (int g = 0; g < 8; ++g)
@@ -364,12 +448,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <int DCH>
+template <int DCH, int POLY>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const AttnFwdParams& p, cudaStream_t stream) {
   constexpr int SMEM = DCH * 16384 + 2 * 2 * DCH * 8192 + 16384 + 256;
   static bool configured = false;
-  auto kern = attn_fwd_kernel<DCH>;
+  auto kern = attn_fwd_kernel<DCH, POLY>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -20;
     configured = true;
@@ -923,6 +1007,15 @@ static int launch_attn_bwd(const CUtensorMap& tq128, const CUtensorMap& tk64, co
 
 using namespace aeris;
 
+// Softmax arithmetic of the head_dim-64 forward kernel: -1 = scalar, exp unit only; 0 = two-wide fp32 arithmetic;
+// 2, 3, 4 = two-wide with that many of every eight score pairs on the polynomial exp2.
+static int g_fwd_poly = -1;
+extern "C" int aeris_attn_set_fwd_variant(int poly) {
+  if (poly != -1 && poly != 0 && poly != 2 && poly != 3 && poly != 4) return -1;
+  g_fwd_poly = poly;
+  return 0;
+}
+
 // q, k, v: base pointers of row-major [n_win * N, ld*] bf16 tensors; *_col0 = column of head 0.
 static int attn_fwd_impl(const void* q, int ldq, int q_col0, const void* k, int ldk, int k_col0, const void* v,
                          int ldv, int v_col0, void* o, int ldo, float* lse, int n_win, int N, int H, int head_dim,
@@ -965,7 +1058,14 @@ static int attn_fwd_impl(const void* q, int ldq, int q_col0, const void* k, int 
   if ((r = make_tmap_3d_bf16(&tq, q, ldq, N, n_win, ldq, static_cast<uint64_t>(N) * ldq, 64, TILE))) return r;
   if ((r = make_tmap_3d_bf16(&tk, k, ldk, N, n_win, ldk, static_cast<uint64_t>(N) * ldk, 64, KVT))) return r;
   if ((r = make_tmap_3d_bf16(&tv, v, ldv, N, n_win, ldv, static_cast<uint64_t>(N) * ldv, 64, KVT))) return r;
-  return head_dim == 64 ? launch_attn_fwd<1>(tq, tk, tv, p, stream) : launch_attn_fwd<2>(tq, tk, tv, p, stream);
+  if (head_dim == 128) return launch_attn_fwd<2, -1>(tq, tk, tv, p, stream);
+  switch (g_fwd_poly) {            // head_dim 64: the exp unit is the limiter, see softmax_row64
+    case 0: return launch_attn_fwd<1, 0>(tq, tk, tv, p, stream);
+    case 2: return launch_attn_fwd<1, 2>(tq, tk, tv, p, stream);
+    case 3: return launch_attn_fwd<1, 3>(tq, tk, tv, p, stream);
+    case 4: return launch_attn_fwd<1, 4>(tq, tk, tv, p, stream);
+    default: return launch_attn_fwd<1, -1>(tq, tk, tv, p, stream);
+  }
 }
 
 // Backward. qkv: fused [T, ldq] tensor (q/k/v column blocks at *_col0); o, d_o: [T, ldo]; dqkv: [T, ldg] (same

@@ -13,7 +13,43 @@ namespace aeris {
 
 struct PeerPtrs {
   const __nv_bfloat16* p[16];
+#ifdef AERIS_BOUNDS_CHECK
+  // checking build: every gather code (source rank, source row) is validated before the access; a bad one records
+  // ERR_BOUNDS in the status word and the row is read as zeros (never a trap, never the access)
+  int n;               // number of valid entries of p
+  unsigned src_rows;   // rows of every source buffer (0: unknown, only the rank is checked)
+  int* status;
+#endif
 };
+
+#ifdef AERIS_BOUNDS_CHECK
+static unsigned g_chk_src_rows = 0;
+static int* g_chk_status = nullptr;
+__device__ __forceinline__ bool gather_code_ok(const PeerPtrs& pp, uint32_t code) {
+  const unsigned rank = code >> 28, row = code & 0x0fffffffu;
+  const bool ok = rank < static_cast<unsigned>(pp.n) && pp.p[rank] != nullptr && (pp.src_rows == 0 || row < pp.src_rows);
+  if (!ok && pp.status) atomicCAS(pp.status, 0, ERR_BOUNDS);
+  return ok;
+}
+#define AERIS_GATHER_OK(pp, code) gather_code_ok(pp, code)
+#define AERIS_FILL_CHECK(pp, n_peers) do { (pp).n = (n_peers); (pp).src_rows = g_chk_src_rows; (pp).status = g_chk_status; } while (0)
+#else
+#define AERIS_GATHER_OK(pp, code) true
+#define AERIS_FILL_CHECK(pp, n_peers) do { } while (0)
+#endif
+
+// Checking build only (no effect otherwise): the status word and the number of rows of the source buffers of the
+// gathers launched next. Returns 1 when the library was built with the checks, else 0.
+extern "C" int aeris_debug_set_gather_bounds(int* status, unsigned src_rows) {
+#ifdef AERIS_BOUNDS_CHECK
+  g_chk_status = status;
+  g_chk_src_rows = src_rows;
+  return 1;
+#else
+  (void)status; (void)src_rows;
+  return 0;
+#endif
+}
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
   const uint4 u = *reinterpret_cast<const uint4*>(p);
@@ -101,13 +137,15 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
       nxt[k] = make_uint4(0u, 0u, 0u, 0u);
       if (active && rr < r1) {
         const __nv_bfloat16* src;
+        bool ok = true;
         if (gidx) {
           const uint32_t code = gidx[rr];
+          ok = AERIS_GATHER_OK(peers, code);
           src = peers.p[code >> 28] + static_cast<size_t>(code & 0x0fffffffu) * D + c0;
         } else {
           src = x + static_cast<size_t>(rr) * D + c0;
         }
-        nxt[k] = *reinterpret_cast<const uint4*>(src);
+        if (ok) nxt[k] = *reinterpret_cast<const uint4*>(src);
       }
     }
   };
@@ -289,6 +327,10 @@ __global__ void gather_rows_kernel(const uint32_t* __restrict__ gidx, PeerPtrs p
     const long long r = i / vec_per_row;
     const int v = static_cast<int>(i - r * vec_per_row);
     const uint32_t code = gidx[r];
+    if (!AERIS_GATHER_OK(peers, code)) {
+      reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * D)[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
     const uint4* src = reinterpret_cast<const uint4*>(peers.p[code >> 28] +
                                                       static_cast<size_t>(code & 0x0fffffffu) * D) + v;
     reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * D)[v] = *src;
@@ -532,6 +574,7 @@ extern "C" int aeris_modnorm_fwd(const void* x, const void* gidx, const void* co
   PeerPtrs pp{};
   for (int i = 0; i < n_peers && i < 16; ++i) pp.p[i] = reinterpret_cast<const __nv_bfloat16*>(peer_ptrs[i]);
   if (gidx && n_peers <= 0) return -2;
+  AERIS_FILL_CHECK(pp, n_peers);
   const int rpc = pick_rows_per_cta(rows);
   int grid = (rows + FWD_RPI - 1) / FWD_RPI;
   if (grid > aeris_num_sms() * 8) grid = aeris_num_sms() * 8;
@@ -564,6 +607,7 @@ extern "C" int aeris_gather_rows(const void* gidx, const void* const* peer_ptrs,
   if (D % 8 || rows <= 0 || n_peers <= 0) return -1;
   PeerPtrs pp{};
   for (int i = 0; i < n_peers && i < 16; ++i) pp.p[i] = reinterpret_cast<const __nv_bfloat16*>(peer_ptrs[i]);
+  AERIS_FILL_CHECK(pp, n_peers);
   const int grid = grid_for(rows * (D / 8), 256, aeris_num_sms() * 16);
   gather_rows_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint32_t*>(gidx), pp, reinterpret_cast<__nv_bfloat16*>(out), rows, D);

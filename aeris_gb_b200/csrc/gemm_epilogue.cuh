@@ -139,6 +139,13 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
       const int sec = c0 / p.scat_sec_w;
       const int hc = c0 - sec * p.scat_sec_w;
       const int owner = hc / p.scat_own_w;
+#ifdef AERIS_BOUNDS_CHECK
+      // checking build: the owner must be one of the (at most 8) ranks with a buffer; otherwise record and skip
+      if (owner < 0 || owner >= 8 || p.scat_peers[owner] == nullptr) {
+        if (p.status) atomicCAS(p.status, 0, ERR_BOUNDS);
+        continue;
+      }
+#endif
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld +
                            sec * p.scat_own_w + (hc - owner * p.scat_own_w);
       uint32_t o[16];
@@ -156,6 +163,14 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
   } else if (p.epi == EPI_RS_PUSH) {
     const int owner = row_ok ? row / p.scat_n_local : 0;
     const size_t drow = static_cast<size_t>(p.scat_rank) * p.scat_n_local + (row - owner * p.scat_n_local);
+#ifdef AERIS_BOUNDS_CHECK
+    // checking build: a row whose owner is not one of the (at most 8) ranks with a buffer is recorded and not stored
+    // (the lane stays in the warp-wide staging below, as rows past the end of the matrix do)
+    if (row_ok && (owner < 0 || owner >= 8 || p.scat_peers[owner < 8 ? owner : 0] == nullptr)) {
+      if (p.status) atomicCAS(p.status, 0, ERR_BOUNDS);
+      row_ok = false;
+    }
+#endif
     __nv_bfloat16* rowdst = reinterpret_cast<__nv_bfloat16*>(p.scat_peers[owner]) + drow * p.scat_ld + tn * BN;
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {

@@ -207,9 +207,10 @@ def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv
             n = nw * meta.L
             xc = x[r0:r0 + n]
             if gather is not None:
-                table, peers, _src = gather
+                table, peers, src = gather
                 E.modnorm_fwd(None, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h[:n],
-                              gather_idx=table[r0:r0 + n], peer_ptrs=peers, x_out=xc, rows=n)
+                              gather_idx=table[r0:r0 + n], peer_ptrs=peers, x_out=xc, rows=n,
+                              src_rows=src.shape[0])
             else:
                 E.modnorm_fwd(xc, sc1, sh1, wn1, mode=meta.mode, eps=meta.eps, out=h[:n])
             if meta.sp is None:
@@ -366,7 +367,7 @@ class FusedBlock(torch.autograd.Function):
             alloc = _pool_alloc(peer_fn, gradient=True)
             back = (alloc(table_bwd.numel(), dx.shape[1], dx.dtype) if alloc is not None else
                     torch.empty((table_bwd.numel(), dx.shape[1]), dtype=dx.dtype, device=dx.device))
-            E.gather_rows(table_bwd, peers, back)
+            E.gather_rows(table_bwd, peers, back, src_rows=dx.shape[0])
             dx = back
         out = [ret[k].to(params[k].dtype) if ret[k] is not None else None
                for k in ("n1", "to_qkv", "wo", "n2", "w1", "w2")]
@@ -426,7 +427,7 @@ class Regroup(torch.autograd.Function):
         ctx.table_bwd, ctx.peer_fn = table_bwd, peer_fn
         out = torch.empty((table_fwd.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
         peers = peer_fn(x, "fwd") if peer_fn is not None else [x.data_ptr()]
-        E.gather_rows(table_fwd, peers, out)
+        E.gather_rows(table_fwd, peers, out, src_rows=x.shape[0])
         return out
 
     @staticmethod
@@ -436,5 +437,5 @@ class Regroup(torch.autograd.Function):
         alloc = _pool_alloc(ctx.peer_fn, gradient=True)      # the previous layer's dy: see FusedBlock.backward
         out = (alloc(ctx.table_bwd.numel(), dy.shape[1], dy.dtype) if alloc is not None else
                torch.empty((ctx.table_bwd.numel(), dy.shape[1]), dtype=dy.dtype, device=dy.device))
-        E.gather_rows(ctx.table_bwd, peers, out)
+        E.gather_rows(ctx.table_bwd, peers, out, src_rows=dy.shape[0])
         return out, None, None, None

@@ -60,6 +60,15 @@ def attn_fwd(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int, *, out: torc
     return out, lse
 
 
+def set_fwd_variant(poly: int) -> None:
+    """Softmax arithmetic of the head_dim-64 forward kernel: -1 = scalar fp32 with every exponential on the exp unit;
+    0 = two-wide fp32 instructions; 2, 3, 4 = two-wide with that many of every eight score pairs exponentiated by a
+    cubic polynomial on the FMA pipe (the exp unit is what limits attention at head_dim 64)."""
+    rc = _l.lib().aeris_attn_set_fwd_variant(int(poly))
+    if rc != 0:
+        raise ValueError(f"no forward variant {poly}")
+
+
 def attn_reference(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int) -> torch.Tensor:
     """Plain PyTorch fp32 restatement (used by tests and by the CPU oracle)."""
     q, k, v = qkv.float().view(n_win, N, 3, H, d).permute(2, 0, 3, 1, 4)

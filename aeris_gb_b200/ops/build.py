@@ -13,11 +13,15 @@ from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
-LIB_PATH = CSRC / "libaeris_b200.so"
+# AERIS_BOUNDS_CHECK=1 selects the checking build (-DAERIS_BOUNDS_CHECK): every gather code and push owner is
+# validated on the device, a bad one is recorded in the status word and the access skipped. It stands in for a
+# memory checker on machines where none can be run; it is a library of its own so both can sit side by side.
+CHECKED = os.environ.get("AERIS_BOUNDS_CHECK") == "1"
+LIB_PATH = CSRC / ("libaeris_b200_chk.so" if CHECKED else "libaeris_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--use_fast_math", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
-]
+] + (["-DAERIS_BOUNDS_CHECK"] if CHECKED else [])
 
 
 def _nvcc() -> str:
@@ -41,7 +45,7 @@ def _digest() -> str:
 
 
 def needs_build() -> bool:
-    stamp = CSRC / "build" / "digest.txt"
+    stamp = CSRC / ("build_chk" if CHECKED else "build") / "digest.txt"
     return not (LIB_PATH.exists() and stamp.exists() and stamp.read_text().strip() == _digest())
 
 
@@ -49,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile every .cu to an object (in parallel) and link the shared library. Returns its path."""
     if not force and not needs_build():
         return LIB_PATH
-    out_dir = CSRC / "build"
+    out_dir = CSRC / ("build_chk" if CHECKED else "build")
     out_dir.mkdir(exist_ok=True)
     nvcc = _nvcc()
 

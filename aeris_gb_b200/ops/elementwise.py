@@ -6,6 +6,7 @@ import ctypes
 import torch
 
 from . import lib as _l
+from .build import CHECKED as _CHECKED
 
 MODE_MOD_THEN_NORM = 0   # h = RMSNorm(x * (1 + scale) + shift) * w      (layerwise_t_emb_after_mod_norm)
 MODE_NORM_THEN_MOD = 1   # h = (RMSNorm(x) * w) * (1 + scale) + shift    (DiT ordering)
@@ -19,10 +20,14 @@ def _peer_array(ptrs: list[int]):
 def modnorm_fwd(x: torch.Tensor, scale: torch.Tensor | None, shift: torch.Tensor | None, w: torch.Tensor, *,
                 mode: int, eps: float, out: torch.Tensor | None = None, gather_idx: torch.Tensor | None = None,
                 peer_ptrs: list[int] | None = None, x_out: torch.Tensor | None = None,
-                rows: int | None = None, out_lo: torch.Tensor | None = None) -> torch.Tensor:
-    """``w`` bf16, or fp32 (the output head's norm); ``out_lo`` optionally receives ``h - bf16(h)``."""
+                rows: int | None = None, out_lo: torch.Tensor | None = None,
+                src_rows: int | None = None) -> torch.Tensor:
+    """``w`` bf16, or fp32 (the output head's norm); ``out_lo`` optionally receives ``h - bf16(h)``. ``src_rows``:
+    rows of every peer buffer the gather table points into (used by the checking build only)."""
     D = w.numel()
     rows = rows if rows is not None else (gather_idx.numel() if gather_idx is not None else x.shape[0])
+    if _CHECKED and gather_idx is not None:
+        set_gather_bounds(src_rows or 0)
     if out is None:
         out = torch.empty((rows, D), dtype=torch.bfloat16, device=w.device)
     peers = _peer_array(peer_ptrs) if gather_idx is not None else None
@@ -46,8 +51,17 @@ def modnorm_bwd(x: torch.Tensor, dh: torch.Tensor, dres: torch.Tensor | None, sc
     return dx
 
 
-def gather_rows(gather_idx: torch.Tensor, peer_ptrs: list[int], out: torch.Tensor) -> torch.Tensor:
+def set_gather_bounds(src_rows: int) -> bool:
+    """Checking build (AERIS_BOUNDS_CHECK=1) only: rows of the source buffers of the gathers launched next, so that
+    every table entry is validated on the device. Returns whether the loaded library checks at all."""
+    return bool(_l.lib().aeris_debug_set_gather_bounds(_l.ptr(_l.status_word()), int(src_rows)))
+
+
+def gather_rows(gather_idx: torch.Tensor, peer_ptrs: list[int], out: torch.Tensor,
+                src_rows: int | None = None) -> torch.Tensor:
     rows, D = out.shape
+    if _CHECKED:
+        set_gather_bounds(src_rows or 0)
     rc = _l.lib().aeris_gather_rows(_l.ptr(gather_idx), _peer_array(peer_ptrs), len(peer_ptrs), _l.ptr(out),
                                     _l._c_ll(rows), D, _l.stream_ptr())
     _l.check(rc, "aeris_gather_rows")

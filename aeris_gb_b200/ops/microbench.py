@@ -18,10 +18,13 @@ import os
 
 import torch
 
+from ..utils.clocks import ClockSampler
 from . import attention as A
 from . import elementwise as E
 from . import gemm as G
 from . import lib as L
+
+_CLOCKS: list = []      # one record per timed region of this process
 
 
 def _peaks():
@@ -36,12 +39,15 @@ def _time(fn, iters):
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
+    clk = ClockSampler(torch.cuda.current_device())
+    clk.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    _CLOCKS.append(clk.stop())
     L.check_status(sync=False)
     return e0.elapsed_time(e1) / iters
 
@@ -66,6 +72,8 @@ def main():
     ap.add_argument("--dim", type=int, default=1536)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--one-cta", action="store_true", help="force the one-CTA GEMM kernel")
+    ap.add_argument("--fwd-variant", type=int, default=None,
+                    help="attn_fwd: softmax arithmetic of the head_dim-64 kernel (-1, 0, 2, 3, 4; see ops.attention)")
     a = ap.parse_args()
     dev = "cuda"
     tf_peak, bw_peak, src = _peaks()
@@ -91,8 +99,13 @@ def main():
         qkv = torch.randn(nw * N, 3 * H * d, device=dev).bfloat16()
         o = torch.empty(nw * N, H * d, device=dev, dtype=torch.bfloat16)
         lse = torch.empty(nw, H, N, device=dev)
+        if a.fwd_variant is not None:
+            A.set_fwd_variant(a.fwd_variant)
+            out["fwd_variant"] = a.fwd_variant
         A.attn_fwd(qkv, nw, N, H, d, out=o, lse=lse)
         if a.kernel == "attn_fwd":
+            ref = A.attn_reference(qkv[:2 * N], 2, N, H, d)
+            out["rel_err_vs_fp32"] = ((o[:2 * N].float() - ref).norm() / ref.norm()).item()
             ms = _time(lambda: A.attn_fwd(qkv, nw, N, H, d, out=o, lse=lse), a.iters)
             fl = 4.0 * nw * H * N * N * d
         else:
@@ -251,6 +264,7 @@ def main():
                                    max_norm=0.0, ema_beta=0.999), a.iters)
         by = n * (5 * 4 + 5 * 4 + 2.0)
         out.update(n=n, ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / ms / 1e6 / bw_peak, peak_source=src)
+    out["clocks"] = _CLOCKS[-1] if _CLOCKS else None
     print(json.dumps(out))
 
 

@@ -32,6 +32,9 @@ class HaloExchange:
         self._buf = None
         self._hdl = None
         self._flag = torch.zeros(1, device=self.device)
+        import os
+        self._nccl_barrier = os.environ.get("AERIS_HALO_NCCL_BARRIER") == "1"
+        self._rank_barrier = None
         self._pool: list[torch.Tensor] = []       # two alternating symmetric output buffers
         self._pool_ptrs: list[list[int]] = []
         self._pool_hdl: list = []
@@ -46,8 +49,15 @@ class HaloExchange:
         self._peer_ptrs = [int(p) for p in self._hdl.buffer_ptrs]
 
     def _barrier(self):
-        # stream-ordered rank barrier (tiny NCCL all-reduce on the current stream)
-        dist.all_reduce(self._flag, group=self.group)
+        """Stream-ordered rank barrier: epoch flags in peer memory (one small kernel, release stores to every peer and
+        a bounded acquire spin on the own flags), or with AERIS_HALO_NCCL_BARRIER=1 a one-element NCCL all-reduce."""
+        if self._nccl_barrier:
+            dist.all_reduce(self._flag, group=self.group)
+            return
+        if self._rank_barrier is None:
+            from ..engine.fused_dp import RankBarrier
+            self._rank_barrier = RankBarrier(self.group, self.device)
+        self._rank_barrier()
 
     def output_buffer(self, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         """``[rows, cols]`` tensor inside the symmetric buffer whose turn it is (collective on first use and whenever a

@@ -1,0 +1,109 @@
+"""Replay of the device-side signalling protocols under adversarial schedules, on the CPU.
+
+The kernels synchronise ranks through monotone epoch words in peer memory (``csrc/comm.cu``: rank r release-stores
+its epoch into word r of every peer's flag row and acquire-spins on its own row until every word has reached the
+epoch, comparing with a signed 32-bit difference) and through monotone arrival counters (``csrc/gemm_ag.cuh``). Here
+the same rules run as interleaved atomic steps chosen by hypothesis, and the safety properties are checked: nobody
+leaves barrier k before everybody entered it, data written before a barrier is seen after it, a slow rank several
+epochs behind never lets a fast rank through, and the comparison survives the 32-bit wrap of the epoch."""
+import numpy as np
+from hypothesis import given, settings, strategies as st
+
+MASK = 0xFFFFFFFF
+
+
+def _behind(seen: int, epoch: int) -> bool:
+    """``static_cast<int32_t>(seen - epoch) < 0`` of the kernels."""
+    d = (seen - epoch) & MASK
+    return d >= 0x80000000
+
+
+class Rank:
+    def __init__(self, r, world, epoch0):
+        self.r, self.world, self.epoch = r, world, epoch0
+        self.phase, self.k = "work", 0          # work -> store(q = 0..world-1) -> spin -> work ...
+        self.q = 0
+        self.entered, self.left = [], []
+
+
+def _run(world, rounds, schedule, epoch0):
+    flags = np.full((world, world), epoch0 & MASK, dtype=np.uint64)      # flags[r][q]: q's epoch as seen by r
+    data = np.zeros(world, dtype=np.int64)                               # "payload" each rank writes before a barrier
+    ranks = [Rank(r, world, epoch0 & MASK) for r in range(world)]
+    seen_after = [[] for _ in range(world)]
+    steps = 0
+    it = iter(schedule)
+    while any(x.k < rounds for x in ranks):
+        steps += 1
+        assert steps < 200_000, "no progress: the protocol dead-locked"
+        try:
+            r = next(it) % world
+        except StopIteration:
+            r = steps % world                   # after the adversarial prefix: round robin until everybody is done
+        x = ranks[r]
+        if x.k >= rounds:
+            continue
+        if x.phase == "work":
+            data[r] = x.k + 1                   # the write that the barrier has to publish
+            x.epoch = (x.epoch + 1) & MASK
+            x.entered.append(steps)
+            x.phase, x.q = "store", 0
+        elif x.phase == "store":                # one release store per step: peers may run in between
+            flags[x.q][r] = x.epoch
+            x.q += 1
+            if x.q == world:
+                x.phase = "spin"
+        else:
+            if all(not _behind(int(flags[r][q]), x.epoch) for q in range(world)):
+                seen_after[r].append(data.copy())
+                x.left.append(steps)
+                x.k += 1
+                x.phase = "work"
+    return ranks, seen_after
+
+
+@settings(max_examples=150, deadline=None)
+@given(world=st.integers(2, 8), rounds=st.integers(1, 5), schedule=st.lists(st.integers(0, 7), max_size=400),
+       epoch0=st.sampled_from([0, 1, 0x7FFFFFFE, 0xFFFFFFFD]))
+def test_epoch_barrier_is_safe_under_any_interleaving(world, rounds, schedule, epoch0):
+    ranks, seen_after = _run(world, rounds, schedule, epoch0)
+    for k in range(rounds):
+        last_entry = max(x.entered[k] for x in ranks)
+        assert all(x.left[k] > last_entry for x in ranks), "a rank left the barrier before every rank had entered it"
+        for r in range(world):
+            assert (seen_after[r][k] >= k + 1).all(), "a write made before the barrier is not visible after it"
+
+
+def test_fast_rank_cannot_lap_a_slow_one():
+    """One rank runs ahead as far as the protocol lets it (it is scheduled exclusively): it must stop inside its
+    first barrier, because the others have not arrived."""
+    ranks, _ = _run(3, 1, [0] * 50 + [1, 2] * 50, epoch0=0)
+    assert ranks[0].left[0] > max(ranks[1].entered[0], ranks[2].entered[0])
+
+
+@settings(max_examples=100, deadline=None)
+@given(n_chunks=st.integers(1, 6), schedule=st.lists(st.integers(0, 1), max_size=200), call=st.integers(1, 5))
+def test_arrival_counter_consumer_never_reads_a_chunk_early(n_chunks, schedule, call):
+    """All-gather -> GEMM: the producer copies chunk c, then bumps the monotone arrival word to ``call``; the consumer's
+    tile for chunk c waits until the word has reached the value of this call. Counters are never reset between calls,
+    so a value left by an earlier call must not satisfy the wait."""
+    arrived = [call - 1] * n_chunks            # state after the previous call
+    copied = [False] * n_chunks
+    pc, cc = 0, 0                              # producer / consumer progress
+    it = iter(schedule)
+    guard = 0
+    while cc < n_chunks:
+        guard += 1
+        assert guard < 10_000
+        who = next(it, guard % 2)
+        if who == 0 and pc < 2 * n_chunks:
+            c, half = divmod(pc, 2)
+            if half == 0:
+                copied[c] = True
+            else:
+                arrived[c] = call
+            pc += 1
+        elif who == 1:
+            if arrived[cc] - call >= 0:
+                assert copied[cc], "consumer passed the wait before the chunk was copied"
+                cc += 1

@@ -62,7 +62,7 @@ def test_gemm_epilogues(M, N, K):
 
 
 @pytest.mark.parametrize("nw,N,H,d", [(2, 64, 2, 64), (3, 256, 2, 64), (3, 900, 4, 64), (2, 900, 2, 128), (2, 100, 1, 64),
-                                        (2, 64, 4, 32), (2, 900, 2, 32)])
+                                        (2, 64, 4, 32), (2, 900, 2, 32), (1, 3600, 2, 128), (1, 3600, 2, 64)])
 def test_attention_fwd_bwd(nw, N, H, d):
     from aeris_gb_b200.ops import attention as A
     qkv = torch.randn(nw * N, 3 * H * d, device=DEV).bfloat16()
@@ -100,6 +100,54 @@ def test_attention_fwd_rising_scores(N, d):
     q, k, _ = qkv.float().view(nw, N, 3, H, d).permute(2, 0, 3, 1, 4)
     lref = torch.logsumexp((q @ k.transpose(-1, -2)) / math.sqrt(d), -1) / math.log(2)
     assert (lse - lref).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("variant", [0, 2, 3, 4])
+def test_attention_fwd_softmax_variants(variant):
+    """The head_dim-64 forward kernel with two-wide fp32 softmax arithmetic and part of the exponentials on the
+    polynomial exp2: plain and strongly rising scores against the fp32 formulation, same tolerances as the default."""
+    from aeris_gb_b200.ops import attention as A
+    A.set_fwd_variant(variant)
+    try:
+        nw, N, H, d = 3, 900, 4, 64
+        qkv = torch.randn(nw * N, 3 * H * d, device=DEV).bfloat16()
+        o, lse = A.attn_fwd(qkv, nw, N, H, d)
+        ref = A.attn_reference(qkv.float(), nw, N, H, d)
+        assert rel_err(o, ref) < TOL
+        q, k, _ = qkv.float().view(nw, N, 3, H, d).permute(2, 0, 3, 1, 4)
+        lref = torch.logsumexp((q @ k.transpose(-1, -2)) / math.sqrt(d), -1) / math.log(2)
+        assert (lse - lref).abs().max().item() < 1e-3
+        g = torch.Generator(device=DEV).manual_seed(3)
+        r = torch.randn(nw, N, 3, H, d, device=DEV, generator=g)
+        r[:, :, 0] *= 3.0
+        r[:, :, 1] *= torch.linspace(0.2, 6.0, N, device=DEV).view(1, N, 1, 1)
+        r = r.reshape(nw * N, 3 * H * d).bfloat16()
+        o2, _ = A.attn_fwd(r, nw, N, H, d)
+        assert torch.isfinite(o2.float()).all()
+        assert rel_err(o2, A.attn_reference(r.float(), nw, N, H, d)) < 1.5e-2
+    finally:
+        A.set_fwd_variant(-1)
+
+
+def test_attention_bwd_rising_scores():
+    """Backward on scores that spread over many powers of two along the key sequence (sharp softmax rows): the
+    recomputed probabilities come from the forward's log-sum-exp, so nothing may overflow or lose the small terms."""
+    from aeris_gb_b200.ops import attention as A
+    nw, N, H, d = 2, 900, 2, 64
+    g = torch.Generator(device=DEV).manual_seed(5)
+    r = torch.randn(nw, N, 3, H, d, device=DEV, generator=g)
+    r[:, :, 0] *= 2.0
+    r[:, :, 1] *= torch.linspace(0.2, 4.0, N, device=DEV).view(1, N, 1, 1)
+    qkv = r.reshape(nw * N, 3 * H * d).bfloat16()
+    go = torch.randn(nw * N, H * d, device=DEV, generator=g).bfloat16()
+    o, lse = A.attn_fwd(qkv, nw, N, H, d)
+    dqkv = A.attn_bwd(qkv, o, go, lse, nw, N, H, d)
+    x = qkv.float().requires_grad_(True)
+    A.attn_reference(x, nw, N, H, d).backward(go.float())
+    assert torch.isfinite(dqkv.float()).all()
+    HD = H * d
+    for i in range(3):
+        assert rel_err(dqkv[:, i * HD:(i + 1) * HD], x.grad[:, i * HD:(i + 1) * HD]) < 2e-2
 
 
 @pytest.mark.parametrize("D", [128, 1536])
