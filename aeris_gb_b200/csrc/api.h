@@ -28,9 +28,10 @@ int aeris_attn_bwd(const void* qkv, int ldq, int q_col0, int k_col0, int v_col0,
 int aeris_gemm_scatter_heads(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int b_mn,
                              const void* const* peers, int sp, int sp_rank, int n_local, int L, int sec_w, int* status,
                              void* stream);
-// Softmax arithmetic of the head_dim-64 forward kernel (-1 scalar; 0, 2, 3, 4 two-wide with that many of every eight
-// score pairs on the polynomial exp2). Returns non-zero for an unknown variant.
-int aeris_attn_set_fwd_variant(int poly);
+// Variant of the attention forward kernel: poly = softmax arithmetic at head_dim 64 (-1 scalar; 0 two-wide; 2 two-wide
+// with two of every eight score pairs on the polynomial exp2); p_in_tmem = probabilities kept in tensor memory as the
+// A operand of P V. Returns non-zero for an unknown variant.
+int aeris_attn_set_fwd_variant(int poly, int p_in_tmem);
 // Checking build (-DAERIS_BOUNDS_CHECK) only: status word and source rows for the gathers launched next; returns 1 when
 // the library validates gather codes, 0 when it was built without the checks.
 int aeris_debug_set_gather_bounds(int* status, unsigned src_rows);

@@ -152,31 +152,63 @@ __device__ __forceinline__ void rescale_tmem_rows(uint32_t taddr, int cols, floa
   tmem_wait_st();
 }
 
+// Depth of the K and V rings of the forward kernel: at head_dim 64 three CTAs of 72 KB share an SM, at 128 two of 112 KB.
+#ifdef AERIS_ATTN_TRACE
+// Measurement build only: warp 2, lane 0 of CTA (0, 0, 0) stamps clock64 at the phase boundaries of every tile.
+__device__ long long* g_attn_trace = nullptr;
+#define ATTN_STAMP(slot) do { if (trace_on) g_attn_trace[(j) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define ATTN_STAMP(slot) do { } while (0)
+#endif
+
+// Forward kernel modes. 0: probabilities through shared memory, three CTAs per SM at head_dim 64. 1: probabilities in
+// tensor memory, over the score columns they came from (P V takes its A operand from TMEM). 2: as 1 with four lighter
+// CTAs per SM. (A variant with two score buffers, which computes the scores of tile j + 1 under the softmax of tile j
+// without the shared-memory round trip, fits only two CTAs per SM and measured no faster.)
+template <int DCH, int MODE> struct AttnFwdRing {
+  static constexpr int NSK = (DCH == 1 && MODE != 2) ? 3 : 2;
+  static constexpr int NSV = 2;
+  static constexpr int MIN_CTAS = (DCH == 2) ? 2 : (MODE == 2 ? 4 : 3);
+};
+
 // POLY < 0: scalar softmax arithmetic, every exponential on the exp unit; POLY >= 0: two-wide fp32 arithmetic with POLY of
 // every eight score pairs exponentiated by the polynomial.
-template <int DCH, int POLY>
-__global__ void __launch_bounds__(ATT_THREADS, (DCH == 1) ? 3 : 2)
+// PTMEM: the probabilities never touch shared memory. Each softmax thread writes its row of bf16 pairs back into the
+// TMEM columns it has just read the scores from, and P V takes its A operand from tensor memory. An M128 x N64 x K16
+// product with both operands in shared memory reads 6 KB for 32 cycles of math, more than the 128 B/cycle the shared
+// memory delivers, so the kernel with P in shared memory (16 KB written and 16 KB read back per tile, on top of
+// Q, K and V) is bound by shared-memory bandwidth rather than by the tensor or the exp unit.
+template <int DCH, int POLY, int MODE>
+__global__ void __launch_bounds__(ATT_THREADS, AttnFwdRing<DCH, MODE>::MIN_CTAS)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
   constexpr int HD = 64 * DCH;
   constexpr int Q_BYTES = DCH * 16384;
-  constexpr int KV_BYTES = 2 * DCH * 8192;  // K tile + V tile (64 rows each)
-  constexpr int NST = 2;
-  constexpr int P_BYTES = 16384;            // [128 x 64] bf16
+  constexpr int T_BYTES = DCH * 8192;       // one K tile or one V tile (64 rows)
+  // K and V travel in rings of their own: a K tile is free as soon as its Q K^T has completed, a whole softmax before
+  // the V tile of the same step, so its successor is requested that much earlier and the load latency hides behind
+  // the softmax of the tiles in between.
+  constexpr bool PTMEM = MODE != 0;
+  constexpr int NSK = AttnFwdRing<DCH, MODE>::NSK, NSV = AttnFwdRing<DCH, MODE>::NSV;
+  constexpr int P_BYTES = PTMEM ? 0 : 16384;   // [128 x 64] bf16
   constexpr int TMEM_COLS = (DCH == 1) ? 128 : 256;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + Q_BYTES;
-  uint8_t* sP = sKV + NST * KV_BYTES;
+  uint8_t* sKr = sQ + Q_BYTES;
+  uint8_t* sVr = sKr + NSK * T_BYTES;
+  uint8_t* sP = sVr + NSV * T_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;     // scores of tile j are in TMEM
-  uint64_t* s_free = bars + 6;     // every softmax warp has read them into registers
-  uint64_t* p_full = bars + 7;     // probabilities of tile j are in shared memory
-  uint64_t* pv_done = bars + 8;    // P V of tile j has completed (P buffer reusable, accumulator up to date)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* k_full = bars + 1;     // [NSK <= 4]
+  uint64_t* k_empty = bars + 5;    // [NSK <= 4]
+  uint64_t* v_full = bars + 9;     // [NSV <= 4]
+  uint64_t* v_empty = bars + 13;   // [NSV <= 4]
+  uint64_t* s_full = bars + 17;    // scores of tile j are in TMEM
+  uint64_t* s_free = bars + 18;    // every softmax warp has read them into registers
+  uint64_t* p_full = bars + 19;    // probabilities of tile j are in shared memory
+  uint64_t* pv_done = bars + 20;   // P V of tile j has completed (P buffer reusable, accumulator up to date)
+  static_assert(NSK <= 4 && NSV <= 4, "barrier slots");
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -200,7 +232,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
     mbar_init(q_full, 1);
-    for (int i = 0; i < NST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < NSK; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < NSV; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
     // only the softmax warps that own at least one real query row take part in the hand-shakes: a warp without rows
     // would run a tile ahead of the others and its arrivals would complete a phase that belongs to the slower warps
     const int n_valid_warps = min(4, (N - qt * TILE + 31) / 32);
@@ -221,32 +254,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < DCH; ++c)
         tma_load_3d(sQ + c * 16384, &tm_q, q_full, p.q_col0 + head * HD + c * 64, qt * TILE, win);
-      int st = 0;
-      uint32_t ph = 0;
-      for (int j = 0; j < nkv; ++j) {
-        if (!mbar_wait(&kv_empty[st], ph ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
-        uint8_t* sK = sKV + st * KV_BYTES;
-        uint8_t* sV = sK + DCH * 8192;
-        mbar_expect_tx(&kv_full[st], KV_BYTES);
+      // K_i, then V_{i-1}: the order in which their slots come free (K_i after Q K^T of tile i - NSK, V_{i-1} after P V
+      // of tile i - 1 - NSV, which completes later), so no wait holds up a load whose slot is already free
+      for (int i = 0; i <= nkv; ++i) {
+        if (i < nkv) {
+          const int st = i % NSK;
+          if (!mbar_wait(&k_empty[st], ((i / NSK) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
+          mbar_expect_tx(&k_full[st], T_BYTES);
 #pragma unroll
-        for (int c = 0; c < DCH; ++c) {
-          tma_load_3d(sK + c * 8192, &tm_k, &kv_full[st], p.k_col0 + head * HD + c * 64, j * KVT, win);
-          tma_load_3d(sV + c * 8192, &tm_v, &kv_full[st], p.v_col0 + head * HD + c * 64, j * KVT, win);
+          for (int c = 0; c < DCH; ++c)
+            tma_load_3d(sKr + st * T_BYTES + c * 8192, &tm_k, &k_full[st], p.k_col0 + head * HD + c * 64, i * KVT, win);
         }
-        if (++st == NST) { st = 0; ph ^= 1; }
+        if (i >= 1) {
+          const int j = i - 1, st = j % NSV;
+          if (!mbar_wait(&v_empty[st], ((j / NSV) & 1) ^ 1, p.status, ERR_TIMEOUT_ATTN)) break;
+          mbar_expect_tx(&v_full[st], T_BYTES);
+#pragma unroll
+          for (int c = 0; c < DCH; ++c)
+            tma_load_3d(sVr + st * T_BYTES + c * 8192, &tm_v, &v_full[st], p.v_col0 + head * HD + c * 64, j * KVT, win);
+        }
       }
     }
   } else if (warp == 1) {
     if (elect_one_sync()) {
       bool ok = mbar_wait(q_full, 0, p.status, ERR_TIMEOUT_ATTN);
-      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aKV = smem_u32(sKV);
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aKr = smem_u32(sKr), aVr = smem_u32(sVr);
       // S = Q K_j^T  (A = Q K-major, B = K K-major, reduction over d)
       auto issue_qk = [&](int j) -> bool {
-        const int st = j % NST;
-        if (!mbar_wait(&kv_full[st], (j / NST) & 1, p.status, ERR_TIMEOUT_ATTN)) return false;
+        const int st = j % NSK;
+        if (!mbar_wait(&k_full[st], (j / NSK) & 1, p.status, ERR_TIMEOUT_ATTN)) return false;
         tc_fence_after();
         const int ncur = (j == nkv - 1) ? n_last : KVT;
-        const uint32_t aK = aKV + st * KV_BYTES;
+        const uint32_t aK = aKr + st * T_BYTES;
         const uint32_t idesc_qk = make_idesc_bf16(TILE, ncur, 0, 0);
 #pragma unroll
         for (int kk = 0; kk < 4 * DCH; ++kk) {
@@ -255,27 +294,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_ss(tS, make_smem_desc(aQ + qoff, 0, 1024), make_smem_desc(aK + koff, 0, 1024), idesc_qk, kk > 0);
         }
         tc_commit(s_full);
+        tc_commit(&k_empty[st]);       // the K tile is free once these products have completed
         return true;
       };
       if (ok) ok = issue_qk(0);
       for (int j = 0; j < nkv && ok; ++j) {
-        const int st = j % NST;
+        const int st = j % NSV;
         const int ncur = (j == nkv - 1) ? n_last : KVT;
-        if (j + 1 < nkv) {     // the next tile's scores, as soon as this tile's have been read out of TMEM
-          if (!mbar_wait(s_free, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
-          tc_fence_after();
-          if (!issue_qk(j + 1)) { ok = false; break; }
+        if constexpr (!PTMEM) {
+          if (j + 1 < nkv) {     // the next tile's scores, as soon as this tile's have been read out of TMEM
+            if (!mbar_wait(s_free, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+            tc_fence_after();
+            if (!issue_qk(j + 1)) { ok = false; break; }
+          }
         }
+        if (!mbar_wait(&v_full[st], (j / NSV) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
         if (!mbar_wait(p_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
         tc_fence_after();
         // O += P_j V_j  (A = P K-major over kv, B = V MN-major: d contiguous, kv rows strided)
-        const uint32_t aV = aKV + st * KV_BYTES + DCH * 8192;
+        const uint32_t aV = aVr + st * T_BYTES;
         const uint32_t idesc_pv = make_idesc_bf16(TILE, HD, 0, 1);
-        for (int kk = 0; kk < ncur / 16; ++kk)
-          umma_ss(tO, make_smem_desc(aP + kk * 32, 0, 1024), make_smem_desc(aV + kk * 2048, 8192, 1024), idesc_pv,
-                  (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < ncur / 16; ++kk) {
+          const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
+          if constexpr (PTMEM)      // A = P in the score columns: 16 bf16 = 8 columns per K step
+            umma_ts(tO, tS + kk * 8, make_smem_desc(aV + kk * 2048, 8192, 1024), idesc_pv, acc);
+          else
+            umma_ss(tO, make_smem_desc(aP + kk * 32, 0, 1024), make_smem_desc(aV + kk * 2048, 8192, 1024), idesc_pv, acc);
+        }
         tc_commit(pv_done);
-        tc_commit(&kv_empty[st]);
+        tc_commit(&v_empty[st]);
+        if constexpr (PTMEM) {
+          // the tensor core executes in issue order: these scores overwrite P_j only after P_j V_j has consumed it
+          if (j + 1 < nkv && !issue_qk(j + 1)) { ok = false; break; }
+        }
       }
     }
   } else {
@@ -301,22 +352,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       m_ref = m_new;
       return true;
     };
+#ifdef AERIS_ATTN_TRACE
+    const bool trace_on = g_attn_trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&
+                          warp == 2 && lane == 0;
+#endif
     for (int j = 0; j < nkv && ok && warp_valid; ++j) {
       const bool last = (j == nkv - 1);
+      ATTN_STAMP(0);
+      const uint32_t tSj = tS;
       if (!mbar_wait(s_full, j & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
       tc_fence_after();
+      ATTN_STAMP(1);
       bool waited = false;
       if (!last || rem == 0) {
         // full 64-column tile: one TMEM read, scores stay in registers, the TMEM buffer is released at once
         uint32_t v0[32], v1[32];
         if (warp_valid) {
-          tmem_ld32(tS + lane_addr, v0);
-          tmem_ld32(tS + lane_addr + 32, v1);
+          tmem_ld32(tSj + lane_addr, v0);
+          tmem_ld32(tSj + lane_addr + 32, v1);
           tmem_wait_ld();
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(s_free);
+        ATTN_STAMP(2);
+        if constexpr (!PTMEM) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_free);
+        }
         if (warp_valid) {
           // four independent chains of eight 3-input maxima instead of one chain of thirty-two
           float mxc[4];
@@ -334,6 +395,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (__any_sync(0xffffffffu, m_new - m_ref > RESCALE_LOG2)) {
             if (!rescale(j, m_new, waited)) { ok = false; break; }
           }
+          ATTN_STAMP(3);
           uint32_t pk[32];
           if constexpr (POLY >= 0) {
             l += softmax_row64<POLY>(v0, v1, sl2, m_ref, pk);
@@ -355,10 +417,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
           }
-          if (j > 0 && !waited && !mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+          ATTN_STAMP(4);
+          if constexpr (PTMEM) {
+            // scores of tile j exist, so P V of tile j - 1 (issued before them) is done: the columns are this thread's
+            tmem_st32(tSj + lane_addr, pk);
+            tmem_wait_st();
+          } else {
+            if (j > 0 && !waited && !mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
 #pragma unroll
-          for (int g = 0; g < 8; ++g)
-            *reinterpret_cast<uint4*>(sP + swz128(row, g)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+            for (int g = 0; g < 8; ++g)
+              *reinterpret_cast<uint4*>(sP + swz128(row, g)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+          }
         }
       } else {
         // last, partial tile: n_last (multiple of 16) columns computed, `rem` of them valid; no tile follows
@@ -367,7 +436,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll 1
           for (int c = 0; c < n_last; c += 16) {
             uint32_t v[16];
-            tmem_ld16(tS + lane_addr + c, v);
+            tmem_ld16(tSj + lane_addr + c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i)
@@ -377,12 +446,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (__any_sync(0xffffffffu, m_new - m_ref > RESCALE_LOG2)) {
             if (!rescale(j, m_new, waited)) { ok = false; break; }
           }
-          if (j > 0 && !waited && !mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+          if constexpr (!PTMEM) {
+            if (j > 0 && !waited && !mbar_wait(pv_done, (j - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) { ok = false; break; }
+          }
           float rs = 0.f;
 #pragma unroll 1
           for (int c = 0; c < n_last; c += 16) {
             uint32_t v[16], pk[8];
-            tmem_ld16(tS + lane_addr + c, v);
+            tmem_ld16(tSj + lane_addr + c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -393,21 +464,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               rs += p0 + p1;
               pk[i] = pack_bf16x2(p0, p1);
             }
+            if constexpr (PTMEM) {
+              // 16 scores become 8 columns of bf16 pairs at column c / 2 <= c: only scores already consumed are overwritten
+              tmem_st8(tSj + lane_addr + (c >> 1), pk);
+            } else {
 #pragma unroll
-            for (int g = 0; g < 2; ++g)
-              *reinterpret_cast<uint4*>(sP + swz128(row, (c >> 3) + g)) =
-                  make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+              for (int g = 0; g < 2; ++g)
+                *reinterpret_cast<uint4*>(sP + swz128(row, (c >> 3) + g)) =
+                    make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+            }
           }
+          if constexpr (PTMEM) tmem_wait_st();
           l += rs;
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(s_free);
+        if constexpr (!PTMEM) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_free);
+        }
       }
-      fence_proxy_async_smem();
+      ATTN_STAMP(5);
+      if constexpr (!PTMEM) fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
+      ATTN_STAMP(6);
     }
     if (ok && warp_valid && mbar_wait(pv_done, (nkv - 1) & 1, p.status, ERR_TIMEOUT_ATTN)) {
       tc_fence_after();
@@ -448,18 +529,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <int DCH, int POLY>
+static int g_fwd_smem_pad = 0;   // extra dynamic shared memory per CTA: lowers the number of CTAs per SM (measurements)
+
+template <int DCH, int POLY, int MODE>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const AttnFwdParams& p, cudaStream_t stream) {
-  constexpr int SMEM = DCH * 16384 + 2 * 2 * DCH * 8192 + 16384 + 256;
-  static bool configured = false;
-  auto kern = attn_fwd_kernel<DCH, POLY>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -20;
-    configured = true;
+  constexpr int SMEM = DCH * 16384 + (AttnFwdRing<DCH, MODE>::NSK + AttnFwdRing<DCH, MODE>::NSV) * DCH * 8192 +
+                       (MODE != 0 ? 0 : 16384) + 256;
+  static int configured = -1;
+  auto kern = attn_fwd_kernel<DCH, POLY, MODE>;
+  const int smem = SMEM + g_fwd_smem_pad;
+  if (configured != smem) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
+    configured = smem;
   }
   dim3 grid((p.N + TILE - 1) / TILE, p.H, p.n_win);
-  kern<<<grid, ATT_THREADS, SMEM, stream>>>(tq, tk, tv, p);
+  kern<<<grid, ATT_THREADS, smem, stream>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
@@ -1007,12 +1092,25 @@ static int launch_attn_bwd(const CUtensorMap& tq128, const CUtensorMap& tk64, co
 
 using namespace aeris;
 
-// Softmax arithmetic of the head_dim-64 forward kernel: -1 = scalar, exp unit only; 0 = two-wide fp32 arithmetic;
-// 2, 3, 4 = two-wide with that many of every eight score pairs on the polynomial exp2.
+// Variant of the forward kernel. poly (head_dim 64 only): -1 = scalar softmax arithmetic, exp unit only; 0 = two-wide
+// fp32 arithmetic; 2 = two-wide with two of every eight score pairs on the polynomial exp2. mode: see AttnFwdRing
+// (0 probabilities through shared memory; 1 in tensor memory; 2 in tensor memory, four CTAs per SM).
 static int g_fwd_poly = -1;
-extern "C" int aeris_attn_set_fwd_variant(int poly) {
-  if (poly != -1 && poly != 0 && poly != 2 && poly != 3 && poly != 4) return -1;
+static int g_fwd_mode = 0;
+extern "C" int aeris_attn_set_fwd_variant(int poly, int mode) {
+  if ((poly != -1 && poly != 0 && poly != 2) || mode < 0 || mode > 2) return -1;
   g_fwd_poly = poly;
+  g_fwd_mode = mode;
+  return 0;
+}
+#ifdef AERIS_ATTN_TRACE
+extern "C" int aeris_attn_set_trace(long long* buf) {
+  return cudaMemcpyToSymbol(aeris::g_attn_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -1;
+}
+#endif
+extern "C" int aeris_attn_set_fwd_smem_pad(int bytes) {
+  if (bytes < 0 || bytes > 160 * 1024) return -1;
+  g_fwd_smem_pad = bytes;
   return 0;
 }
 
@@ -1058,14 +1156,20 @@ static int attn_fwd_impl(const void* q, int ldq, int q_col0, const void* k, int 
   if ((r = make_tmap_3d_bf16(&tq, q, ldq, N, n_win, ldq, static_cast<uint64_t>(N) * ldq, 64, TILE))) return r;
   if ((r = make_tmap_3d_bf16(&tk, k, ldk, N, n_win, ldk, static_cast<uint64_t>(N) * ldk, 64, KVT))) return r;
   if ((r = make_tmap_3d_bf16(&tv, v, ldv, N, n_win, ldv, static_cast<uint64_t>(N) * ldv, 64, KVT))) return r;
-  if (head_dim == 128) return launch_attn_fwd<2, -1>(tq, tk, tv, p, stream);
-  switch (g_fwd_poly) {            // head_dim 64: the exp unit is the limiter, see softmax_row64
-    case 0: return launch_attn_fwd<1, 0>(tq, tk, tv, p, stream);
-    case 2: return launch_attn_fwd<1, 2>(tq, tk, tv, p, stream);
-    case 3: return launch_attn_fwd<1, 3>(tq, tk, tv, p, stream);
-    case 4: return launch_attn_fwd<1, 4>(tq, tk, tv, p, stream);
-    default: return launch_attn_fwd<1, -1>(tq, tk, tv, p, stream);
+  if (head_dim == 128) {
+    switch (g_fwd_mode) {
+      case 1: return launch_attn_fwd<2, -1, 1>(tq, tk, tv, p, stream);
+      default: return launch_attn_fwd<2, -1, 0>(tq, tk, tv, p, stream);
+    }
   }
+  const bool poly = g_fwd_poly == 2;
+  switch (g_fwd_mode) {
+    case 1: return poly ? launch_attn_fwd<1, 2, 1>(tq, tk, tv, p, stream) : launch_attn_fwd<1, -1, 1>(tq, tk, tv, p, stream);
+    case 2: return launch_attn_fwd<1, -1, 2>(tq, tk, tv, p, stream);
+    default: break;
+  }
+  if (g_fwd_poly == 0) return launch_attn_fwd<1, 0, 0>(tq, tk, tv, p, stream);
+  return poly ? launch_attn_fwd<1, 2, 0>(tq, tk, tv, p, stream) : launch_attn_fwd<1, -1, 0>(tq, tk, tv, p, stream);
 }
 
 // Backward. qkv: fused [T, ldq] tensor (q/k/v column blocks at *_col0); o, d_o: [T, ldo]; dqkv: [T, ldg] (same

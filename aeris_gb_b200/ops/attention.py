@@ -60,13 +60,14 @@ def attn_fwd(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int, *, out: torc
     return out, lse
 
 
-def set_fwd_variant(poly: int) -> None:
-    """Softmax arithmetic of the head_dim-64 forward kernel: -1 = scalar fp32 with every exponential on the exp unit;
-    0 = two-wide fp32 instructions; 2, 3, 4 = two-wide with that many of every eight score pairs exponentiated by a
-    cubic polynomial on the FMA pipe (the exp unit is what limits attention at head_dim 64)."""
-    rc = _l.lib().aeris_attn_set_fwd_variant(int(poly))
+def set_fwd_variant(poly: int = -1, mode: int = 0) -> None:
+    """Variant of the forward kernel. ``poly`` (head_dim 64): -1 = scalar fp32 softmax arithmetic with every exponential
+    on the exp unit; 0 = two-wide fp32 instructions; 2 = two-wide with two of every eight score pairs exponentiated by
+    a cubic polynomial on the FMA pipe. ``mode``: 0 = probabilities through shared memory; 1 = probabilities kept in
+    tensor memory as the A operand of P V; 2 = as 1 with four lighter CTAs per SM."""
+    rc = _l.lib().aeris_attn_set_fwd_variant(int(poly), int(mode))
     if rc != 0:
-        raise ValueError(f"no forward variant {poly}")
+        raise ValueError(f"no forward variant poly={poly} mode={mode}")
 
 
 def attn_reference(qkv: torch.Tensor, n_win: int, N: int, H: int, d: int) -> torch.Tensor:

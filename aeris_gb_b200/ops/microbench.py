@@ -36,9 +36,17 @@ def _peaks():
 
 
 def _time(fn, iters):
+    """Mean milliseconds per launch: 3 warm-up launches, then at least ``iters`` launches and at least ~0.8 s of them,
+    so that the clock sampler (one sample per 200 ms) sees the kernel under load."""
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    iters = max(iters, min(20000, int(800.0 / max(e0.elapsed_time(e1), 1e-3))))
     clk = ClockSampler(torch.cuda.current_device())
     clk.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -73,7 +81,9 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--one-cta", action="store_true", help="force the one-CTA GEMM kernel")
     ap.add_argument("--fwd-variant", type=int, default=None,
-                    help="attn_fwd: softmax arithmetic of the head_dim-64 kernel (-1, 0, 2, 3, 4; see ops.attention)")
+                    help="attn_fwd: softmax arithmetic of the head_dim-64 kernel (-1, 0, 2; see ops.attention)")
+    ap.add_argument("--fwd-mode", type=int, default=0, help="attn_fwd: kernel mode 0..2 (see ops.attention.set_fwd_variant)")
+    ap.add_argument("--smem-pad", type=int, default=0, help="attn_fwd: extra shared memory per CTA (fewer CTAs per SM)")
     a = ap.parse_args()
     dev = "cuda"
     tf_peak, bw_peak, src = _peaks()
@@ -99,9 +109,12 @@ def main():
         qkv = torch.randn(nw * N, 3 * H * d, device=dev).bfloat16()
         o = torch.empty(nw * N, H * d, device=dev, dtype=torch.bfloat16)
         lse = torch.empty(nw, H, N, device=dev)
-        if a.fwd_variant is not None:
-            A.set_fwd_variant(a.fwd_variant)
-            out["fwd_variant"] = a.fwd_variant
+        if a.fwd_variant is not None or a.fwd_mode:
+            A.set_fwd_variant(a.fwd_variant if a.fwd_variant is not None else -1, a.fwd_mode)
+            out["fwd_variant"], out["fwd_mode"] = a.fwd_variant, a.fwd_mode
+        if a.smem_pad:
+            L.lib().aeris_attn_set_fwd_smem_pad(a.smem_pad)
+            out["smem_pad"] = a.smem_pad
         A.attn_fwd(qkv, nw, N, H, d, out=o, lse=lse)
         if a.kernel == "attn_fwd":
             ref = A.attn_reference(qkv[:2 * N], 2, N, H, d)

@@ -102,14 +102,15 @@ def test_attention_fwd_rising_scores(N, d):
     assert (lse - lref).abs().max().item() < 2e-2
 
 
-@pytest.mark.parametrize("variant", [0, 2, 3, 4])
-def test_attention_fwd_softmax_variants(variant):
-    """The head_dim-64 forward kernel with two-wide fp32 softmax arithmetic and part of the exponentials on the
-    polynomial exp2: plain and strongly rising scores against the fp32 formulation, same tolerances as the default."""
+@pytest.mark.parametrize("variant,mode,d", [(0, 0, 64), (2, 0, 64), (-1, 1, 64), (2, 1, 64), (-1, 2, 64), (-1, 1, 128)])
+def test_attention_fwd_variants(variant, mode, d):
+    """The forward kernel with two-wide fp32 softmax arithmetic, part of the exponentials on the polynomial exp2, and
+    the probabilities kept in tensor memory: plain and strongly rising scores (partial last tile included) against
+    the fp32 formulation, same tolerances as the default kernel."""
     from aeris_gb_b200.ops import attention as A
-    A.set_fwd_variant(variant)
+    A.set_fwd_variant(variant, mode)
     try:
-        nw, N, H, d = 3, 900, 4, 64
+        nw, N, H = 3, 900, 4
         qkv = torch.randn(nw * N, 3 * H * d, device=DEV).bfloat16()
         o, lse = A.attn_fwd(qkv, nw, N, H, d)
         ref = A.attn_reference(qkv.float(), nw, N, H, d)
@@ -126,7 +127,7 @@ def test_attention_fwd_softmax_variants(variant):
         assert torch.isfinite(o2.float()).all()
         assert rel_err(o2, A.attn_reference(r.float(), nw, N, H, d)) < 1.5e-2
     finally:
-        A.set_fwd_variant(-1)
+        A.set_fwd_variant(-1, 0)
 
 
 def test_attention_bwd_rising_scores():
