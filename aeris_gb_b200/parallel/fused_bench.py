@@ -5,9 +5,12 @@
 Sections (``--only tp,sp,halo,dp``): tensor-parallel MLP (all-gather -> GEMM, GEMM -> reduce-scatter), Ulysses
 sequence-parallel attention (head scatter in the QKV GEMM epilogue + token-owner push in the attention epilogue),
 window-parallel halo gather inside modulate+RMSNorm, and the gradient reduce-scatter + AdamW + all-gather step.
-Prints one JSON line (rank 0): times are CUDA-event milliseconds, max over ranks, median of ``--iters`` runs after
-warm-up. ``roofline_ms`` of a fused path is the slowest of FLOPs / ``--peak-tflops``, NVLink bytes per GPU and
-direction / ``--link-gbs`` and (memory-bound kernels) HBM bytes / ``--hbm-gbs``.
+Prints one JSON line (rank 0): times are CUDA-event milliseconds per call, max over ranks, median of five batches of
+``--iters`` back-to-back calls after warm-up (a batch is bracketed by a barrier and a device synchronisation).
+``roofline_ms`` of a fused path is the slowest of FLOPs / ``--peak-tflops``, NVLink bytes per GPU and direction /
+``--link-gbs`` and (memory-bound kernels) HBM bytes / ``--hbm-gbs``; the defaults are the measured copy bandwidth and
+the measured burst cuBLAS rate of ``MEASURED_PEAKS.json`` (these kernels are timed in isolation). ``clocks`` is the
+SM-clock and throttle-reason record of rank 0's GPU over the whole run.
 """
 from __future__ import annotations
 
@@ -22,23 +25,32 @@ from ..ops import gemm as G
 from . import tensor as TP
 
 
-def _time(fn, iters, warmup=3):
+def _time(fn, iters, warmup=3, batches=5):
     for _ in range(warmup):
         fn()
     ts = []
-    for _ in range(iters):
+    for _ in range(batches):
         dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        for _ in range(iters):
+            fn()
         e1.record()
         torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ts.append(t.item())
     ts.sort()
     return ts[len(ts) // 2]
+
+
+def _measured_peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    return 1590.0, 6650.0, "fallback"
 
 
 def bench_sp(a, dev, res):
@@ -153,19 +165,26 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="tp,sp,halo,dp")
     ap.add_argument("--params", type=int, default=1 << 29)
-    ap.add_argument("--hbm-gbs", type=float, default=6458.0)
+    ap.add_argument("--hbm-gbs", type=float, default=None)
     ap.add_argument("--rows", type=int, default=64800, help="gathered rows (all ranks)")
     ap.add_argument("--dim", type=int, default=1536)
     ap.add_argument("--hidden", type=int, default=4096)
-    ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--peak-tflops", type=float, default=1406.8)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--peak-tflops", type=float, default=None)
     ap.add_argument("--link-gbs", type=float, default=770.0)
     a = ap.parse_args()
+    tf, bw, src = _measured_peaks()
+    a.peak_tflops = a.peak_tflops or tf
+    a.hbm_gbs = a.hbm_gbs or bw
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=dev)
-    res = {"world": world}
+    res = {"world": world, "peak_tflops": a.peak_tflops, "hbm_gbs": a.hbm_gbs, "link_gbs": a.link_gbs,
+           "peak_source": src}
+    from ..utils.clocks import ClockSampler
+    clk = ClockSampler(int(os.environ["LOCAL_RANK"]))
+    clk.start()
     only = a.only.split(",")
     if "sp" in only and world in (2, 4, 8):
         bench_sp(a, dev, res)
@@ -177,6 +196,7 @@ def main():
         bench_tp(a, dev, res, rank, world)
     from ..ops import lib as L
     L.check_status()
+    res["clocks"] = clk.stop()
     if rank == 0:
         print(json.dumps(res))
     dist.barrier()
