@@ -1,6 +1,7 @@
-"""Worker of the GPU pipeline-parallel test: the instruction-schedule engine with NCCL p2p between the stages (PP = 2,
-one GPU per stage group, CUDA kernels in every block) has to reproduce the losses and the updated weights of the same
-engine with every stage on one GPU. argv[1] = 1 uses the overlapped 1F1B schedule."""
+"""Worker of the GPU pipeline-parallel test: the instruction-schedule engine with NCCL p2p between the stages (CUDA
+kernels in every block, peer-memory halo and Ulysses exchanges inside the stages) has to reproduce the losses and the
+updated weights of the same engine with every stage on one GPU. argv: overlap (1 = overlapped 1F1B schedule), PP,
+WP_X, SP (defaults: 0, world, 1, 1)."""
 import os
 import sys
 
@@ -27,20 +28,27 @@ def _idx(eng):
     return eng.loads
 
 
+def _block(img, eng):
+    hb, wb = IMG[0] // eng.grid.WP_Y, IMG[1] // eng.grid.WP_X
+    return img[:, eng.c.wp_y * hb:(eng.c.wp_y + 1) * hb, eng.c.wp_x * wb:(eng.c.wp_x + 1) * wb].contiguous()
+
+
 def build(grid, rank, dev, overlap, groups=None):
     cfg = AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=128, heads=2, head_dim=64,
-                      mlp_dim=256, n_layers=4, sublayers=1, norm_eps=1e-3, chunk_windows=5)
+                      mlp_dim=256, n_layers=4, sublayers=1, norm_eps=1e-3, chunk_windows=5, wp=(grid.WP_Y, grid.WP_X),
+                      sp=grid.SP)
     ecfg = EngineConfig(gas=4, overlap_p2p=overlap, checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5)
     eng = ParallelEngine(cfg, OptimConfig(lr=1e-2, lr_rampup_img=0, grad_clip_max_norm=1.0, weight_decay=0.0),
                          DiffusionConfig(grad_scale_parity=False, cond_channels=CC), ecfg, grid, rank, dev,
-                         data_fn=lambda e: (_field(1000 + _idx(e), CC), _field(2000 + _idx(e), CH)), groups=groups)
+                         data_fn=lambda e: (_block(_field(1000 + _idx(e), CC), e), _block(_field(2000 + _idx(e), CH), e)),
+                         groups=groups)
     for st, sd in eng.module.logical_state_dicts().items():     # identical weights for any split
         g = torch.Generator().manual_seed(100 + st)
         for k, v in sd.items():
             if v.dtype.is_floating_point and "inv_freq" not in k:
                 v.copy_((torch.randn(v.shape, generator=g) * 0.05).to(v.dtype))
     eng.opt = type(eng.opt)(eng.module, eng.ocfg)
-    eng.noise_fn = lambda e: _field(3000 + _idx(e), CH)
+    eng.noise_fn = lambda e: _block(_field(3000 + _idx(e), CH), e)
     eng.t_fn = lambda e: torch.tensor([0.2 + 0.13 * (_idx(e) % 9)])
     return eng
 
@@ -48,6 +56,9 @@ def build(grid, rank, dev, overlap, groups=None):
 def main():
     overlap = bool(int(sys.argv[1])) if len(sys.argv) > 1 else False
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    PP = int(sys.argv[2]) if len(sys.argv) > 2 else world
+    WPX = int(sys.argv[3]) if len(sys.argv) > 3 else 1
+    SP = int(sys.argv[4]) if len(sys.argv) > 4 else 1
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     import datetime
@@ -61,7 +72,7 @@ def main():
         ref_loss.append(float(ref.tot_loss))
     ref_sd = {st: {k: v.clone() for k, v in sd.items()} for st, sd in ref.module.logical_state_dicts().items()}
     del ref
-    eng = build(ProcessGrid(world, PP=world), rank, dev, overlap)
+    eng = build(ProcessGrid(world, PP=PP, WP_X=WPX, SP=SP), rank, dev, overlap)
     loss = []
     for _ in range(iters):
         eng.exec_schedule()
@@ -76,7 +87,7 @@ def main():
     ok = worst < 3e-2
     if eng.is_last_stage():
         ok = ok and all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(loss, ref_loss))
-        print(f"pp{world} overlap={overlap}: losses {loss} vs single-GPU {ref_loss}; worst weight diff {worst:.2e}", flush=True)
+        print(f"pp{PP} wp{WPX} sp{SP} overlap={overlap}: losses {loss} vs single-GPU {ref_loss}; worst weight diff {worst:.2e}", flush=True)
     flag = torch.tensor([0.0 if ok else 1.0], device=dev)
     dist.all_reduce(flag)
     dist.barrier()

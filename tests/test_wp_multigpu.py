@@ -61,3 +61,16 @@ def test_pipeline_parallel_nccl(overlap):
                         "--master-addr", "127.0.0.1", "--master-port", str(29560 + overlap), worker, str(overlap)],
                        capture_output=True, text=True, timeout=240)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("n,pp,wpx,sp", [(4, 2, 2, 1), (4, 2, 1, 2), (8, 2, 2, 2)])
+def test_pipeline_with_window_and_sequence_parallel_stages(n, pp, wpx, sp):
+    """PP x WP x SP on GPUs (overlapped 1F1B over NCCL p2p; halo pulls and Ulysses pushes over peer memory inside every
+    stage) against all stages on one GPU."""
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    worker = os.path.join(os.path.dirname(__file__), "pp_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29570 + n + sp), worker, "1", str(pp), str(wpx),
+                        str(sp)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
