@@ -1,7 +1,7 @@
 """Render rollout fields to an animated GIF on the CPU (matplotlib Agg backend; no GL, no display).
 
 Reference: scripts/animate.py:74-137, 189-232 (matplotlib + cartopy FuncAnimation from HDF5 rollouts). matplotlib and
-cartopy are not installed in the target image; the script imports them lazily and says so. Without cartopy the fields
+cartopy are optional dependencies: the script imports them lazily and says so when one is missing. Without cartopy the fields
 are drawn on a plain equirectangular axis.
 
     python -m aeris_gb_b200.cli.animate --input rollout.npy --variable 2m_temperature --out t2m.gif

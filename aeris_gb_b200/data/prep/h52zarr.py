@@ -2,7 +2,7 @@
 
 Reference: scripts/data_processing/bh52zarr_dist.py:126-262 with a dask-distributed cluster started by
 ``dask-launch.sh`` and a 10x retry loop around each write. The conversion needs ``zarr`` (and optionally ``dask``);
-neither is installed in the target image, so the module imports them lazily and the CLI reports what is missing. The
+both are optional dependencies: the module imports them lazily and the CLI reports what is missing. The
 chunked copy itself is a plain loop over (member, time) slabs that worker processes split by ``--rank/--world``.
 
     python -m aeris_gb_b200.data.prep.h52zarr --src rollout_dir --dst out.zarr --variables-from 73

@@ -36,8 +36,12 @@ def merge(src: str, dst: str, channels: int, rank: int = 0, world: int = 1, shap
     full_shape = (n, channels, *shape_hw)
     if rank == 0 and not os.path.exists(out_path):
         np.lib.format.open_memmap(out_path, mode="w+", dtype=np.float32, shape=full_shape).flush()
-    while not os.path.exists(out_path):      # other workers wait for rank 0 to create the file
-        pass
+    import time
+    t0 = time.monotonic()
+    while not os.path.exists(out_path):      # other workers wait (at most ten minutes) for rank 0 to create the file
+        if time.monotonic() - t0 > 600.0:
+            raise TimeoutError(f"rank {rank}: {out_path} was not created by rank 0 within 600 s")
+        time.sleep(0.2)
     out = np.lib.format.open_memmap(out_path, mode="r+")
     for i in my_range(n, rank, world):
         a = np.asarray(open_array(files[i])[...], dtype=np.float32)

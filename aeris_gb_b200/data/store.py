@@ -1,6 +1,6 @@
 """Array storage behind the datasets: HDF5 through ``h5py`` when it is installed, ``.npy`` memory maps otherwise.
 
-The reference reads HDF5 only (src/aeris/data/era5.py:346-358). The target image has no h5py, so every dataset goes
+The reference reads HDF5 only (src/aeris/data/era5.py:346-358). h5py is an optional dependency, so every dataset goes
 through :func:`open_array`, which accepts ``file.hdf5`` (dataset name ``input``) or ``file.npy`` and returns an object
 with ``shape`` and numpy-style indexing. :func:`save_array` writes the format the current environment can read back.
 """

@@ -1,4 +1,4 @@
-"""Hydra-compatible configuration surface without Hydra/OmegaConf (neither is installed in the target image).
+"""Hydra-compatible configuration surface without Hydra/OmegaConf (neither is a dependency of this package).
 
 Same key names at the global level as the reference's YAML tree (configs/train.yaml composing ``trainer/defaults``,
 ``optimizer/adamw`` and ``experiment/<name>``; keys listed in the reference at configs/experiment/train.yaml:1-86),

@@ -26,8 +26,10 @@ def main() -> int:
     work = os.path.join("/tmp", "aeris_ref_build")          # pip may write into the tree it builds from
     shutil.rmtree(work, ignore_errors=True)
     shutil.copytree(src, work)
-    cmd = [sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps", "--find-links",
-           "/opt/wheelhouse", "--target", DEST, work]
+    cmd = [sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps"]
+    if os.environ.get("PIP_FIND_LINKS_DIR"):           # an offline folder of wheels, where there is one
+        cmd += ["--find-links", os.environ["PIP_FIND_LINKS_DIR"]]
+    cmd += ["--target", DEST, work]
     r = subprocess.run(cmd, capture_output=True, text=True)
     how = "pip"
     if r.returncode != 0 or not os.path.isdir(os.path.join(DEST, "aeris")):
