@@ -142,11 +142,19 @@ def main(argv=None):
 
     if PP == 1 and (SP == 1 or device.type == "cuda"):
         # one process group per sample (WP x SP ranks, ordered wp_y, wp_x, sp), its SP sub-groups, and the weight group
-        groups = grid.build_groups(rank, kinds=("replica", "sp", "weight")) if world > 1 else {}
+        tp_on = mcfg.tp > 1             # model.TP: the MLP weights split over the SP group (or the WP group)
+        kinds = ("replica", "sp", "weight") + (("tp", "tp_ortho") if tp_on else ())
+        groups = grid.build_groups(rank, kinds=kinds) if world > 1 else {}
         mcfg.sp = SP
+        if tp_on:
+            tp_ranks = grid.tp_ranks(rank)
+            if mcfg.tp != len(tp_ranks):
+                raise SystemExit(f"model.TP = {mcfg.tp} must equal the size of the tensor-parallel group "
+                                 f"({len(tp_ranks)}: SP when SP > 1, else WP_Y x WP_X)")
+            mcfg.tp_rank = tp_ranks.index(rank)
         trainer = Trainer(mcfg, ocfg, dcfg, device, seed=int(cfg.seed), wp_group=groups.get("replica"),
                           dp_size=grid.DP, dp_rank=c.dp, weight_group=groups.get("weight"),
-                          sp_group=groups.get("sp"))
+                          sp_group=groups.get("sp"), tp_group=groups.get("tp"), tp_ortho_group=groups.get("tp_ortho"))
         trainer.timers.enabled = bool(cfg.trainer.get("report_timings", False))
         if cfg.model.get("load") and ckpt_dir:
             if load_stage_checkpoint(ckpt_dir, trainer.model, trainer.opt, device):

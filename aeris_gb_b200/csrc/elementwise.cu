@@ -208,7 +208,7 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
 // flushed with atomics at the end: dscale, dshift (fp32 [D], one modulation vector per launch) and dw (fp32 [D]).
 // MAXT / MINB: launch bounds by row width: up to 1536 columns 192 threads and two CTAs per SM (three were measured slower: spills), up to 5120 columns
 // 640 threads, wider rows 1024 threads (register cap 64: spills, but it launches).
-template <int MAXT, int MINB>
+template <int MAXT, int MINB, int RPI>
 __global__ void __launch_bounds__(MAXT, MINB)
 modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dh,
                                    const __nv_bfloat16* __restrict__ dres, const float* __restrict__ scale,
@@ -216,7 +216,10 @@ modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                                    __nv_bfloat16* __restrict__ dx, float* __restrict__ dscale,
                                    float* __restrict__ dshift, float* __restrict__ dw, int rows, int D, int mode,
                                    float eps, int rows_per_cta, const float* __restrict__ wf) {
-  __shared__ float red[2 * 2 * 32];
+  // RPI rows per iteration share one block-wide reduction, and the next RPI rows are requested before it: with
+  // RPI = 2 every thread keeps 12 sixteen-byte loads in flight (one row at a time left the memory system idle
+  // during the reduction)
+  __shared__ float red[2 * 2 * RPI * 32];
   const int c0 = threadIdx.x * 8;
   const bool active = c0 < D;
   float sc[8], sh[8], wv[8], a_sc[8], a_sh[8], a_w[8];
@@ -229,15 +232,22 @@ modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
   (void)rows_per_cta;
   const int r1 = rows;
+  const int stride = gridDim.x * RPI;
   int parity = 0;
-  // the next row's three vectors are requested before the current row is reduced
-  uint4 nx = make_uint4(0u, 0u, 0u, 0u), ng = nx, nr = nx;
-  auto fetch = [&](int r) {
-    if (active) {
-      const size_t off = static_cast<size_t>(r) * D + c0;
-      nx = *reinterpret_cast<const uint4*>(x + off);
-      ng = *reinterpret_cast<const uint4*>(dh + off);
-      if (dres) nr = *reinterpret_cast<const uint4*>(dres + off);
+  uint4 nx[RPI], ng[RPI], nr[RPI];
+#pragma unroll
+  for (int k = 0; k < RPI; ++k) nx[k] = ng[k] = nr[k] = make_uint4(0u, 0u, 0u, 0u);
+  // iteration `it` of this CTA covers rows it * stride + blockIdx.x + k * gridDim.x, k < RPI (interleaved with the others)
+  auto fetch = [&](int base) {
+#pragma unroll
+    for (int k = 0; k < RPI; ++k) {
+      const int r = base + k * static_cast<int>(gridDim.x);
+      if (active && r < r1) {
+        const size_t off = static_cast<size_t>(r) * D + c0;
+        nx[k] = *reinterpret_cast<const uint4*>(x + off);
+        ng[k] = *reinterpret_cast<const uint4*>(dh + off);
+        if (dres) nr[k] = *reinterpret_cast<const uint4*>(dres + off);
+      }
     }
   };
   auto unpack8 = [](const uint4& u, float (&f)[8]) {
@@ -249,63 +259,75 @@ modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       f[2 * i + 1] = t.y;
     }
   };
-  if (static_cast<int>(blockIdx.x) < r1) fetch(blockIdx.x);
-  for (int r = blockIdx.x; r < r1; r += gridDim.x, parity ^= 1) {
-    float v[8], g[8], dr[8];
-    unpack8(nx, v);
-    unpack8(ng, g);
-    unpack8(nr, dr);
-    if (r + static_cast<int>(gridDim.x) < r1) fetch(r + gridDim.x);
-    float o[8];
+  fetch(blockIdx.x);
+  for (int base = blockIdx.x; base < r1; base += stride, parity ^= 1) {
+    float v[RPI][8], g[RPI][8], dr[RPI][8];
+#pragma unroll
+    for (int k = 0; k < RPI; ++k) {
+      unpack8(nx[k], v[k]);
+      unpack8(ng[k], g[k]);
+      unpack8(nr[k], dr[k]);
+    }
+    if (base + stride < r1) fetch(base + stride);
+    float s[2 * RPI];
     if (mode == 0) {
-      // y = x(1+sc)+sh ; h = y * rinv * w
-      float y[8], gy[8];
-      float s[2] = {0.f, 0.f};
+      // y = x(1+sc)+sh ; h = y * rinv * w       (v <- y, g stays, gy recomputed after the reduction)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        y[i] = fmaf(v[i], sc[i], v[i]) + sh[i];
-        gy[i] = g[i] * wv[i];
-        s[0] += y[i] * y[i];
-        s[1] += y[i] * gy[i];
-      }
-      if (!active) { s[0] = 0.f; s[1] = 0.f; }
-      block_sum<2>(s, red, parity);
-      const float rinv = rsqrtf(s[0] / D + eps);
-      const float coef = rinv * rinv * rinv * (s[1] / D);
+      for (int k = 0; k < RPI; ++k) {
+        s[2 * k] = 0.f; s[2 * k + 1] = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float dy = rinv * gy[i] - y[i] * coef;
-        a_w[i] += g[i] * y[i] * rinv;
-        a_sc[i] += dy * v[i];
-        a_sh[i] += dy;
-        o[i] = dr[i] + fmaf(dy, sc[i], dy);
+        for (int i = 0; i < 8; ++i) {
+          const float y = fmaf(v[k][i], sc[i], v[k][i]) + sh[i];
+          s[2 * k] += y * y;
+          s[2 * k + 1] += y * (g[k][i] * wv[i]);
+        }
+        if (!active || base + k * static_cast<int>(gridDim.x) >= r1) { s[2 * k] = 0.f; s[2 * k + 1] = 0.f; }
       }
     } else {
       // n = x * rinv ; hn = n * w ; h = hn(1+sc)+sh
-      float gn[8];
-      float s[2] = {0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float dhn = fmaf(g[i], sc[i], g[i]);
-        gn[i] = dhn * wv[i];
-        s[0] += v[i] * v[i];
-        s[1] += v[i] * gn[i];
-      }
-      if (!active) { s[0] = 0.f; s[1] = 0.f; }
-      block_sum<2>(s, red, parity);
-      const float rinv = rsqrtf(s[0] / D + eps);
-      const float coef = rinv * rinv * rinv * (s[1] / D);
+      for (int k = 0; k < RPI; ++k) {
+        s[2 * k] = 0.f; s[2 * k + 1] = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float n = v[i] * rinv;
-        const float dhn = fmaf(g[i], sc[i], g[i]);
-        a_sc[i] += g[i] * n * wv[i];
-        a_sh[i] += g[i];
-        a_w[i] += dhn * n;
-        o[i] = dr[i] + rinv * gn[i] - v[i] * coef;
+        for (int i = 0; i < 8; ++i) {
+          const float gn = fmaf(g[k][i], sc[i], g[k][i]) * wv[i];
+          s[2 * k] += v[k][i] * v[k][i];
+          s[2 * k + 1] += v[k][i] * gn;
+        }
+        if (!active || base + k * static_cast<int>(gridDim.x) >= r1) { s[2 * k] = 0.f; s[2 * k + 1] = 0.f; }
       }
     }
-    if (active) store8(dx + static_cast<size_t>(r) * D + c0, o);
+    block_sum<2 * RPI>(s, red, parity);
+#pragma unroll
+    for (int k = 0; k < RPI; ++k) {
+      const int r = base + k * static_cast<int>(gridDim.x);
+      if (!active || r >= r1) continue;
+      const float rinv = rsqrtf(s[2 * k] / D + eps);
+      const float coef = rinv * rinv * rinv * (s[2 * k + 1] / D);
+      float o[8];
+      if (mode == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float y = fmaf(v[k][i], sc[i], v[k][i]) + sh[i];
+          const float dy = rinv * (g[k][i] * wv[i]) - y * coef;
+          a_w[i] += g[k][i] * y * rinv;
+          a_sc[i] += dy * v[k][i];
+          a_sh[i] += dy;
+          o[i] = dr[k][i] + fmaf(dy, sc[i], dy);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float n = v[k][i] * rinv;
+          const float dhn = fmaf(g[k][i], sc[i], g[k][i]);
+          a_sc[i] += g[k][i] * n * wv[i];
+          a_sh[i] += g[k][i];
+          a_w[i] += dhn * n;
+          o[i] = dr[k][i] + rinv * (dhn * wv[i]) - v[k][i] * coef;
+        }
+      }
+      store8(dx + static_cast<size_t>(r) * D + c0, o);
+    }
   }
   if (active) {
 #pragma unroll
@@ -593,8 +615,8 @@ extern "C" int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres
   if (rpc < 16) rpc = rows < 16 ? rows : 16;  // amortise the atomic flush of the column sums
   const int grid = (rows + rpc - 1) / rpc;    // every CTA takes about rpc rows, interleaved with the others
   const int nt = row_threads(D);
-  auto kern = (nt <= 192) ? modnorm_bwd_kernel<192, 2> : (nt <= 640) ? modnorm_bwd_kernel<640, 1>
-                                                                      : modnorm_bwd_kernel<1024, 1>;
+  auto kern = (nt <= 192) ? modnorm_bwd_kernel<192, 2, 2> : (nt <= 640) ? modnorm_bwd_kernel<640, 1, 1>
+                                                                         : modnorm_bwd_kernel<1024, 1, 1>;
   kern<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(dh),
       reinterpret_cast<const __nv_bfloat16*>(dres), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),

@@ -117,8 +117,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   const int kb_total = (p.K + G2_BK - 1) / G2_BK;
   const int kb_per_split = (kb_total + p.k_splits - 1) / p.k_splits;
   const int total_tiles = m_tiles * n_tiles * p.k_splits;
-  const int tm_rot = AG ? (p.ag_rank * p.ag_rows) / (2 * G2_BM) : 0;
-  auto phys_tm = [&](int tm) { return AG ? (tm + tm_rot) % m_tiles : tm; };
+  const int tm_rot = AG ? (p.ag_rank * p.ag_rows) / (2 * G2_BM) : p.tm_rot;
+  auto phys_tm = [&](int tm) { return (tm + tm_rot) % m_tiles; };
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_a);
@@ -386,6 +386,7 @@ extern "C" int aeris_gemm_rs_push(const void* A, const void* B, int M, int N, in
   p.b_tile_stride = G2_BN; p.b_half_off = G2_BN / 2;
   for (int i = 0; i < world; ++i) p.scat_peers[i] = const_cast<void*>(peers[i]);
   p.scat_rank = rank; p.scat_n_local = rows_per_rank; p.scat_ld = ld_dst;
+  p.tm_rot = static_cast<int>((static_cast<long long>((rank + 1) % world) * rows_per_rank) / (2 * G2_BM));
   CUtensorMap ta, tb;
   int r = make_tmap_2d_bf16(&ta, A, K, M, lda, G2_BK, G2_BM);
   if (r) return r;

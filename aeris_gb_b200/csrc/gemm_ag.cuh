@@ -5,9 +5,9 @@
 
 namespace aeris {
 
-// Two copier warps (6, 7): they sit on the schedulers of epilogue warps, not on those of the TMA-issuing warp 0 and the
-// MMA-issuing warp 1, whose single threads must never wait for an issue slot.
-constexpr int AG_COPY_THREADS = 64;
+// Four copier warps behind the six GEMM warps: 128 threads x 8 vectors keep 16 KB of posted peer stores in flight per
+// SM, which the link needs at 8 ranks (two warps reached 360 GB/s of egress there).
+constexpr int AG_COPY_THREADS = 128;
 constexpr int AG_UNROLL = 8;          // 16-byte vectors in flight per copier thread (local loads, posted peer stores)
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const unsigned* p) {

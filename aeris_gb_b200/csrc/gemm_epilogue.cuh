@@ -44,6 +44,9 @@ struct GemmParams {
   const unsigned* ag_count;
   unsigned ag_expect;
   int ag_world, ag_rank, ag_rows;
+  int tm_rot;       // first m-tile (of 256 rows) visited by the two-CTA kernel; the others follow cyclically. The
+                    // reduce-scatter GEMM starts at the rows of rank + 1 and ends with its own, so that at any moment
+                    // every rank pushes to a different owner and no GPU's ingress carries all the traffic
   int staged_out;   // bf16-output epilogues: move rows through the warp's shared-memory stage (coalesced global stores)
   int staged_red;   // split-K fp32 accumulation: stage 32 rows x 64 columns and issue the reductions row-contiguously
   int* status;

@@ -130,7 +130,11 @@ def save_stage_checkpoint(directory: str, module, opt, it: int | None = None, wr
     and ``write`` is True on one of them). Writes one file per logical stage the module holds."""
     if write:
         os.makedirs(directory, exist_ok=True)
-    model_sd = _logical(module, module.state_dict())
+    flat_sd = module.state_dict()
+    if getattr(opt, "tp_group", None) is not None:      # tensor-parallel shards are stored as full tensors
+        from ..parallel.tensor import full_state_dict
+        flat_sd = full_state_dict(flat_sd, opt.tp_group)
+    model_sd = _logical(module, flat_sd)
     if hasattr(opt, "host_copies"):
         opt.host_copies = write        # a sharded optimizer gathers collectively; only the writer copies to the host
     master = _logical(module, dict(opt.master_state_dict()))
@@ -214,9 +218,10 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     return True
 
 
-def load_stage_weights(directory: str, module, use_ema: bool = True) -> bool:
+def load_stage_weights(directory: str, module, use_ema: bool = True, tp: int = 1, tp_rank: int = 0) -> bool:
     """Inference: only the weights of the module's logical stages, from ``ema_state_dict`` (or ``model_state_dict``),
-    as the reference's inference engine does (src/aeris/parallelism/sp_inference_engine.py:552-573)."""
+    as the reference's inference engine does (src/aeris/parallelism/sp_inference_engine.py:552-573). ``tp`` /
+    ``tp_rank``: the module holds tensor-parallel shards of the stored full MLP weights."""
     which = "ema_state_dict" if use_ema else "model_state_dict"
     new = {}
     try:
@@ -232,6 +237,9 @@ def load_stage_weights(directory: str, module, use_ema: bool = True) -> bool:
     with torch.no_grad():
         for k, t in new.items():
             if k in own:
+                if tp > 1:
+                    from ..parallel.tensor import fit_to_shard
+                    t = fit_to_shard(k, t, own[k], tp, tp_rank)
                 own[k].copy_(t.to(own[k].dtype))
     return True
 

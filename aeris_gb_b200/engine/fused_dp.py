@@ -53,14 +53,15 @@ class _Seg:
 
 
 class FusedShardedOptimizer:
-    def __init__(self, model: nn.Module, cfg: OptimConfig, group, device, use_multicast: bool = True):
+    def __init__(self, model: nn.Module, cfg: OptimConfig, group, device, use_multicast: bool = True, params=None):
+        """``params``: the (name, parameter) pairs to manage; default: every trainable parameter of ``model``."""
         import torch.distributed._symmetric_memory as symm_mem
         self.cfg, self.group, self.device = cfg, group, torch.device(device)
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.step_count, self.cur_nimg = 0, 0
         nd = no_decay_names(model, cfg.decay_policy)
         segs: dict[tuple[bool, bool], _Seg] = {}
-        for n, p in model.named_parameters():
+        for n, p in (params if params is not None else model.named_parameters()):
             if not p.requires_grad:
                 continue
             key = (p.dtype != torch.float32, n not in nd)
@@ -133,8 +134,10 @@ class FusedShardedOptimizer:
         for s in self.segments:
             s.grad.zero_()
 
-    def reduce_and_step(self, batch_img: int, grad_scale: float) -> torch.Tensor:
-        """Whole update. Returns the device scalar with the squared global gradient norm (after scaling)."""
+    def reduce_and_step(self, batch_img: int, grad_scale: float, extra_sumsq: torch.Tensor | None = None) -> torch.Tensor:
+        """Whole update. Returns the device scalar with the squared global gradient norm (after scaling).
+        ``extra_sumsq``: squared norm (already scaled and complete) of gradients that another optimizer manages and
+        that count towards the same clipping norm (tensor-parallel shards)."""
         c, lib = self.cfg, L.lib()
         self.step_count += 1
         lr = lr_at(self.cur_nimg, c.lr, c)
@@ -155,6 +158,8 @@ class FusedShardedOptimizer:
         # the scalar reduction doubles as the barrier that says every rank has finished READING peer gradients
         dist.all_reduce(self._sumsq, group=self.group)
         self._sumsq += self._sumsq_local * (grad_scale * grad_scale)
+        if extra_sumsq is not None:
+            self._sumsq += extra_sumsq.to(self._sumsq.dtype)
         max_norm = c.grad_clip_max_norm if c.grad_clip else 0.0
         for s in self.segments:
             wd = c.weight_decay if s.decay else 0.0

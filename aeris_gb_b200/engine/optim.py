@@ -103,14 +103,15 @@ class FlatOptimizer:
     other parameter gets a post-accumulate hook that folds ``.grad`` into ``main_grad`` and frees it.
     """
 
-    def __init__(self, model: nn.Module, cfg: OptimConfig, device=None):
+    def __init__(self, model: nn.Module, cfg: OptimConfig, device=None, params=None):
+        """``params``: the (name, parameter) pairs to manage; default: every trainable parameter of ``model``."""
         self.cfg = cfg
         self.model = model
         self.step_count = 0
         self.cur_nimg = 0
         nd = no_decay_names(model, cfg.decay_policy)
         segs: dict[tuple[bool, bool], _Segment] = {}
-        for n, p in model.named_parameters():
+        for n, p in (params if params is not None else model.named_parameters()):
             if not p.requires_grad:
                 continue
             key = (p.dtype != torch.float32, n not in nd)
@@ -161,7 +162,7 @@ class FlatOptimizer:
 
     def grad_norm_sq(self, grad_scale: float) -> torch.Tensor:
         """Device scalar (float64): sum of squares of (grad * grad_scale) over this rank's buffers."""
-        dev = self.segments[0].grad.device
+        dev = self.segments[0].grad.device if self.segments else "cpu"
         if self._norm_sq is None:
             self._norm_sq = torch.zeros(1, dtype=torch.float64, device=dev)
         self._norm_sq.zero_()

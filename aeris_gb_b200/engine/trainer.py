@@ -44,7 +44,7 @@ class Trainer:
     def __init__(self, model_cfg: AerisConfig, optim_cfg: OptimConfig, diff_cfg: DiffusionConfig, device,
                  seed: int = 1234, wp_group=None, dp_size: int = 1, dp_rank: int = 0, model: AerisModel | None = None,
                  fused_dp: bool | None = None, use_multicast: bool = False, sp_group=None,
-                 fused_io: bool | None = None, weight_group=None):
+                 fused_io: bool | None = None, weight_group=None, tp_group=None, tp_ortho_group=None):
         self.cfg, self.ocfg, self.dcfg = model_cfg, optim_cfg, diff_cfg
         self.device = torch.device(device)
         # `wp_group`: every rank that shares a sample (WP grid x SP), ordered (wp_y, wp_x, sp); `sp_group`: the ranks that
@@ -53,6 +53,18 @@ class Trainer:
         self.sp_group = sp_group
         # `weight_group`: every rank that holds a replica of the weights (WP x SP x DP); gradients are reduced over it
         self.weight_group = weight_group if weight_group is not None else wp_group
+        # `tp_group` (model_cfg.tp > 1): the ranks that split the MLP weights between them; they hold different token
+        # rows of the same sample. Default: the SP group when sp > 1, else the WP group. `tp_ortho_group`: the ranks of
+        # the weight group that hold the same shard (None when the tensor-parallel group is the whole weight group)
+        self.tp_group = None
+        if model_cfg.tp > 1:
+            self.tp_group = tp_group if tp_group is not None else (sp_group if model_cfg.sp > 1 else wp_group)
+            assert self.tp_group is not None and dist.get_world_size(self.tp_group) == model_cfg.tp, \
+                "AerisConfig.tp must equal the size of the tensor-parallel group"
+            assert model_cfg.tp_rank == dist.get_rank(self.tp_group), "AerisConfig.tp_rank is this rank's place in it"
+            n_weight = dist.get_world_size(self.weight_group) if self.weight_group is not None else 1
+            assert tp_ortho_group is not None or n_weight == model_cfg.tp, \
+                "a weight group larger than the tensor-parallel group needs tp_ortho_group"
         self.wp_size = model_cfg.wp[0] * model_cfg.wp[1] * model_cfg.sp
         self.wp_rank = dist.get_rank(wp_group) if (self.wp_size > 1) else 0
         self.sp_rank = self.wp_rank % model_cfg.sp
@@ -62,7 +74,11 @@ class Trainer:
         # weight-group collectives: this library's peer-memory kernels (default on GPUs with > 1 rank) or NCCL
         n_replicas = self.wp_size * dp_size
         self.fused_dp = (n_replicas > 1 and self.device.type == "cuda") if fused_dp is None else fused_dp
-        if self.fused_dp:
+        if self.tp_group is not None:
+            from .tp_optim import TPOptimizer
+            self.opt = TPOptimizer(self.model, optim_cfg, self.device, self.weight_group, self.tp_group, tp_ortho_group,
+                                   fused=self.fused_dp, use_multicast=use_multicast)
+        elif self.fused_dp:
             from .fused_dp import FusedShardedOptimizer
             self.opt = FusedShardedOptimizer(self.model, optim_cfg, self.weight_group, self.device, use_multicast)
         else:
@@ -92,12 +108,19 @@ class Trainer:
         self.timers = DeviceTimers(enabled=False)
         self.last_norm = 0.0
         self._sp_exchange = None
+        self._tp_exchange = None
 
     # ------------------------------------------------------------------------------------------------ helpers
     def context(self, batch: int) -> StreamContext:
         if batch not in self._ctx:
             peer_fn = self.halo.peer_fn if self.halo is not None else None
-            ctx = StreamContext(self.cfg, batch, self.wp_rank, peer_fn, wp_group=self.wp_group, sp_group=self.sp_group)
+            ctx = StreamContext(self.cfg, batch, self.wp_rank, peer_fn, wp_group=self.wp_group, sp_group=self.sp_group,
+                                tp_group=self.tp_group)
+            if self.tp_group is not None and self.device.type == "cuda":
+                if self._tp_exchange is None:
+                    from ..parallel.tensor import TPExchange
+                    self._tp_exchange = TPExchange(self.tp_group, self.device)
+                ctx.tp_exchange = self._tp_exchange
             if self.cfg.sp > 1 and self.device.type == "cuda":
                 if self._sp_exchange is None:
                     from ..models.fused import SPExchange
@@ -239,7 +262,7 @@ class Trainer:
         scale = 1.0 / (self.dp_size * gas)
         if not self.dcfg.grad_scale_parity:
             scale /= self.wp_size
-        if self.fused_dp:
+        if self.fused_dp or self.tp_group is not None:
             self._nsq = self.opt.reduce_and_step(gas * self.dp_size, scale)
             return
         if self.wp_size > 1 or self.dp_size > 1:

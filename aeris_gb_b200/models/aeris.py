@@ -49,6 +49,10 @@ class AerisConfig:
     data_dtype: torch.dtype = torch.float32
     wp: tuple[int, int] = (1, 1)
     sp: int = 1                     # Ulysses sequence-parallel degree
+    # tensor-parallel MLP: w1 / w2 of every block split over ``tp`` ranks that hold different token rows of the same
+    # sample (the SP group when sp > 1, else the WP group); ``tp_rank`` selects this rank's shard at construction
+    tp: int = 1
+    tp_rank: int = 0
     chunk_windows: int = 64
     shift_layers: str = "odd"       # which layers use the half-window shift: "odd" | "none"
     oracle_checkpoint: bool = False  # PyTorch (oracle) path only: recompute every block in backward
@@ -96,8 +100,11 @@ class AerisConfig:
 class StreamContext:
     """Per-forward information the stage modules need about the token stream."""
 
-    def __init__(self, cfg: AerisConfig, batch: int, rank: int = 0, peer_fn=None, wp_group=None, sp_group=None):
+    def __init__(self, cfg: AerisConfig, batch: int, rank: int = 0, peer_fn=None, wp_group=None, sp_group=None,
+                 tp_group=None):
         self.cfg = cfg
+        self.tp_group = tp_group      # tensor-parallel MLP group, None when TP = 1
+        self.tp_exchange = None       # CUDA path: parallel.tensor.TPExchange of that group
         self.wp_group = wp_group      # torch.distributed group of the WP peers (CPU re-partition, result gathers)
         self.sp_group = sp_group      # Ulysses sequence-parallel group, None when SP = 1
         self.sp_exchange = None       # CUDA path: fused.SPExchange of that group
@@ -203,12 +210,23 @@ class AttentionParams(nn.Module):
 
 
 class FeedForwardParams(nn.Module):
-    def __init__(self, dim, hidden, own_norm: bool = False):
+    """``tp > 1``: this rank's shard of the SwiGLU weights (``w1``: its gate rows, then its up rows; ``w2``: its input
+    columns). The full-size weights are drawn first and then cut, so that a tensor-parallel model built from the same
+    seed holds exactly the slices of the unsharded model. The parameters carry ``tp_shard`` = "w1" / "w2"."""
+
+    def __init__(self, dim, hidden, own_norm: bool = False, tp: int = 1, tp_rank: int = 0):
         super().__init__()
         if own_norm:                       # plain mode: the MLP normalises its own input (parallel_swin.py:88-96)
             self.norm = nn.RMSNorm(dim)
         self.w1 = nn.Linear(dim, 2 * hidden, bias=False)
         self.w2 = nn.Linear(hidden, dim, bias=False)
+        if tp > 1:
+            from ..parallel.tensor import shard_mlp_weights
+            assert hidden % tp == 0
+            w1_r, w2_r = shard_mlp_weights(self.w1.weight.detach(), self.w2.weight.detach(), tp, tp_rank)
+            self.w1.weight, self.w1.out_features = nn.Parameter(w1_r), 2 * hidden // tp     # no further random draws
+            self.w2.weight, self.w2.in_features = nn.Parameter(w2_r), hidden // tp
+            self.w1.weight.tp_shard, self.w2.weight.tp_shard = "w1", "w2"
 
 
 class ModulationLinear(nn.Module):
@@ -301,17 +319,18 @@ class SwinLayer(nn.Module):
                     nn.RMSNorm(d),
                     AttentionParams(d, cfg.heads, cfg.head_dim, None if cfg.rit else "unused"),
                     nn.RMSNorm(d),
-                    FeedForwardParams(d, cfg.mlp_dim),
+                    FeedForwardParams(d, cfg.mlp_dim, tp=cfg.tp, tp_rank=cfg.tp_rank),
                     ModulationLinear(d, 6 * d, cfg.layerwise_t_emb),
                 ]) for _ in range(cfg.sublayers)
             ])
         elif cfg.sublayers > 1:         # plain pre-norm blocks, module names as in parallel_swin.py:446-451
             self.modulelist = nn.ModuleList([
                 nn.ModuleList([AttentionParams(d, cfg.heads, cfg.head_dim, "own"),
-                               FeedForwardParams(d, cfg.mlp_dim, own_norm=True)]) for _ in range(cfg.sublayers)])
+                               FeedForwardParams(d, cfg.mlp_dim, own_norm=True, tp=cfg.tp, tp_rank=cfg.tp_rank)])
+                for _ in range(cfg.sublayers)])
         else:
             self.attn = AttentionParams(d, cfg.heads, cfg.head_dim, "own")
-            self.ff = FeedForwardParams(d, cfg.mlp_dim, own_norm=True)
+            self.ff = FeedForwardParams(d, cfg.mlp_dim, own_norm=True, tp=cfg.tp, tp_rank=cfg.tp_rank)
 
     def blocks(self):
         """(norm1 weight, attention parameters, norm2 weight, MLP parameters, modulation module or None) per block."""
@@ -352,7 +371,9 @@ class SwinLayer(nn.Module):
                 meta = fused.BlockMeta(ctx.grid.windows_per_rank, ctx.grid.n_local, cfg.heads, cfg.head_dim,
                                        E.MODE_MOD_THEN_NORM if after_mod_norm else E.MODE_NORM_THEN_MOD,
                                        eps, cfg.chunk_windows, sp=ctx.sp_exchange if ctx.grid.sp > 1 else None,
-                                       rope=ctx.rope(x.device))
+                                       rope=ctx.rope(x.device), tp=ctx.tp_exchange if cfg.tp > 1 else None)
+                if cfg.tp > 1 and ctx.tp_exchange is None:
+                    raise RuntimeError("tensor parallelism on CUDA needs StreamContext.tp_exchange (tensor.TPExchange)")
                 rg = None
                 if j == 0 and regroup is not None:
                     rg = (ctx.table(regroup[0], regroup[1], x.device), ctx.table(regroup[1], regroup[0], x.device),
@@ -376,9 +397,13 @@ class SwinLayer(nn.Module):
                     from ..parallel.sequence import sp_window_attention
                     attn = lambda qkv, nw, nl, H, d: sp_window_attention(qkv, nw, nl, H, d, ctx.sp_group,
                                                                            inner or O.window_attention)
+                mlp = None
+                if cfg.tp > 1:
+                    from ..parallel.tensor import TPMlpCollective
+                    mlp = lambda h2, w1=ff.w1.weight, w2=ff.w2.weight: TPMlpCollective.apply(h2, w1, w2, ctx.tp_group)
                 run = lambda xx, mm: O.block_forward(xx, mm, p, n_win_per_sample=ctx.grid.windows_per_rank,
                                                      L=ctx.grid.n_local, heads=cfg.heads, head_dim=cfg.head_dim,
-                                                     after_mod_norm=after_mod_norm, eps=eps, attention=attn)
+                                                     after_mod_norm=after_mod_norm, eps=eps, attention=attn, mlp=mlp)
                 if cfg.oracle_checkpoint and torch.is_grad_enabled():
                     x = torch.utils.checkpoint.checkpoint(run, x, m, use_reentrant=False)
                 else:

@@ -31,6 +31,7 @@ class BlockMeta:
     chunk_windows: int = 64
     sp: "SPExchange | None" = None     # Ulysses sequence parallelism: L is then the LOCAL token count of a window
     rope: tuple | None = None          # (cos, sin) [L, head_dim / 2]: optional 2-D rotary embedding of q and k
+    tp: object | None = None           # parallel.tensor.TPExchange: w1 / w2 are this rank's shards of the MLP weights
 
 
 class Workspace:
@@ -177,6 +178,21 @@ def _sp_attention_bwd(meta: BlockMeta, dx1: torch.Tensor, wog: torch.Tensor, nw:
     return dqkv_loc
 
 
+def _tp_mlp_fwd(tp, x1, sc2, sh2, wn2, meta: BlockMeta, w1, w2, g2, act, y_out):
+    """Tensor-parallel MLP half of a chunk: ``y = x1 + g2 * reduce_scatter(swiglu(all_gather(h2) @ w1_r^T) @ w2_r^T)``
+    with both collectives inside the GEMM kernels (parallel/tensor.py). The modulate+norm kernel writes this rank's
+    rows of h2 straight into the all-gather buffer; the barrier inside the reduce-scatter orders a chunk's reads
+    before the next chunk's pushes."""
+    from ..parallel import tensor as TP
+    n, D = x1.shape
+    M = tp.tp * n
+    a_buf, peers = tp.buffer("ag_x", (M, D))
+    E.modnorm_fwd(x1, sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=a_buf[tp.rank * n:(tp.rank + 1) * n])
+    tp.barrier()
+    TP.gemm_allgather_a(tp, a_buf, peers, w1, out=act[:M], epi=G.EPI_SWIGLU)
+    TP.gemm_reduce_scatter(tp, act[:M], w2, resid=x1, gate=g2, out=y_out)
+
+
 def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv, wo, wn2, w1, w2,
                   out: torch.Tensor | None = None, gather=None) -> torch.Tensor:
     """x: [B * n_win * L, D] bf16 window-major; mod: [B, 6D] fp32 (shift1, scale1, gate1, shift2, scale2, gate2).
@@ -197,7 +213,8 @@ def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv
     qkv = ws.get("qkv", (cmax, 3 * HD), bf, dev)
     o = ws.get("o", (cmax, HD), bf, dev)
     x1 = ws.get("x1", (cmax, D), bf, dev)
-    act = ws.get("act", (cmax, F), bf, dev)
+    tpn = meta.tp.tp if meta.tp is not None else 1       # gathered rows x local features: the same element count
+    act = ws.get("act", (cmax * tpn, F), bf, dev)
     lse = ws.get("lse", (cmax * meta.heads,), torch.float32, dev)
     mod = mod.contiguous()
     for b in range(B):
@@ -223,6 +240,9 @@ def block_forward(x: torch.Tensor, mod: torch.Tensor, meta: BlockMeta, wn1, wqkv
             else:
                 oc = _sp_attention_fwd(meta, h[:n], wqkv, nw, keep_local=False)[0]
             G.gemm(oc, wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
+            if meta.tp is not None:
+                _tp_mlp_fwd(meta.tp, x1[:n], sc2, sh2, wn2, meta, w1, w2, g2, act, y[r0:r0 + n])
+                continue
             E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=h[:n])
             G.gemm(h[:n], w1, out=act[:n], epi=G.EPI_SWIGLU)
             G.gemm(act[:n], w2, out=y[r0:r0 + n], epi=G.EPI_GATE_RESID, resid=x1[:n], gate=g2)
@@ -244,10 +264,12 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
     qkv = ws.get("qkv", (cmax, 3 * HD), bf, dev)
     o = ws.get("o", (cmax, HD), bf, dev)
     x1 = ws.get("x1", (cmax, D), bf, dev)
-    act = ws.get("act", (cmax, F), bf, dev)
+    tp = meta.tp
+    tpn = tp.tp if tp is not None else 1
+    act = ws.get("act", (cmax * tpn, F), bf, dev)
     lse = ws.get("lse", (cmax * meta.heads,), f32, dev)
     h2 = ws.get("h2", (cmax, D), bf, dev)
-    u = ws.get("u", (cmax, 2 * F), bf, dev)
+    u = ws.get("u", (cmax * tpn, 2 * F), bf, dev)
     dh = ws.get("dh", (cmax, D), bf, dev)
     dx1 = ws.get("dx1", (cmax, D), bf, dev)
     d_o = ws.get("d_o", (cmax, HD), bf, dev)
@@ -283,14 +305,31 @@ def block_backward(x: torch.Tensor, mod: torch.Tensor, dy: torch.Tensor, meta: B
             else:
                 oc, sp_state = _sp_attention_fwd(meta, h1[:n], wqkv, nw, keep_local=True)
             G.gemm(oc, wo, out=x1[:n], epi=G.EPI_GATE_RESID, resid=xc, gate=g1)
-            E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=h2[:n])
-            G.gemm(h2[:n], w1, out=act[:n], epi=G.EPI_SWIGLU_BOTH, aux=u[:n])         # act and the raw [gate | up]
-            # ---- MLP half: y = x1 + g2 * (act @ w2^T)
-            G.gemm(dyc, act[:n], a_t=True, b_t=True, out=G2, epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
-            # dact = (dy * g2) @ w2 never reaches memory: the epilogue turns it into du, overwriting u
-            G.gemm(dyc, w2g, b_t=True, out=u[:n], epi=G.EPI_SWIGLU_BWD, resid=u[:n])
-            G.gemm(u[:n], w1, b_t=True, out=dh[:n])                                    # dh2 = du @ w1
-            G.gemm(u[:n], h2[:n], a_t=True, b_t=True, out=grads["w1"], epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+            if tp is not None:
+                # tensor-parallel MLP half: h2 and dy are gathered over the group inside the two GEMMs that consume
+                # them, the partial dh2 is reduced and scattered by the epilogue of the GEMM that produces it
+                from ..parallel import tensor as TP
+                Mg = tpn * n
+                sl = slice(tp.rank * n, (tp.rank + 1) * n)
+                x_buf, x_peers = tp.buffer("ag_x", (Mg, D))
+                g_buf, g_peers = tp.buffer("ag_dy", (Mg, D))
+                E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=x_buf[sl])
+                g_buf[sl].copy_(dyc)
+                tp.barrier()
+                TP.gemm_allgather_a(tp, x_buf, x_peers, w1, out=act[:Mg], epi=G.EPI_SWIGLU_BOTH, aux=u[:Mg])
+                TP.gemm_allgather_a(tp, g_buf, g_peers, w2g, b_t=True, out=u[:Mg], epi=G.EPI_SWIGLU_BWD, resid=u[:Mg])
+                G.gemm(g_buf, act[:Mg], a_t=True, b_t=True, out=G2, epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+                G.gemm(u[:Mg], x_buf, a_t=True, b_t=True, out=grads["w1"], epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+                TP.gemm_reduce_scatter(tp, u[:Mg], w1, b_t=True, name="rs_dx", out=dh[:n])
+            else:
+                E.modnorm_fwd(x1[:n], sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, out=h2[:n])
+                G.gemm(h2[:n], w1, out=act[:n], epi=G.EPI_SWIGLU_BOTH, aux=u[:n])     # act and the raw [gate | up]
+                # ---- MLP half: y = x1 + g2 * (act @ w2^T)
+                G.gemm(dyc, act[:n], a_t=True, b_t=True, out=G2, epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
+                # dact = (dy * g2) @ w2 never reaches memory: the epilogue turns it into du, overwriting u
+                G.gemm(dyc, w2g, b_t=True, out=u[:n], epi=G.EPI_SWIGLU_BWD, resid=u[:n])
+                G.gemm(u[:n], w1, b_t=True, out=dh[:n])                                # dh2 = du @ w1
+                G.gemm(u[:n], h2[:n], a_t=True, b_t=True, out=grads["w1"], epi=G.EPI_ACC_F32, k_splits=ksplit_tok)
             E.modnorm_bwd(x1[:n], dh[:n], dyc, sc2, sh2, wn2, mode=meta.mode, eps=meta.eps, dx=dx1[:n],
                           dscale=dsc2, dshift=dsh2, dw=grads["n2"])
             # ---- attention half: x1 = x + g1 * (o @ wo^T)

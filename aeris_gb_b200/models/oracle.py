@@ -113,12 +113,13 @@ def swiglu(u: torch.Tensor) -> torch.Tensor:
 
 
 def block_forward(x: torch.Tensor, mod: torch.Tensor, p: dict, *, n_win_per_sample: int, L: int, heads: int,
-                  head_dim: int, after_mod_norm: bool, eps: float, attention=None) -> torch.Tensor:
+                  head_dim: int, after_mod_norm: bool, eps: float, attention=None, mlp=None) -> torch.Tensor:
     """One transformer block on a window-major token stream (parallel_swin.py:454-472).
 
     x: [B * n_win_per_sample * L, D]; mod: [B, 6 D] = (shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp,
     gate_mlp); p: weights ``n1, to_qkv, wo, n2, w1, w2``. ``L`` is the number of tokens of a window held locally
-    (the whole window unless sequence parallel); ``attention`` overrides the attention call (Ulysses SP).
+    (the whole window unless sequence parallel); ``attention`` overrides the attention call (Ulysses SP), ``mlp`` the
+    feed-forward call on the normalised rows (tensor-parallel MLP).
     """
     B = mod.shape[0]
     T, D = x.shape
@@ -136,6 +137,6 @@ def block_forward(x: torch.Tensor, mod: torch.Tensor, p: dict, *, n_win_per_samp
     a = F.linear(o, p["wo"]).view(B, T // B, D)
     xs = xs + g1.unsqueeze(1) * a
     h2 = pre(xs, sh2, sc2, p["n2"]).reshape(T, D)
-    m = F.linear(swiglu(F.linear(h2, p["w1"])), p["w2"]).view(B, T // B, D)
+    m = (mlp(h2) if mlp is not None else F.linear(swiglu(F.linear(h2, p["w1"])), p["w2"])).view(B, T // B, D)
     xs = xs + g2.unsqueeze(1) * m
     return xs.reshape(T, D)

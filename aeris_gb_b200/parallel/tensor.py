@@ -176,6 +176,117 @@ def tp_mlp_reference(h: torch.Tensor, w1_r: torch.Tensor, w2_r: torch.Tensor, gr
     return y[rank * n_loc:(rank + 1) * n_loc].to(h.dtype)
 
 
+class TPMlpCollective(torch.autograd.Function):
+    """The tensor-parallel SwiGLU MLP with ``torch.distributed`` collectives and a hand-written backward pass (any
+    backend; the CPU / gloo path of the model and the statement of what the fused kernels compute):
+    ``y = reduce_scatter_rows(swiglu(all_gather_rows(h) @ w1_r^T) @ w2_r^T)``."""
+
+    @staticmethod
+    def _gather(t, group):
+        parts = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(parts, t.contiguous(), group=group)
+        return torch.cat(parts)
+
+    @staticmethod
+    def _scatter_sum(t, group):
+        t = t.float().contiguous()
+        dist.all_reduce(t, group=group)
+        n = t.shape[0] // dist.get_world_size(group)
+        r = dist.get_rank(group)
+        return t[r * n:(r + 1) * n]
+
+    @staticmethod
+    def forward(ctx, h, w1, w2, group):
+        x = TPMlpCollective._gather(h, group)
+        u = x @ w1.t()
+        f = u.shape[1] // 2
+        act = torch.nn.functional.silu(u[:, :f]) * u[:, f:]
+        ctx.group = group
+        ctx.save_for_backward(h, w1, w2)
+        return TPMlpCollective._scatter_sum(act @ w2.t(), group).to(h.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, w1, w2 = ctx.saved_tensors
+        x = TPMlpCollective._gather(h, ctx.group)
+        g = TPMlpCollective._gather(dy, ctx.group)
+        u = x @ w1.t()
+        f = u.shape[1] // 2
+        gate, up = u[:, :f].float(), u[:, f:].float()
+        sig = torch.sigmoid(gate)
+        act = (gate * sig * up).to(h.dtype)
+        dact = (g @ w2).float()
+        du = torch.cat([dact * up * sig * (1 + gate * (1 - sig)), dact * gate * sig], dim=1).to(h.dtype)
+        dw2 = g.t() @ act
+        dw1 = du.t() @ x
+        dh = TPMlpCollective._scatter_sum(du @ w1, ctx.group).to(h.dtype)
+        return dh, dw1, dw2, None
+
+
+def tp_kind(name: str, p=None) -> str | None:
+    """"w1" / "w2" for the tensor-parallel-sharded weights of a model built with ``tp > 1``, else None."""
+    k = getattr(p, "tp_shard", None)
+    if k is not None:
+        return k
+    if "latent_embed" in name:           # the noise-level embedding's own w1 / w2 are replicated
+        return None
+    if name.endswith(".w1.weight"):
+        return "w1"
+    if name.endswith(".w2.weight"):
+        return "w2"
+    return None
+
+
+def shard_tensor(kind: str, full: torch.Tensor, tp: int, rank: int) -> torch.Tensor:
+    """Rank ``rank``'s shard of a full ``w1``-shaped [2F, D] or ``w2``-shaped [D, F] tensor (weights, masters, Adam
+    moments and EMA all share the parameter's shape)."""
+    if kind == "w1":
+        F = full.shape[0] // 2
+        f = F // tp
+        return torch.cat([full[rank * f:(rank + 1) * f], full[F + rank * f:F + (rank + 1) * f]], dim=0).contiguous()
+    f = full.shape[1] // tp
+    return full[:, rank * f:(rank + 1) * f].contiguous()
+
+
+def unshard_tensors(kind: str, shards: list[torch.Tensor]) -> torch.Tensor:
+    """Inverse of :func:`shard_tensor` over the shards of all ranks, in rank order."""
+    if kind == "w1":
+        f = shards[0].shape[0] // 2
+        return torch.cat([s[:f] for s in shards] + [s[f:] for s in shards], dim=0)
+    return torch.cat(shards, dim=1)
+
+
+def gather_full(kind: str, shard: torch.Tensor, group) -> torch.Tensor:
+    """Collective over the tensor-parallel group: the full tensor on every rank (on the shard's device)."""
+    parts = [torch.empty_like(shard) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, shard.contiguous(), group=group)
+    return unshard_tensors(kind, parts)
+
+
+def full_state_dict(named: dict[str, torch.Tensor], group) -> dict[str, torch.Tensor]:
+    """A dict of per-parameter tensors with the tensor-parallel shards replaced by the gathered full tensors
+    (collective: every rank of ``group`` calls it with the same keys in the same order)."""
+    out = {}
+    for k, v in named.items():
+        kind = tp_kind(k)
+        if kind is None:
+            out[k] = v
+        else:
+            dev = v.device
+            if dist.get_backend(group) == "nccl" and not v.is_cuda:
+                v = v.cuda()
+            out[k] = gather_full(kind, v, group).to(dev)
+    return out
+
+
+def fit_to_shard(name: str, t: torch.Tensor, like: torch.Tensor, tp: int, rank: int) -> torch.Tensor:
+    """``t`` as stored in a checkpoint (full size) cut down to this rank's shard when ``like`` is a shard."""
+    kind = tp_kind(name)
+    if kind is None or tuple(t.shape) == tuple(like.shape) or tp <= 1:
+        return t
+    return shard_tensor(kind, t, tp, rank)
+
+
 class TPFeedForward(torch.nn.Module):
     """SwiGLU feed-forward whose weights are sharded over a tensor-parallel group (see module docstring)."""
 

@@ -79,6 +79,16 @@ class ProcessGrid:
         c = self.coords(rank)
         return self.grid[:, :, :, c.pp, :].flatten().tolist()
 
+    def tp_ranks(self, rank: int) -> list[int]:
+        """The ranks that split the MLP weights of a tensor-parallel model between them: ranks that hold different
+        token rows of the same sample, i.e. the SP group when SP > 1, else the WP x SP ranks of the sample."""
+        return self.sp_ranks(rank) if self.SP > 1 else self.replica_ranks(rank)
+
+    def tp_ortho_ranks(self, rank: int) -> list[int]:
+        """The ranks of the weight group that hold the same tensor-parallel shard as ``rank``."""
+        pos = self.tp_ranks(rank).index(rank)
+        return [q for q in self.weight_ranks(rank) if self.tp_ranks(q).index(q) == pos]
+
     def stage_heads(self) -> list[int]:
         """One rank per pipeline stage (dp = wp = sp = 0): the ranks that write checkpoints (:1229)."""
         return self.grid[0, 0, 0, :, 0].flatten().tolist()
@@ -94,7 +104,8 @@ class ProcessGrid:
 
     def all_group_lists(self, kind: str) -> list[list[int]]:
         fn = {"sp": self.sp_ranks, "pp": self.pp_ranks, "wp": self.wp_ranks, "dp": self.dp_ranks,
-              "weight": self.weight_ranks, "replica": self.replica_ranks}[kind]
+              "weight": self.weight_ranks, "replica": self.replica_ranks, "tp": self.tp_ranks,
+              "tp_ortho": self.tp_ortho_ranks}[kind]
         seen, out = set(), []
         for r in range(self.used):
             g = tuple(fn(r))

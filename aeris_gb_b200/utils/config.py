@@ -221,7 +221,8 @@ def model_config(cfg: Config):
         max_period=float(m.get("sinusoidal_emb_max_period", 10000)), wp=(m.get("WP_Y", 1), m.get("WP_X", 1)),
         chunk_windows=int(m.get("chunk_windows", 64)), norm_eps=m.get("norm_eps"),
         shift_layers=m.get("shift_mode", "odd"), diffusion=bool(m.get("diffusion", True)),
-        rit=bool(m.get("rit", False)), emb_norm=bool(m.get("emb_norm", False)) and bool(m.get("rit", False)))
+        rit=bool(m.get("rit", False)), emb_norm=bool(m.get("emb_norm", False)) and bool(m.get("rit", False)),
+        tp=int(m.get("TP", 1)))
 
 
 def optim_config(cfg: Config):

@@ -9,7 +9,8 @@ weights, full optimizer step inside the timed region. Prints ONE JSON line on ra
 
 Other arms: ``--impl reference`` (the unmodified reference modules on stock PyTorch kernels, data parallel), ``--impl torch-eager`` (the same model
 through stock PyTorch ops, an informational same-math baseline), ``--mode infer`` (seconds per autoregressive forecast
-step, one ensemble member per GPU), ``--sp S`` (WP = N / S with Ulysses sequence parallelism S).
+step, one ensemble member per GPU), ``--sp S`` (WP = N / S with Ulysses sequence parallelism S), ``--tp T`` (MLP weights
+split over the SP group, or over all ranks without SP).
 """
 from __future__ import annotations
 
@@ -260,6 +261,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the number of Swin layers (development only)")
     ap.add_argument("--chunk-windows", type=int, default=0)
     ap.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel degree (WP = gpus / sp)")
+    ap.add_argument("--tp", type=int, default=1,
+                    help="tensor-parallel MLP degree: the SP group when --sp > 1, else all WP ranks (must equal its size)")
     ap.add_argument("--mode", default="train", choices=["train", "infer"],
                     help="infer: one autoregressive forecast step per member, one member per GPU (s/step)")
     ap.add_argument("--sampler-steps", type=int, default=10)
@@ -311,7 +314,18 @@ def main():
             g_ = dist.new_group(list(range(r0, r0 + args.sp)))
             if r0 <= rank < r0 + args.sp:
                 sp_group = g_
-    trainer = Trainer(cfg, OptimConfig(), DiffusionConfig(), dev, wp_group=group, sp_group=sp_group,
+    tp_kw = {}
+    if args.tp > 1:
+        # the tensor-parallel group: the SP group, or every rank when there is no SP; the ranks holding the same shard
+        tp_size = args.sp if args.sp > 1 else world
+        assert args.tp == tp_size, f"--tp must be {tp_size} in this layout"
+        cfg.tp, cfg.tp_rank = args.tp, rank % args.tp
+        if tp_size < world:
+            for pos in range(tp_size):
+                g_ = dist.new_group(list(range(pos, world, tp_size)))
+                if rank % tp_size == pos:
+                    tp_kw["tp_ortho_group"] = g_
+    trainer = Trainer(cfg, OptimConfig(), DiffusionConfig(), dev, wp_group=group, sp_group=sp_group, **tp_kw,
                       **(dict(fused_io=False, fused_dp=False) if eager else {}))
     g = cfg.grid()
     hb, wb = cfg.img[0] // cfg.wp[0], cfg.img[1] // cfg.wp[1]
@@ -376,7 +390,8 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "tflops_per_gpu": flops / (ms_dev / 1e3) / 1e12 / world,
             "config": {"model": model_label({**FLAGSHIP[args.scale], "n_layers": cfg.n_layers}),
-                       "params": cfg.param_count(), "global_batch": B, "seq_len": cfg.img[0] * cfg.img[1], "parallelism": f"wp{world // args.sp}" + (f"xsp{args.sp}" if args.sp > 1 else ""),
+                       "params": cfg.param_count(), "global_batch": B, "seq_len": cfg.img[0] * cfg.img[1], "parallelism": f"wp{world // args.sp}" + (f"xsp{args.sp}" if args.sp > 1 else "")
+                       + (f"xtp{args.tp}(mlp)" if args.tp > 1 else ""),
                        "scale": args.scale, "activation_checkpointing": "per block",
                        "l2": "inputs (597 MB/step/GPU) and activations are far larger than L2"},
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "parity": parity,

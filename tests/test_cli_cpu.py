@@ -97,3 +97,20 @@ def test_reference_benchmark_experiment_trains_at_toy_size():
                 "optimizer.lr=0.01", "trainer.lr_rampup_kimg=0"], nproc=4, port=29763)
     losses = [float(l.split("loss ")[1].split()[0]) for l in out.splitlines() if " loss " in l]
     assert len(losses) == 3 and all(l == l for l in losses) and losses[-1] < losses[0]
+
+
+def test_train_cli_with_tensor_parallel_mlp(tmp_path):
+    """``model.TP``: the MLP weights split over the two window-parallel ranks; the run trains, checkpoints (full
+    tensors on disk) and a second run resumes from the checkpoint."""
+    import torch
+    args = ["aeris_gb_b200.cli.train", "experiment=tiny_cpu", "model.WP_X=2", "model.TP=2", "optimizer.lr=0.003",
+            "trainer.lr_rampup_kimg=0", f"model.checkpoint_dir={tmp_path}", "trainer.checkpoint_every=2"]
+    out = _run(args + ["trainer.benchmark_steps=4"], nproc=2, port=29771)
+    losses = [float(l.split("loss ")[1].split()[0]) for l in out.splitlines() if " loss " in l]
+    assert len(losses) == 4 and losses[-1] < losses[0]
+    ck = torch.load(tmp_path / "checkpoint_PP1.pth", map_location="cpu", weights_only=True)
+    w1 = [v for k, v in ck["model_state_dict"].items() if k.endswith("w1.weight")][0]
+    assert tuple(w1.shape) == (512, 128)                      # 2 x mlp_dim rows: the gathered, unsharded weight
+    out = _run(args + ["trainer.benchmark_steps=6", "model.load=true"], nproc=2, port=29772)
+    assert "loaded a checkpoint" in out
+    assert len([l for l in out.splitlines() if " loss " in l]) == 2
