@@ -339,6 +339,168 @@ modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+// The same backward for rows of up to 1536 columns (at most six warps per row), cut down to what the instruction
+// issue rate allows: the one-row-at-a-time kernel above executed about 42 warp instructions per element and kept the
+// schedulers 53 % busy with three resident warps each, i.e. it was bound by instruction issue, not by memory.
+//   * every per-element operation works on a pair of columns (`*.f32x2`, half the issue slots);
+//   * two rows share one block-wide reduction, whose cross-warp part is one shared-memory load and seven shuffles per
+//     thread (lane k * 8 + w holds value k of warp w) instead of 24 loads and adds;
+//   * 1 + scale is formed once per thread.
+__global__ void __launch_bounds__(192, 2)
+modnorm_bwd_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dh,
+                        const __nv_bfloat16* __restrict__ dres, const float* __restrict__ scale,
+                        const float* __restrict__ shift, const __nv_bfloat16* __restrict__ w,
+                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dscale, float* __restrict__ dshift,
+                        float* __restrict__ dw, int rows, int D, int mode, float eps, const float* __restrict__ wf) {
+  constexpr int RPI = 2;
+  __shared__ float red[2][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 64; i += blockDim.x) (&red[0][0])[i] = 0.f;   // slots of absent warps stay zero
+  const int c0 = threadIdx.x * 8;
+  const bool active = c0 < D;
+  uint64_t sc1[4], sh[4], wv[4], a_sc[4], a_sh[4], a_w[4];
+  {
+    float t_sc[8], t_sh[8], t_w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { t_sc[i] = 0.f; t_sh[i] = 0.f; t_w[i] = 0.f; }
+    if (active) {
+      if (scale) loadf8(scale + c0, t_sc);
+      if (shift) loadf8(shift + c0, t_sh);
+      if (wf) loadf8(wf + c0, t_w); else load8(w + c0, t_w);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sc1[i] = f2_pack(1.f + t_sc[2 * i], 1.f + t_sc[2 * i + 1]);
+      sh[i] = f2_pack(t_sh[2 * i], t_sh[2 * i + 1]);
+      wv[i] = f2_pack(t_w[2 * i], t_w[2 * i + 1]);
+      a_sc[i] = a_sh[i] = a_w[i] = 0ull;
+    }
+  }
+  __syncthreads();
+  const int r1 = rows;
+  const int gstep = gridDim.x;
+  const int stride = gstep * RPI;
+  const float inv_d = 1.f / D;
+  int parity = 0;
+  uint4 nx[RPI], ng[RPI], nr[RPI];
+#pragma unroll
+  for (int k = 0; k < RPI; ++k) nx[k] = ng[k] = nr[k] = make_uint4(0u, 0u, 0u, 0u);
+  auto fetch = [&](int base) {
+#pragma unroll
+    for (int k = 0; k < RPI; ++k) {
+      const int r = base + k * gstep;
+      if (active && r < r1) {
+        const size_t off = static_cast<size_t>(r) * D + c0;
+        nx[k] = *reinterpret_cast<const uint4*>(x + off);
+        ng[k] = *reinterpret_cast<const uint4*>(dh + off);
+        if (dres) nr[k] = *reinterpret_cast<const uint4*>(dres + off);
+      }
+    }
+  };
+  fetch(blockIdx.x);
+  for (int base = blockIdx.x; base < r1; base += stride, parity ^= 1) {
+    uint64_t v[RPI][4], g[RPI][4];
+    uint4 dr[RPI];
+#pragma unroll
+    for (int k = 0; k < RPI; ++k) {
+      const uint32_t xw[4] = {nx[k].x, nx[k].y, nx[k].z, nx[k].w}, gw[4] = {ng[k].x, ng[k].y, ng[k].z, ng[k].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[k][i] = f2_from_bf16x2(xw[i]);
+        g[k][i] = f2_from_bf16x2(gw[i]);
+      }
+      dr[k] = nr[k];
+    }
+    if (base + stride < r1) fetch(base + stride);
+    // ---- the two row sums of each row: mode 0  sum y^2, sum y (g w);  mode 1  sum x^2, sum x (g (1 + sc) w)
+    float s[2 * RPI];
+#pragma unroll
+    for (int k = 0; k < RPI; ++k) {
+      uint64_t p0 = 0ull, p1 = 0ull;
+      if (mode == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint64_t y = f2_fma(v[k][i], sc1[i], sh[i]);
+          p0 = f2_fma(y, y, p0);
+          p1 = f2_fma(y, f2_mul(g[k][i], wv[i]), p1);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          p0 = f2_fma(v[k][i], v[k][i], p0);
+          p1 = f2_fma(v[k][i], f2_mul(f2_mul(g[k][i], sc1[i]), wv[i]), p1);
+        }
+      }
+      float a0, a1, b0, b1;
+      f2_unpack(p0, a0, a1);
+      f2_unpack(p1, b0, b1);
+      const bool live = active && base + k * gstep < r1;
+      s[2 * k] = live ? a0 + a1 : 0.f;
+      s[2 * k + 1] = live ? b0 + b1 : 0.f;
+    }
+    // ---- block-wide sums
+#pragma unroll
+    for (int j = 0; j < 2 * RPI; ++j) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int j = 0; j < 2 * RPI; ++j) red[parity][j * 8 + warp] = s[j];
+    }
+    __syncthreads();
+    float t = red[parity][lane];
+    t += __shfl_xor_sync(0xffffffffu, t, 4);
+    t += __shfl_xor_sync(0xffffffffu, t, 2);
+    t += __shfl_xor_sync(0xffffffffu, t, 1);
+#pragma unroll
+    for (int j = 0; j < 2 * RPI; ++j) s[j] = __shfl_sync(0xffffffffu, t, j * 8);
+    // ---- gradients
+#pragma unroll
+    for (int k = 0; k < RPI; ++k) {
+      const int r = base + k * gstep;
+      if (!active || r >= r1) continue;
+      const float rinv = rsqrtf(s[2 * k] * inv_d + eps);
+      const float ncoef = -rinv * rinv * rinv * (s[2 * k + 1] * inv_d);
+      const uint64_t rinv2 = f2_pack(rinv, rinv), ncoef2 = f2_pack(ncoef, ncoef);
+      const uint32_t dw4[4] = {dr[k].x, dr[k].y, dr[k].z, dr[k].w};
+      uint32_t ow[4];
+      if (mode == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint64_t y = f2_fma(v[k][i], sc1[i], sh[i]);
+          const uint64_t dy = f2_fma(ncoef2, y, f2_mul(rinv2, f2_mul(g[k][i], wv[i])));
+          a_w[i] = f2_fma(f2_mul(g[k][i], y), rinv2, a_w[i]);
+          a_sc[i] = f2_fma(dy, v[k][i], a_sc[i]);
+          a_sh[i] = f2_add(a_sh[i], dy);
+          ow[i] = f2_to_bf16x2(f2_fma(dy, sc1[i], f2_from_bf16x2(dw4[i])));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint64_t n = f2_mul(v[k][i], rinv2);
+          const uint64_t dhn = f2_mul(g[k][i], sc1[i]);
+          a_sc[i] = f2_fma(f2_mul(g[k][i], n), wv[i], a_sc[i]);
+          a_sh[i] = f2_add(a_sh[i], g[k][i]);
+          a_w[i] = f2_fma(dhn, n, a_w[i]);
+          const uint64_t t2 = f2_fma(rinv2, f2_mul(dhn, wv[i]), f2_from_bf16x2(dw4[i]));
+          ow[i] = f2_to_bf16x2(f2_fma(ncoef2, v[k][i], t2));
+        }
+      }
+      *reinterpret_cast<uint4*>(dx + static_cast<size_t>(r) * D + c0) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  }
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float lo, hi;
+      if (dscale) { f2_unpack(a_sc[i], lo, hi); atomicAdd(dscale + c0 + 2 * i, lo); atomicAdd(dscale + c0 + 2 * i + 1, hi); }
+      if (dshift) { f2_unpack(a_sh[i], lo, hi); atomicAdd(dshift + c0 + 2 * i, lo); atomicAdd(dshift + c0 + 2 * i + 1, hi); }
+      if (dw) { f2_unpack(a_w[i], lo, hi); atomicAdd(dw + c0 + 2 * i, lo); atomicAdd(dw + c0 + 2 * i + 1, hi); }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ row gather
 __global__ void gather_rows_kernel(const uint32_t* __restrict__ gidx, PeerPtrs peers,
                                    __nv_bfloat16* __restrict__ out, long long rows, int D) {
@@ -615,8 +777,14 @@ extern "C" int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres
   if (rpc < 16) rpc = rows < 16 ? rows : 16;  // amortise the atomic flush of the column sums
   const int grid = (rows + rpc - 1) / rpc;    // every CTA takes about rpc rows, interleaved with the others
   const int nt = row_threads(D);
-  auto kern = (nt <= 192) ? modnorm_bwd_kernel<192, 2, 2> : (nt <= 640) ? modnorm_bwd_kernel<640, 1, 1>
-                                                                         : modnorm_bwd_kernel<1024, 1, 1>;
+  if (nt <= 192) {
+    modnorm_bwd_pair_kernel<<<grid, nt, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(dh),
+        reinterpret_cast<const __nv_bfloat16*>(dres), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
+        reinterpret_cast<__nv_bfloat16*>(dx), dscale, dshift, dw, rows, D, mode, eps, w_f32);
+    return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  }
+  auto kern = (nt <= 640) ? modnorm_bwd_kernel<640, 1, 1> : modnorm_bwd_kernel<1024, 1, 1>;
   kern<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(dh),
       reinterpret_cast<const __nv_bfloat16*>(dres), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),

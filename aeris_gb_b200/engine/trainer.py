@@ -106,6 +106,8 @@ class Trainer:
         # device timers / NVTX ranges around the phases of a step (resolved lazily; enable with trainer.timers.enabled)
         from ..utils.timers import DeviceTimers
         self.timers = DeviceTimers(enabled=False)
+        if self.halo is not None:
+            self.halo.timers = self.timers
         self.last_norm = 0.0
         self._sp_exchange = None
         self._tp_exchange = None

@@ -39,6 +39,7 @@ class HaloExchange:
         self._pool_ptrs: list[list[int]] = []
         self._pool_hdl: list = []
         self._turn = 0
+        self.timers = None            # utils.timers.DeviceTimers: when enabled, the barriers are timed as "halo_barrier"
 
     def _ensure(self, numel: int, dtype: torch.dtype):
         if self._buf is not None and self._buf.numel() >= numel and self._buf.dtype == dtype:
@@ -51,6 +52,13 @@ class HaloExchange:
     def _barrier(self):
         """Stream-ordered rank barrier: epoch flags in peer memory (one small kernel, release stores to every peer and
         a bounded acquire spin on the own flags), or with AERIS_HALO_NCCL_BARRIER=1 a one-element NCCL all-reduce."""
+        if self.timers is not None and self.timers.enabled:
+            with self.timers.region("halo_barrier"):      # device time of the flag kernel = arrival skew of the ranks
+                self._barrier_now()
+        else:
+            self._barrier_now()
+
+    def _barrier_now(self):
         if self._nccl_barrier:
             dist.all_reduce(self._flag, group=self.group)
             return

@@ -263,6 +263,9 @@ def main():
     ap.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel degree (WP = gpus / sp)")
     ap.add_argument("--tp", type=int, default=1,
                     help="tensor-parallel MLP degree: the SP group when --sp > 1, else all WP ranks (must equal its size)")
+    ap.add_argument("--phases", type=int, default=0,
+                    help="after the timed steps, run this many more with device timers around the phases of a step "
+                         "(load, fwd, bwd, reduce_step, halo_barrier) and print their milliseconds per step, max over ranks")
     ap.add_argument("--mode", default="train", choices=["train", "infer"],
                     help="infer: one autoregressive forecast step per member, one member per GPU (s/step)")
     ap.add_argument("--sampler-steps", type=int, default=10)
@@ -381,6 +384,15 @@ def main():
         e2e = {"value": B / (ms_e / 1e3), "unit": "samples/s", "ms_per_step": ms_e, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": 4, "last_loss": loss}
     L.check_status()
+    phases = None
+    if args.phases > 0:
+        trainer.timers.enabled = True
+        trainer.timers.use_nvtx = False
+        sync_all()
+        for i in range(args.phases):
+            step_device(i)
+        phases = {k: v / args.phases for k, v in trainer.timers.resolve().items()}
+        trainer.timers.enabled = False
     flops = trainer.flops_per_step(B)
     if rank == 0:
         out = {
@@ -396,6 +408,7 @@ def main():
                        "l2": "inputs (597 MB/step/GPU) and activations are far larger than L2"},
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "parity": parity,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+            **({"phases_ms_per_step": phases} if phases else {}),
         }
         print(json.dumps(out))
     if world > 1:
