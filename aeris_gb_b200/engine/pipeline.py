@@ -40,6 +40,7 @@ class EngineConfig:
     gas: int = 1                          # micro-batches per optimizer step (batch 1 each, as in the reference)
     overlap_p2p: bool = False
     dist_optimizer: bool = False
+    fused_io: bool | None = None      # noising + embedding and head + loss on the CUDA kernels (default: on GPUs)
     rs_grads: bool = True
     checkpoint_dir: str | None = None
     checkpoint_every: int = 100           # iterations (:1225)
@@ -98,6 +99,8 @@ class ParallelEngine:
         self.t_fn = None               # tests: noise level as a function of the sample, independent of the DP split
         self.keep_grads = False        # tests: keep a copy of the reduced, scaled gradients of the last step
         self.loads = 0
+        self.fused_io = (self.device.type == "cuda" and model_cfg.diffusion) if ecfg.fused_io is None else ecfg.fused_io
+        self._io_tables = None
         halo = None
         if grid.WP_Y * grid.WP_X * grid.SP > 1 and self.device.type == "cuda":
             from ..parallel.symm import HaloExchange
@@ -157,6 +160,22 @@ class ParallelEngine:
         n = L // SP
         return tok.view(-1, L, tok.shape[-1])[:, self.c.sp * n:(self.c.sp + 1) * n].reshape(-1, tok.shape[-1])
 
+    def _io_plan(self):
+        """What the fused input and output ends need for the micro-batch about to be loaded. The noise is counter
+        based: seed = (engine seed, optimizer step), counter = (global sample index, pixel, channel), so the first and
+        the last pipeline stage draw the same field without talking, whatever the WP / SP / PP split."""
+        from ..models import fused_io
+        from ..ops import diffusion as DF
+        if self._io_tables is None:
+            ay, ax = fused_io.ape_tables(self.cfg, self.device)
+            w_lat = TF.latitude_weights(self.cfg.img[0], self.dcfg.w_lat_add).to(self.device).contiguous()
+            self._io_tables = (ay, ax, w_lat)
+        ay, ax, w_lat = self._io_tables
+        step, mb = divmod(self.loads, self.GAS)
+        geom = DF.make_geom(self.ctx.grid, 1, self.replica_rank, sample0=self.c.dp * self.GAS + mb)
+        return fused_io.IoPlan(geom, self.dcfg.sigma_data, (self.ecfg.seed << 32) + step, True, ay, ax, self._w_var,
+                               w_lat, self.cfg.eps(self.cfg.data_dtype))
+
     # ------------------------------------------------------------------------------------------------ instructions
     def load(self, buffer_id):
         if not (self.is_first_stage() or self.is_last_stage()):
@@ -164,6 +183,22 @@ class ParallelEngine:
         item = self.data_fn(self)                    # [1, H/wp_y, W/wp_x, C] blocks of this WP rank (+ interval, rit)
         cond_blk, tgt_blk = item[0], item[1]
         g = self.ctx.grid
+        if self.fused_io and self.cfg.diffusion and self.noise_fn is None:
+            # image blocks stay images: the kernels of the two end stages noise, embed, partition and score them
+            x_img = tgt_blk.to(self.device, non_blocking=True).float().contiguous()
+            if self.t_fn is not None:
+                t = self.t_fn(self).to(self.device)
+            else:
+                t = TF.sample_noise_level(1, self.dcfg.sigma_min, self.dcfg.sigma_max, self.dcfg.sigma_data,
+                                          generator=self.nl_rng, device=self.device, law=self.dcfg.noise_law)
+            cs = torch.stack([torch.cos(t), torch.sin(t)], dim=1).float().contiguous()
+            plan = self._io_plan()
+            self.buf["x"][buffer_id], self.buf["z"][buffer_id], self.buf["t"][buffer_id] = (x_img, cs, plan), None, t
+            if self.is_first_stage():
+                c_img = cond_blk.to(self.device, non_blocking=True).float().contiguous()
+                self.buf["inputs"][buffer_id] = (x_img, c_img, cs, plan)
+            self.loads += 1
+            return
 
         def to_tok(blk):
             B, hb, wb, C = blk.shape
@@ -202,15 +237,23 @@ class ParallelEngine:
 
     def fwd(self, buffer_id):
         x = self.buf["inputs"][buffer_id]
+        tgt = self.buf["x"][buffer_id]
+        loss_io = tgt if (self.is_last_stage() and isinstance(tgt, tuple)) else None      # fused head + loss
         if self.is_first_stage():
-            y, dt = self.module(x, None, self.buf["t"][buffer_id], self.ctx)
+            if isinstance(x, tuple):
+                y, dt = self.module(None, None, self.buf["t"][buffer_id], self.ctx, images=x, loss_io=loss_io)
+            else:
+                y, dt = self.module(x, None, self.buf["t"][buffer_id], self.ctx, loss_io=loss_io)
         else:
-            y, dt = self.module(x, self.buf["dt_in"][buffer_id], None, self.ctx)
+            y, dt = self.module(x, self.buf["dt_in"][buffer_id], None, self.ctx, loss_io=loss_io)
         self.buf["outputs"][buffer_id], self.buf["dt_out"][buffer_id] = y, dt
 
     def bwd(self, buffer_id):
         out = self.buf["outputs"][buffer_id]
-        if self.is_last_stage():
+        if self.is_last_stage() and isinstance(self.buf["x"][buffer_id], tuple):
+            self.loss_acc += out.detach().reshape(()).to(self.loss_acc.dtype)     # `out` is the loss itself
+            out.backward()
+        elif self.is_last_stage():
             x, z, t = self.buf["x"][buffer_id], self.buf["z"][buffer_id], self.buf["t"][buffer_id]
             if self.cfg.diffusion:
                 tr = t.repeat_interleave(x.shape[0])

@@ -65,13 +65,21 @@ class PipelineStage(nn.Module):
     def _regroup(self, x, src, dst, ctx: StreamContext):
         return ctx.regroup_unfused(x, src, dst)
 
-    def forward(self, x: torch.Tensor, dt: torch.Tensor | None, t: torch.Tensor | None, ctx: StreamContext):
+    def forward(self, x: torch.Tensor | None, dt: torch.Tensor | None, t: torch.Tensor | None, ctx: StreamContext,
+                images=None, loss_io=None):
         """First stage: ``x`` = model input tokens [T, C_in] and ``t`` the noise levels; other stages: ``x`` = stream
         [T, D] in this stage's entry layout and ``dt`` the noise-level embedding. Returns ``(y, dt)``; on the last
-        stage ``y`` is the prediction [T, C_out] in the plain layout."""
+        stage ``y`` is the prediction [T, C_out] in the plain layout.
+        CUDA kernels at the ends: ``images = (x_img, c_img, cs, plan)`` replaces ``x`` on the first stage (noising,
+        position encoding, window partition and projection in one pass), ``loss_io = (x_img, cs, plan)`` makes the
+        last stage return the TrigFlow loss instead of the prediction (head, loss and its gradient fused)."""
         cur = self.entry_shift()
         if self.has_input:
-            x, dt = self.input_stage(x, t, ctx)
+            if images is not None:
+                x_img, c_img, cs, plan = images
+                x, dt = self.input_stage.forward_images(x_img, c_img, cs, t, plan)
+            else:
+                x, dt = self.input_stage(x, t, ctx)
             cur = (0, 0)
         for i in self.layer_ids:
             nxt = self.cfg.layer_shift(i)
@@ -79,7 +87,10 @@ class PipelineStage(nn.Module):
             cur = nxt
         if self.has_output:
             x = self._regroup(x, cur, (0, 0), ctx)
-            x = self.output_stage(x, dt, ctx)
+            if loss_io is not None:
+                x = self.output_stage.loss_images(x, dt, *loss_io)
+            else:
+                x = self.output_stage(x, dt, ctx)
         return x, dt
 
     # ---- per-logical-stage state dicts (reference checkpoint layout) -------------------------------------------

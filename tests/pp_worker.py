@@ -1,7 +1,8 @@
 """Worker of the GPU pipeline-parallel test: the instruction-schedule engine with NCCL p2p between the stages (CUDA
 kernels in every block, peer-memory halo and Ulysses exchanges inside the stages) has to reproduce the losses and the
 updated weights of the same engine with every stage on one GPU. argv: overlap (1 = overlapped 1F1B schedule), PP,
-WP_X, SP (defaults: 0, world, 1, 1)."""
+WP_X, SP, fused (defaults: 0, world, 1, 1, 0). fused = 1: the end stages run the fused noising + embedding and head +
+loss kernels with their counter-based noise (the same field for any split); 0: PyTorch ends with injected noise."""
 import os
 import sys
 
@@ -33,11 +34,12 @@ def _block(img, eng):
     return img[:, eng.c.wp_y * hb:(eng.c.wp_y + 1) * hb, eng.c.wp_x * wb:(eng.c.wp_x + 1) * wb].contiguous()
 
 
-def build(grid, rank, dev, overlap, groups=None):
+def build(grid, rank, dev, overlap, groups=None, fused=False):
     cfg = AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=128, heads=2, head_dim=64,
                       mlp_dim=256, n_layers=4, sublayers=1, norm_eps=1e-3, chunk_windows=5, wp=(grid.WP_Y, grid.WP_X),
                       sp=grid.SP)
-    ecfg = EngineConfig(gas=4, overlap_p2p=overlap, checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5)
+    ecfg = EngineConfig(gas=4, overlap_p2p=overlap, checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5,
+                        fused_io=fused)
     eng = ParallelEngine(cfg, OptimConfig(lr=1e-2, lr_rampup_img=0, grad_clip_max_norm=1.0, weight_decay=0.0),
                          DiffusionConfig(grad_scale_parity=False, cond_channels=CC), ecfg, grid, rank, dev,
                          data_fn=lambda e: (_block(_field(1000 + _idx(e), CC), e), _block(_field(2000 + _idx(e), CH), e)),
@@ -48,7 +50,8 @@ def build(grid, rank, dev, overlap, groups=None):
             if v.dtype.is_floating_point and "inv_freq" not in k:
                 v.copy_((torch.randn(v.shape, generator=g) * 0.05).to(v.dtype))
     eng.opt = type(eng.opt)(eng.module, eng.ocfg)
-    eng.noise_fn = lambda e: _block(_field(3000 + _idx(e), CH), e)
+    if not fused:
+        eng.noise_fn = lambda e: _block(_field(3000 + _idx(e), CH), e)
     eng.t_fn = lambda e: torch.tensor([0.2 + 0.13 * (_idx(e) % 9)])
     return eng
 
@@ -59,20 +62,21 @@ def main():
     PP = int(sys.argv[2]) if len(sys.argv) > 2 else world
     WPX = int(sys.argv[3]) if len(sys.argv) > 3 else 1
     SP = int(sys.argv[4]) if len(sys.argv) > 4 else 1
+    fused = bool(int(sys.argv[5])) if len(sys.argv) > 5 else False
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     import datetime
     dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     iters = 2
     # reference: all stages on this GPU, no communication
-    ref = build(ProcessGrid(1, PP=1), 0, dev, False, groups={})
+    ref = build(ProcessGrid(1, PP=1), 0, dev, False, groups={}, fused=fused)
     ref_loss = []
     for _ in range(iters):
         ref.exec_schedule()
         ref_loss.append(float(ref.tot_loss))
     ref_sd = {st: {k: v.clone() for k, v in sd.items()} for st, sd in ref.module.logical_state_dicts().items()}
     del ref
-    eng = build(ProcessGrid(world, PP=PP, WP_X=WPX, SP=SP), rank, dev, overlap)
+    eng = build(ProcessGrid(world, PP=PP, WP_X=WPX, SP=SP), rank, dev, overlap, fused=fused)
     loss = []
     for _ in range(iters):
         eng.exec_schedule()
@@ -90,7 +94,7 @@ def main():
     ok = worst < (3e-2 if WPX * SP == 1 else 8e-2)
     if eng.is_last_stage():
         ok = ok and all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(loss, ref_loss))
-        print(f"pp{PP} wp{WPX} sp{SP} overlap={overlap}: losses {loss} vs single-GPU {ref_loss}; worst weight diff {worst:.2e}", flush=True)
+        print(f"pp{PP} wp{WPX} sp{SP} overlap={overlap} fused_io={fused}: losses {loss} vs single-GPU {ref_loss}; worst weight diff {worst:.2e}", flush=True)
     flag = torch.tensor([0.0 if ok else 1.0], device=dev)
     dist.all_reduce(flag)
     dist.barrier()

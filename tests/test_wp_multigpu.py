@@ -63,6 +63,20 @@ def test_pipeline_parallel_nccl(overlap):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
 
 
+@pytest.mark.parametrize("n,pp,wpx,sp", [(2, 2, 1, 1), (2, 1, 2, 1)])
+def test_pipeline_engine_with_fused_input_and_loss_kernels(n, pp, wpx, sp):
+    """The pipeline engine with its end stages on the fused kernels (noising + position encoding + partition +
+    projection; head + TrigFlow loss + gradient) and their counter-based noise, split over pipeline stages or window
+    ranks, against the same engine on one GPU."""
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    worker = os.path.join(os.path.dirname(__file__), "pp_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29590 + pp), worker, "1", str(pp), str(wpx),
+                        str(sp), "1"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+
+
 @pytest.mark.parametrize("n,pp,wpx,sp", [(4, 2, 2, 1), (4, 2, 1, 2), (8, 2, 2, 2)])
 def test_pipeline_with_window_and_sequence_parallel_stages(n, pp, wpx, sp):
     """PP x WP x SP on GPUs (overlapped 1F1B over NCCL p2p; halo pulls and Ulysses pushes over peer memory inside every
