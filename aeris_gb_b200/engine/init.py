@@ -21,9 +21,21 @@ def init_params(model: nn.Module, cfg, policy: dict | None = None) -> None:
     layers = max(cfg.n_layers * cfg.sublayers, 1)
     depth_scale = (1 / (2 * layers)) ** 0.5
 
-    def tn(w, std):
+    tp, tp_rank = getattr(cfg, "tp", 1), getattr(cfg, "tp_rank", 0)
+
+    def tn(w, std, kind=None):
         if std == 0:
             nn.init.zeros_(w)
+        elif kind is not None:
+            # a tensor-parallel shard: draw the full-size weight and keep this rank's part, so that the ranks of the
+            # group (which share the seed) do not all start from the same values
+            import torch
+            from ..parallel.tensor import shard_tensor
+            shape = (w.shape[0] * tp, w.shape[1]) if kind == "w1" else (w.shape[0], w.shape[1] * tp)
+            full = torch.empty(shape, dtype=torch.float32)
+            nn.init.trunc_normal_(full, std=std)
+            with torch.no_grad():
+                w.copy_(shard_tensor(kind, full, tp, tp_rank).to(w.dtype))
         else:
             nn.init.trunc_normal_(w, std=std)
 
@@ -31,6 +43,14 @@ def init_params(model: nn.Module, cfg, policy: dict | None = None) -> None:
         if not isinstance(m, (nn.Linear, nn.RMSNorm)):
             continue
         w = m.weight
+        if tp > 1:
+            from ..parallel.tensor import tp_kind
+            kind = tp_kind(name + ".weight", w)
+            if kind is not None:
+                scale = depth_scale if (kind == "w2" and p["init_scale_test14"] and not p["init_scale_test15"]) else 1.0
+                zero = kind == "w2" and p["init_scale_test15"]
+                tn(w, 0 if zero else base * scale, kind)
+                continue
         if p["init_scale_test15"] or p["init_scale_test14"]:
             t14 = p["init_scale_test14"] and not p["init_scale_test15"]
             if hasattr(m, "is_time_emb"):

@@ -56,7 +56,13 @@ class ParallelEngine:
         self.cfg, self.ocfg, self.dcfg, self.ecfg = model_cfg, optim_cfg, diff_cfg, ecfg
         self.grid, self.rank, self.device = grid, rank, torch.device(device)
         self.c = grid.coords(rank)
-        self.groups = groups if groups is not None else grid.build_groups(rank)
+        kinds = ("sp", "pp", "wp", "dp", "weight", "replica", "pipe") + (("tp", "tp_ortho") if model_cfg.tp > 1 else ())
+        self.groups = groups if groups is not None else grid.build_groups(rank, kinds=kinds)
+        if model_cfg.tp > 1:            # MLP weights split over the SP group (or the WP group) of this stage
+            tp_ranks = grid.tp_ranks(rank)
+            assert model_cfg.tp == len(tp_ranks), \
+                f"model.TP = {model_cfg.tp} must equal the size of the tensor-parallel group ({len(tp_ranks)})"
+            model_cfg.tp_rank = tp_ranks.index(rank)
         self.PP, self.GAS = grid.PP, ecfg.gas
         assert (model_cfg.wp[0], model_cfg.wp[1], model_cfg.sp) == (grid.WP_Y, grid.WP_X, grid.SP)
         self.wp_rank = self.c.wp_y * grid.WP_X + self.c.wp_x
@@ -67,7 +73,12 @@ class ParallelEngine:
         self.module = PipelineStage(model_cfg, self.stage_ids).to(self.device)
         init_params(self.module, model_cfg, ecfg.init_policy)
         self._broadcast_params()
-        if ecfg.dist_optimizer:
+        if model_cfg.tp > 1:
+            from .tp_optim import TPOptimizer
+            assert not ecfg.dist_optimizer, "the sharded NCCL optimizer is not combined with tensor-parallel shards"
+            self.opt = TPOptimizer(self.module, optim_cfg, self.device, self.groups.get("weight"), self.groups["tp"],
+                                   self.groups.get("tp_ortho"))
+        elif ecfg.dist_optimizer:
             from .dist_optim import DistOptimizer
             self.opt = DistOptimizer(self.module, optim_cfg, self.groups.get("weight"), rs_grads=ecfg.rs_grads)
         else:
@@ -106,7 +117,11 @@ class ParallelEngine:
             from ..parallel.symm import HaloExchange
             halo = HaloExchange(self.groups["replica"], self.device, pool_gradients=False)
         self.ctx = StreamContext(model_cfg, 1, self.replica_rank, halo.peer_fn if halo else None,
-                                 wp_group=self.groups.get("replica"), sp_group=self.groups.get("sp"))
+                                 wp_group=self.groups.get("replica"), sp_group=self.groups.get("sp"),
+                                 tp_group=self.groups.get("tp"))
+        if model_cfg.tp > 1 and self.device.type == "cuda":
+            from ..parallel.tensor import TPExchange
+            self.ctx.tp_exchange = TPExchange(self.groups["tp"], self.device)
         if grid.SP > 1 and self.device.type == "cuda":
             from ..models.fused import SPExchange
             self.ctx.sp_exchange = SPExchange(self.groups["sp"], self.device)
@@ -148,7 +163,13 @@ class ParallelEngine:
         if g is None:
             return
         src = self.grid.rank_of(0, 0, 0, self.c.pp, 0)
-        for p in self.module.parameters():
+        from ..parallel.tensor import tp_kind
+        ortho = self.groups.get("tp_ortho")
+        for n, p in self.module.named_parameters():
+            if self.cfg.tp > 1 and tp_kind(n, p) is not None:
+                if ortho is not None:        # a shard is shared by the ranks that hold the same one
+                    dist.broadcast(p.data, src=self.grid.tp_ortho_ranks(self.rank)[0], group=ortho)
+                continue
             dist.broadcast(p.data, src=src, group=g)
 
     def _sp_slice(self, tok: torch.Tensor) -> torch.Tensor:
@@ -406,7 +427,7 @@ class ParallelEngine:
         and the head rank writes the same files (the reference cannot checkpoint in that mode, :1120-1122)."""
         dist.barrier() if dist.is_initialized() else None
         head = self.rank in self.grid.stage_heads()
-        if head or self.ecfg.dist_optimizer:
+        if head or self.ecfg.dist_optimizer or self.cfg.tp > 1:      # sharded state is gathered by all its holders
             numbered = self.cur_it % self.ecfg.checkpoint_keep_every == 0 and self.cur_it > 0
             save_stage_checkpoint(self.ecfg.checkpoint_dir, self.module, self.opt, it=self.cur_it if numbered else None,
                                   write=head)

@@ -86,6 +86,28 @@ class TPOptimizer:
         self.last_lr = self.tpo.last_lr
         return total
 
+    # ---- the same update in the three phases the pipeline engine drives (NCCL / gloo collectives only) -----------------
+    def reduce(self, group=None):
+        assert not self.fused, "the peer-memory optimizer reduces inside reduce_and_step"
+        if self.ortho_group is not None and dist.get_world_size(self.ortho_group) > 1:
+            for buf in self.tpo.grad_buffers():
+                dist.all_reduce(buf, group=self.ortho_group)
+        if self.weight_group is not None:
+            for buf in self.rep.grad_buffers():
+                dist.all_reduce(buf, group=self.weight_group)
+
+    def grad_norm_sq(self, grad_scale: float) -> torch.Tensor:
+        """Squared norm of this stage's reduced, scaled gradient: replicated parameters once, shards summed over the
+        tensor-parallel group."""
+        nsq_tp = self.tpo.grad_norm_sq(grad_scale).clone()
+        dist.all_reduce(nsq_tp, group=self.tp_group)
+        return self.rep.grad_norm_sq(grad_scale) + nsq_tp
+
+    def step(self, batch_img: int, grad_scale: float, norm_sq: torch.Tensor | None = None):
+        self.rep.step(batch_img=batch_img, grad_scale=grad_scale, norm_sq=norm_sq)
+        self.tpo.step(batch_img=batch_img, grad_scale=grad_scale, norm_sq=norm_sq)
+        self.last_lr = self.tpo.last_lr
+
     # ---- state: replicated entries as the inner optimizer gives them, shards gathered to full tensors ----------------
     def _full(self, named: dict) -> dict:
         return full_state_dict(named, self.tp_group)

@@ -17,14 +17,14 @@ from aeris_gb_b200.parallel.topology import ProcessGrid
 IMG, CH, CC = (16, 32), 6, 4
 
 
-def _cfg(wp=(1, 1), sp=1, layerwise=True):
+def _cfg(wp=(1, 1), sp=1, layerwise=True, tp=1):
     """``layerwise``: True / False = diffusion with per-layer / shared noise embedding; "rit" = random-time-interval
     regression (no noise, the condition is the model input)."""
     rit = layerwise == "rit"
     return AerisConfig(img=IMG, window=(8, 8), in_channels=CC if rit else CH + CC, out_channels=CH, dim=32, heads=2,
                        head_dim=16, mlp_dim=64, n_layers=4, sublayers=1, model_dtype=torch.float32, wp=wp, sp=sp,
                        norm_eps=1e-5, layerwise_t_emb=layerwise is True, after_mod_norm=not rit, diffusion=not rit,
-                       rit=rit)
+                       rit=rit, tp=tp)
 
 
 def _field(seed, C):
@@ -54,7 +54,8 @@ def _noise_fn(eng):
     return _block(_field(3000 + _sample_index(eng), CH), eng)
 
 
-def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_dir, resume, SP=1, layerwise=True):
+def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_dir, resume, SP=1, layerwise=True,
+         TP=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     if world > 1:
         dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -62,16 +63,27 @@ def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_
     ecfg = EngineConfig(gas=gas, overlap_p2p=overlap, dist_optimizer=distopt, checkpoint_dir=ckpt_dir,
                         checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5)
     torch.manual_seed(0)
-    eng = ParallelEngine(_cfg(WP, SP, layerwise), OptimConfig(lr=0.5, eps=1.0, lr_rampup_img=0, grad_clip_max_norm=0.5, weight_decay=0.0),
+    eng = ParallelEngine(_cfg(WP, SP, layerwise, TP), OptimConfig(lr=0.5, eps=1.0, lr_rampup_img=0, grad_clip_max_norm=0.5, weight_decay=0.0),
                          DiffusionConfig(grad_scale_parity=False, cond_channels=CC), ecfg, grid, rank, "cpu",
                          data_fn=_data_fn, groups={} if world == 1 else None)
     # identical initial weights regardless of the split: every logical stage is seeded by its own index
+    from aeris_gb_b200.parallel.tensor import full_state_dict, shard_tensor, tp_kind
     for st, sd in eng.module.logical_state_dicts().items():
         g = torch.Generator().manual_seed(100 + st)
         for k, v in sd.items():
             if v.dtype.is_floating_point and "inv_freq" not in k:
-                v.copy_(torch.randn(v.shape, generator=g) * 0.1)
-    eng.opt = type(eng.opt)(eng.module, eng.ocfg, *([eng.groups.get("weight"), True] if distopt else []))
+                kind = tp_kind(k) if TP > 1 else None
+                if kind is None:
+                    v.copy_(torch.randn(v.shape, generator=g) * 0.1)
+                else:       # this rank's shard of the full-size draw
+                    shape = (v.shape[0] * TP, v.shape[1]) if kind == "w1" else (v.shape[0], v.shape[1] * TP)
+                    v.copy_(shard_tensor(kind, torch.randn(shape, generator=g) * 0.1, TP, eng.cfg.tp_rank))
+    if TP > 1:
+        from aeris_gb_b200.engine.tp_optim import TPOptimizer
+        eng.opt = TPOptimizer(eng.module, eng.ocfg, "cpu", eng.groups.get("weight"), eng.groups["tp"],
+                              eng.groups.get("tp_ortho"))
+    else:
+        eng.opt = type(eng.opt)(eng.module, eng.ocfg, *([eng.groups.get("weight"), True] if distopt else []))
     eng.noise_fn = _noise_fn
     eng.t_fn = lambda e: torch.tensor([0.2 + 0.13 * (_sample_index(e) % 9)])
     eng.keep_grads = True
@@ -84,9 +96,14 @@ def _run(rank, world, port, PP, WP, gas, overlap, distopt, iters, out_dir, ckpt_
         losses.append(eng.tot_loss)
     if ckpt_dir and not resume:
         eng.save_checkpoint()
+    final_sd, final_grads = eng.module.state_dict(), (eng.last_grads if not distopt else {})
+    if TP > 1:          # shards -> full tensors (collective over the tensor-parallel group)
+        final_sd = full_state_dict(final_sd, eng.groups["tp"])
+        final_grads = full_state_dict(final_grads, eng.groups["tp"])
     if eng.c.dp == 0 and eng.c.wp_y == 0 and eng.c.wp_x == 0 and eng.c.sp == 0:
-        torch.save({"sd": {st: {k: v.clone() for k, v in sd.items()} for st, sd in eng.module.logical_state_dicts().items()},
-                    "grads": eng.module.logical_state_dicts(eng.last_grads) if not distopt else {},
+        torch.save({"sd": {st: {k: v.clone() for k, v in sd.items()}
+                           for st, sd in eng.module.logical_state_dicts(final_sd).items()},
+                    "grads": eng.module.logical_state_dicts(final_grads) if not distopt else {},
                     "loss": losses, "norm": eng.total_norm}, os.path.join(out_dir, f"pp{eng.c.pp}.pt"))
     if world > 1:
         dist.barrier()
@@ -98,7 +115,8 @@ def _launch(world, **kw):
     from conftest import free_port
     port = free_port()
     args = (world, port, kw["PP"], kw["WP"], kw["gas"], kw.get("overlap", False), kw.get("distopt", False),
-            kw["iters"], out, kw.get("ckpt_dir"), kw.get("resume", False), kw.get("SP", 1), kw.get("layerwise", True))
+            kw["iters"], out, kw.get("ckpt_dir"), kw.get("resume", False), kw.get("SP", 1), kw.get("layerwise", True),
+            kw.get("TP", 1))
     if world == 1:
         _run(0, *args)
     else:
@@ -126,6 +144,14 @@ def _assert_same(a, b, tol=2e-5):
 @pytest.fixture(scope="module")
 def single():
     return _launch(1, PP=1, WP=(1, 1), gas=4, iters=2)
+
+
+def test_pp2_wp2_with_tensor_parallel_mlp_matches_single_process(single):
+    """The MLP weights of every block split over the two window-parallel ranks of each pipeline stage."""
+    sd, loss, norm = _launch(4, PP=2, WP=(1, 2), gas=4, iters=2, TP=2)
+    _assert_same(sd, single[0], tol=5e-5)
+    assert loss == pytest.approx(single[1], rel=1e-4)
+    assert norm == pytest.approx(single[2], rel=1e-4)
 
 
 def test_pp3_matches_single_process(single):
