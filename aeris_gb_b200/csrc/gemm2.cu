@@ -106,6 +106,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   uint64_t* tempty_bar = tfull_bar + 2;              // [2], leader only: 8 arrivals (4 epilogue warps x 2 CTAs)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
 
+  // AG: the last operand stage is the copier's ring (two 16 KB bulk-copy buffers), with its barriers behind tmem_slot
+  // (the reduce-scatter epilogue gives up the same stage: its fourth warp stages its rows there)
+  const int STAGES = (AG || p.epi == EPI_RS_PUSH) ? G2_STAGES - 1 : G2_STAGES;
+  [[maybe_unused]] uint8_t* ag_ring = smem + (G2_STAGES - 1) * G2_STAGE_BYTES;
+  [[maybe_unused]] uint64_t* ag_bars = reinterpret_cast<uint64_t*>(smem + G2_STAGES * G2_STAGE_BYTES + 256);
+
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t crank = cluster_ctarank();          // 0 = leader (issues the MMAs)
@@ -130,6 +136,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 8);
+      if constexpr (AG) mbar_init(&ag_bars[a], 1);
     }
     fence_barrier_init();
   }
@@ -184,7 +191,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             for (int j = 0; j < 2; ++j)
               tma_load_2d_pair(sb + j * 8192, &tmap_b, fb, tn * G2_BN + (crank * 2 + j) * 64, kb * G2_BK);
           }
-          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -219,7 +226,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
               umma2_ss(tmem_acc, adesc, bdesc, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
             }
             tc_commit2_mc(&empty_bar[stage], 0x3);     // frees the stage in both CTAs
-            if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
           if (!ok) break;
           tc_commit2_mc(&tfull_bar[acc], 0x3);         // accumulator ready in both CTAs
@@ -228,8 +235,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       }
     }
   } else if (AG && warp >= 6) {
-    // ------------------------------------------------------------ all-gather copiers (warps 6, 7 of both CTAs)
-    if constexpr (AG) ag_push_chunk(p, threadIdx.x - G2_THREADS);
+    // ------------------------------------------------------------ all-gather copier (warp 6 of both CTAs)
+    if constexpr (AG) {
+      if (elect_one_sync()) ag_push_chunk(p, ag_ring, ag_bars);
+    }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
     const int q = warp & 3;
@@ -246,12 +255,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       const int row = tm * 2 * G2_BM + crank * G2_BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * G2_BN + (static_cast<uint32_t>(q * 32) << 16);
       const bool kempty = (split * kb_per_split) >= kb_total;
-      gemm_epilogue_row<G2_BN>(p, taddr, row, row < p.M, tn, kempty, smem + G2_PUSH_OFF + q * PUSH_STAGE_BYTES);
+      uint8_t* stg = smem + G2_PUSH_OFF + q * PUSH_STAGE_BYTES;
+      if (p.epi == EPI_RS_PUSH)     // 8704-byte linear stages: three in the push area, the fourth in the freed operand stage
+        stg = (q < 3) ? smem + G2_PUSH_OFF + q * RS_STAGE_BYTES : smem + (G2_STAGES - 1) * G2_STAGE_BYTES;
+      gemm_epilogue_row<G2_BN>(p, taddr, row, row < p.M, tn, kempty, stg);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(leader_tempty0 + acc * 8);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    // the bulk copies of the reduce-scatter push have been performed before this thread leaves (the owners read
+    // their slots after a rank barrier that follows this kernel in the stream)
+    if (p.epi == EPI_RS_PUSH) rs_stage_drain();
   }
 
   tc_fence_before();

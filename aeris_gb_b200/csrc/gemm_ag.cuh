@@ -5,10 +5,12 @@
 
 namespace aeris {
 
-// Four copier warps behind the six GEMM warps: 128 threads x 8 vectors keep 16 KB of posted peer stores in flight per
-// SM, which the link needs at 8 ranks (two warps reached 360 GB/s of egress there).
-constexpr int AG_COPY_THREADS = 128;
-constexpr int AG_UNROLL = 8;          // 16-byte vectors in flight per copier thread (local loads, posted peer stores)
+// One copier warp (6) behind the GEMM warps; its elected lane drives the TMA unit: 16 KB pieces of this CTA's slice go
+// local memory -> shared memory ring (two buffers) -> the peer's buffer as bulk copies, so the transfer needs neither
+// registers nor issue slots and keeps two 16 KB stores in flight per SM. (Copier warps that moved the data through
+// registers with posted 16-byte stores reached about 360 GB/s of egress, whether two or four of them.)
+constexpr int AG_COPY_THREADS = 32;
+constexpr uint32_t AG_PIECE = 16384;
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const unsigned* p) {
   uint32_t v;
@@ -45,29 +47,47 @@ __device__ __forceinline__ bool ag_wait_rows(const GemmParams& p, int row0, int 
   }
   return true;
 }
-// Copier warps: push this CTA's slice of this rank's chunk into every peer's buffer, nearest consumer first, and add one
-// to this rank's arrival word on that peer. `cid` = thread index among the AG_COPY_THREADS copier threads.
-__device__ __forceinline__ void ag_push_chunk(const GemmParams& p, int cid) {
-  const long long vecs = static_cast<long long>(p.ag_rows) * p.K / 8;   // 16-byte vectors of this rank's chunk
-  const long long per = (vecs + gridDim.x - 1) / gridDim.x;
-  const long long v0 = per * blockIdx.x, v1 = min(vecs, v0 + per);
+__device__ __forceinline__ void bulk_load_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+// Copier (one elected thread): push this CTA's slice of this rank's chunk into every peer's buffer, nearest consumer
+// first, and add one to this rank's arrival word on that peer. `ring`: 2 * AG_PIECE bytes of shared memory (16-byte
+// aligned), `bars`: two mbarriers initialised with count 1. Slices start and end on 16-byte boundaries.
+__device__ __forceinline__ void ag_push_chunk(const GemmParams& p, uint8_t* ring, uint64_t* bars) {
+  const long long bytes_total = static_cast<long long>(p.ag_rows) * p.K * 2;
+  const long long per = ((bytes_total / 16 + gridDim.x - 1) / gridDim.x) * 16;
+  const long long b0 = per * blockIdx.x, b1 = min(bytes_total, b0 + per);
   const size_t off = static_cast<size_t>(p.ag_rank) * p.ag_rows * p.K * 2;
-  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.ag_local) + off);
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_local) + off;
+  uint32_t phase[2] = {0u, 0u};
+  int buf = 0;
+  bool ok = true;
   for (int j = 1; j < p.ag_world; ++j) {
     const int dst_rank = (p.ag_rank - j + p.ag_world) % p.ag_world;     // the rank that needs this chunk soonest
-    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.ag_peers[dst_rank]) + off);
-    long long i = v0 + cid;
-    for (; i + (AG_UNROLL - 1) * AG_COPY_THREADS < v1; i += AG_UNROLL * AG_COPY_THREADS) {
-      uint4 t[AG_UNROLL];
-#pragma unroll
-      for (int u = 0; u < AG_UNROLL; ++u) t[u] = src[i + u * AG_COPY_THREADS];
-#pragma unroll
-      for (int u = 0; u < AG_UNROLL; ++u) dst[i + u * AG_COPY_THREADS] = t[u];
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.ag_peers[dst_rank]) + off;
+    for (long long pos = b0; pos < b1 && ok; pos += AG_PIECE) {
+      const uint32_t n = static_cast<uint32_t>(min(static_cast<long long>(AG_PIECE), b1 - pos));
+      // the store that last read this buffer (two pieces ago) has left shared memory
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      mbar_expect_tx(&bars[buf], n);
+      bulk_load_g2s(ring + buf * AG_PIECE, src + pos, n, &bars[buf]);
+      if (!mbar_wait_poll(&bars[buf], phase[buf], p.status, ERR_TIMEOUT_FULL)) { ok = false; break; }
+      phase[buf] ^= 1u;
+      bulk_store_s2g(dst + pos, ring + buf * AG_PIECE, n);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      buf ^= 1;
     }
-    for (; i < v1; i += AG_COPY_THREADS) dst[i] = src[i];
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");            // every store of this chunk has completed
+    asm volatile("fence.proxy.async;" ::: "memory");
     __threadfence_system();
-    asm volatile("bar.sync 1, %0;" ::"n"(AG_COPY_THREADS) : "memory");
-    if (cid == 0)
+    if (ok)
       asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.ag_count_peers[dst_rank] + p.ag_rank) : "memory");
   }
 }

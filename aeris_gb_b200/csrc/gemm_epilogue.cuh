@@ -96,6 +96,36 @@ __device__ __forceinline__ void push_stage_flush2(uint8_t* stage, int lane, __nv
   __syncwarp();
 }
 
+// Reduce-scatter push: the same 32 rows x 128 columns per warp, but laid out linearly (row pitch 272 bytes: 16-byte
+// accesses of the 8 lanes of a quarter warp fall into different banks), because every lane then hands its own 256-byte
+// row segment to the TMA unit as one bulk copy into the owner's slot buffer. The epilogue warp neither issues the 16
+// store instructions per group nor waits on posted peer stores; the copy engine keeps the link busy.
+constexpr int RS_PITCH = 272;
+constexpr int RS_STAGE_BYTES = 32 * RS_PITCH;   // 8704
+__device__ __forceinline__ void rs_stage_put(uint8_t* stage, int lane, int col, const uint32_t (&o)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(stage + lane * RS_PITCH + (col / 8 + i) * 16) =
+        make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+}
+__device__ __forceinline__ void rs_stage_flush_bulk(uint8_t* stage, int lane, __nv_bfloat16* dst_row) {
+  // this lane wrote its row through the generic proxy; the bulk copy reads it through the async proxy
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (dst_row)
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 256;" ::"l"(dst_row),
+                 "r"(smem_u32(stage + lane * RS_PITCH))
+                 : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// before this lane overwrites its staged row: the copy that read it has left shared memory
+__device__ __forceinline__ void rs_stage_reuse_wait() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// before the kernel signals completion / exits: this lane's copies have been performed
+__device__ __forceinline__ void rs_stage_drain() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 // fp32 variant for the split-K reduction: the stage holds 32 rows x 64 fp32 columns; every flush instruction adds two
 // 256-byte row segments to global memory (red.add), so the atomics of one instruction fall into 16 sectors, not 32.
 __device__ __forceinline__ void push_stage_put_f32(uint8_t* stage, int lane, int col, const uint32_t (&v)[32]) {
@@ -184,8 +214,9 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
 #pragma unroll
       for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
       if (stage) {
-        push_stage_put(stage, lane, c & 127, o);
-        if ((c & 127) == 96) push_stage_flush(stage, lane, row_ok ? rowdst + (c - 96) : nullptr);
+        if ((c & 127) == 0) rs_stage_reuse_wait();
+        rs_stage_put(stage, lane, c & 127, o);
+        if ((c & 127) == 96) rs_stage_flush_bulk(stage, lane, row_ok ? rowdst + (c - 96) : nullptr);
       } else if (row_ok) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)

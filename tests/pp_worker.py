@@ -35,7 +35,7 @@ def _block(img, eng):
 
 
 def build(grid, rank, dev, overlap, groups=None, fused=False):
-    cfg = AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=128, heads=2, head_dim=64,
+    cfg = AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=256, heads=4, head_dim=64,
                       mlp_dim=256, n_layers=4, sublayers=1, norm_eps=1e-3, chunk_windows=5, wp=(grid.WP_Y, grid.WP_X),
                       sp=grid.SP)
     ecfg = EngineConfig(gas=4, overlap_p2p=overlap, checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5,
