@@ -2,6 +2,7 @@ import os
 import tempfile
 
 import numpy as np
+import pytest
 import torch
 
 from aeris_gb_b200.data import era5 as E
@@ -99,3 +100,47 @@ def test_synthetic_dataset_blocks():
     c, t = ds[0]
     assert c.shape == (8, 16, 3) and t.shape == (8, 16, 2)
     assert torch.equal(ds[4][0], c)      # pool of 4 distinct samples
+
+
+def test_rollout_to_zarr_v2_store_round_trip(tmp_path):
+    """The rollout -> Zarr conversion with the built-in Zarr v2 writer: multi-level variables become
+    [time, level, lat, lon] arrays, surface variables [time, lat, lon]; two workers split the files; a write that
+    fails transiently is retried."""
+    import json
+    from aeris_gb_b200.data.era5 import variable_names
+    from aeris_gb_b200.data.prep import h52zarr as Z
+    variables = variable_names(73)[:70]
+    rng = np.random.default_rng(0)
+    src = tmp_path / "rollout"
+    src.mkdir()
+    files, arrays = [], []
+    for m in range(3):
+        a = rng.standard_normal((4, 70, 6, 8)).astype(np.float32)
+        np.save(src / f"member{m}.npy", a)
+        files.append(str(src / f"member{m}.npy"))
+        arrays.append(a)
+    dst = str(tmp_path / "out.zarr")
+    for rank in range(2):
+        Z.convert(files, dst, variables, rank=rank, world=2, use_zarr_package=False)
+    assert json.load(open(os.path.join(dst, ".zgroup"))) == {"zarr_format": 2}
+    from aeris_gb_b200.utils.io import compress_variables
+    groups = compress_variables(variables)
+    name, (idx, levels) = next((k, v) for k, v in groups.items() if v[1])
+    for m in range(3):
+        got = Z.read_zarr_v2_array(os.path.join(dst, f"member_{m}", name))
+        assert got.shape == (4, len(levels), 6, 8) and np.array_equal(got, arrays[m][:, idx])
+        meta = json.load(open(os.path.join(dst, f"member_{m}", name, ".zattrs")))
+        assert meta["_ARRAY_DIMENSIONS"] == ["time", "level", "latitude", "longitude"]
+        surf = Z.read_zarr_v2_array(os.path.join(dst, f"member_{m}", "2m_temperature"))
+        assert np.array_equal(surf, arrays[m][:, groups["2m_temperature"][0][0]])
+    # retries: two transient failures, then success; a persistent failure is raised after the last attempt
+    calls = {"n": 0}
+
+    def flaky():
+        calls["n"] += 1
+        if calls["n"] < 3:
+            raise OSError("stale file handle")
+        return "ok"
+    assert Z._write_with_retries(flaky, 10, sleep=lambda s: None) == "ok" and calls["n"] == 3
+    with pytest.raises(OSError):
+        Z._write_with_retries(lambda: (_ for _ in ()).throw(OSError("gone")), 3, sleep=lambda s: None)
