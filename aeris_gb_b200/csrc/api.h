@@ -55,6 +55,9 @@ int aeris_gather_rows(const void* gidx, const void* const* peer_ptrs, int n_peer
 int aeris_swiglu_fwd(const void* u, void* act, long long rows, int F, void* stream);
 int aeris_swiglu_bwd(const void* u, const void* dact, void* du, long long rows, int F, void* stream);
 int aeris_scale_rows(const void* W, const float* g, void* Wg, int R, int C, void* stream);
+// In-place 2-D rotary embedding of the q and k sections of qkv [rows, 3 * heads * d] (bf16); cos / sin: [L, d / 2] fp32.
+int aeris_rope_qk(void* qkv, const float* cos_t, const float* sin_t, long long rows, int L, int heads, int d, int inverse,
+                  void* stream);
 int aeris_gate_grad_finalize(float* G, const void* W, const float* g, float* dW, float* dg, int R, int C,
                              void* stream);
 int aeris_sumsq(const float* x, long long n, double* out, void* stream);

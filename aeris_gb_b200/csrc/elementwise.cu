@@ -564,6 +564,39 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ u, const __n
   }
 }
 
+// ------------------------------------------------------------------------------------------------ rotary embedding
+// In-place axial 2-D rotary embedding of the q and k sections of a fused qkv tensor [rows, 3 * heads * d] (columns
+// q | k | v, head, d): the (2i, 2i + 1) channel pairs of every head rotate by the angle of (token, pair i), with the
+// token = row mod L and cos / sin tables [L, d / 2] (fp32). `inverse` rotates by the negative angles (what the backward
+// pass applies to the gradients of the rotated q and k). One thread: eight channels = four pairs.
+__global__ void rope_qk_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cs, const float* __restrict__ sn,
+                               long long rows, int L, int heads, int d, int inverse) {
+  const int HD = heads * d;
+  const int vec_per_row = 2 * HD / 8;              // q and k sections only
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row) * 8;       // column inside q | k
+    const int within = c % d;                                      // channel inside the head
+    const int tok = static_cast<int>(r % L);
+    __nv_bfloat16* ptr = qkv + static_cast<size_t>(r) * 3 * HD + c;
+    float v[8];
+    load8(ptr, v);
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + static_cast<size_t>(tok) * (d / 2) + within / 2);
+    float4 s4 = *reinterpret_cast<const float4*>(sn + static_cast<size_t>(tok) * (d / 2) + within / 2);
+    if (inverse) { s4.x = -s4.x; s4.y = -s4.y; s4.z = -s4.z; s4.w = -s4.w; }
+    const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+    float o[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      o[2 * k] = v[2 * k] * cc[k] - v[2 * k + 1] * ss[k];
+      o[2 * k + 1] = v[2 * k + 1] * cc[k] + v[2 * k] * ss[k];
+    }
+    store8(ptr, o);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ gate helpers
 // Wg[r, :] = g[r] * W[r, :]  (bf16), used as the B operand of the gated data-gradient GEMMs.
 __global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ W, const float* __restrict__ g,
@@ -826,6 +859,16 @@ extern "C" int aeris_scale_rows(const void* W, const float* g, void* Wg, int R, 
   const int grid = grid_for(static_cast<long long>(R) * (C / 8), 256, aeris_num_sms() * 8);
   scale_rows_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(W), g, reinterpret_cast<__nv_bfloat16*>(Wg), R, C);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int aeris_rope_qk(void* qkv, const float* cos_t, const float* sin_t, long long rows, int L, int heads,
+                             int d, int inverse, void* stream) {
+  if (rows <= 0 || L <= 0 || d % 8 != 0 || heads <= 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t)) & 15) return -3;
+  const int grid = grid_for(rows * (2 * heads * d / 8), 256, aeris_num_sms() * 16);
+  rope_qk_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(qkv), cos_t, sin_t, rows, L, heads, d, inverse);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 

@@ -21,7 +21,7 @@ class InfiniteSampler(Sampler):
         order = np.arange(self.n)
         rnd, window = None, 0
         if self.shuffle:
-            rnd = np.random.RandomState(self.seed)
+            rnd = np.random.default_rng(self.seed)     # the generator class fixes the sample order for a seed
             rnd.shuffle(order)
             window = int(np.rint(order.size * self.window_size))
         idx = self.start_idx
@@ -30,7 +30,7 @@ class InfiniteSampler(Sampler):
             if idx % self.num_replicas == self.rank:
                 yield int(order[i])
             if window >= 2:
-                j = (i - rnd.randint(window)) % order.size
+                j = (i - rnd.integers(window)) % order.size
                 order[i], order[j] = order[j], order[i]
             idx += 1
 

@@ -110,15 +110,11 @@ def _scatter_heads(a: torch.Tensor, w: torch.Tensor, sp: "SPExchange", peers: li
 
 
 def _rope_qk_(qkv: torch.Tensor, meta: BlockMeta, nw: int, inverse: bool = False) -> None:
-    """Rotates the q and k sections of a chunk's fused qkv tensor in place (optional feature, PyTorch element-wise
-    ops; ``inverse`` turns gradients with respect to the rotated q, k into gradients with respect to the projections)."""
-    from . import oracle as O
+    """Rotates the q and k sections of a chunk's fused qkv tensor in place (``rope_qk_kernel``; ``inverse`` turns
+    gradients with respect to the rotated q, k into gradients with respect to the projections)."""
     assert meta.sp is None, "the rotary embedding is not combined with sequence parallelism"
     cos, sin = meta.rope
-    v = qkv.view(nw, meta.L, 3, meta.heads, meta.head_dim)
-    for i in (0, 1):
-        x = v[:, :, i].permute(0, 2, 1, 3)                              # [nw, H, L, d]
-        v[:, :, i] = O.apply_rope_2d(x, cos, sin, inverse).permute(0, 2, 1, 3)
+    E.rope_qk_(qkv, cos.float().contiguous(), sin.float().contiguous(), meta.L, meta.heads, meta.head_dim, inverse)
 
 
 def _chunks(meta: BlockMeta):

@@ -94,6 +94,16 @@ def scale_rows(W: torch.Tensor, g: torch.Tensor, out: torch.Tensor | None = None
     return out
 
 
+def rope_qk_(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, L: int, heads: int, head_dim: int,
+             inverse: bool = False) -> torch.Tensor:
+    """Rotates the q and k sections of ``qkv`` [rows, 3 * heads * head_dim] (bf16, contiguous) in place by the 2-D rotary
+    angles ``cos`` / ``sin`` [L, head_dim / 2] (fp32); row r belongs to token r mod L of its window."""
+    assert qkv.is_contiguous() and qkv.shape[1] == 3 * heads * head_dim and cos.shape == (L, head_dim // 2)
+    _l.check(_l.lib().aeris_rope_qk(_l.ptr(qkv), _l.ptr(cos), _l.ptr(sin), _l._c_ll(qkv.shape[0]), L, heads, head_dim,
+                                    int(inverse), _l.stream_ptr()), "rope_qk")
+    return qkv
+
+
 def gate_grad_finalize(G: torch.Tensor, W: torch.Tensor, g: torch.Tensor, dW: torch.Tensor, dg: torch.Tensor) -> None:
     R, C = W.shape
     _l.check(_l.lib().aeris_gate_grad_finalize(_l.ptr(G), _l.ptr(W), _l.ptr(g), _l.ptr(dW), _l.ptr(dg), R, C,

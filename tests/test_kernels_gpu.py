@@ -196,6 +196,28 @@ def test_modnorm_gather_and_gather_rows():
     assert torch.equal(out, g)
 
 
+@pytest.mark.parametrize("heads,d", [(4, 64), (2, 128)])
+def test_rope_kernel_matches_fp32_rotation_and_its_inverse(heads, d):
+    """In-place 2-D rotary embedding of the q and k sections of a fused qkv tensor against the fp32 formula; v stays
+    untouched; the inverse rotation restores q and k to bf16 rounding."""
+    from aeris_gb_b200.models import oracle as O
+    from aeris_gb_b200.ops import elementwise as E
+    ws, nw = (6, 10), 3
+    L = ws[0] * ws[1]
+    cos, sin = O.rope_2d_cache(ws[0], ws[1], d, 10_000.0, DEV)
+    qkv = torch.randn(nw * L, 3 * heads * d, device=DEV).bfloat16()
+    v5 = qkv.float().view(nw, L, 3, heads, d)
+    ref = v5.clone()
+    for i in (0, 1):
+        ref[:, :, i] = O.apply_rope_2d(v5[:, :, i].permute(0, 2, 1, 3), cos, sin).permute(0, 2, 1, 3)
+    got = qkv.clone()
+    E.rope_qk_(got, cos.float().contiguous(), sin.float().contiguous(), L, heads, d)
+    assert rel_err(got, ref.view(nw * L, -1)) < TOL
+    assert torch.equal(got.view(nw, L, 3, heads, d)[:, :, 2], qkv.view(nw, L, 3, heads, d)[:, :, 2])
+    E.rope_qk_(got, cos.float().contiguous(), sin.float().contiguous(), L, heads, d, inverse=True)
+    assert rel_err(got, qkv) < 2 * TOL
+
+
 def test_swiglu_and_gate_helpers():
     from aeris_gb_b200.ops import elementwise as E
     rows, F = 333, 512

@@ -93,6 +93,18 @@ def test_infinite_sampler_is_rank_strided_and_endless():
     sh = iter(InfiniteSampler(ds, shuffle=True, seed=3))
     drawn = [next(sh) for _ in range(200)]
     assert set(drawn) == set(range(10))          # windowed re-shuffling keeps every element in circulation
+    # the order for a seed is that of numpy's default generator (src/aeris/data/samplers.py:35-45): first the shuffled
+    # permutation, one windowed swap after every index
+    rnd = np.random.default_rng(3)
+    order = np.arange(10)
+    rnd.shuffle(order)
+    expect = []
+    for idx in range(25):
+        i = idx % 10
+        expect.append(int(order[i]))
+        j = (i - rnd.integers(5)) % 10
+        order[i], order[j] = order[j], order[i]
+    assert drawn[:25] == expect
 
 
 def test_synthetic_dataset_blocks():
