@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Puts the reference's sources under ``baseline/_ref`` (kept out of git) for the reference arm of ``bench.py``.
 
-    python baseline/install_ref.py [/path/to/AERIS-GB checkout]
+    python baseline/install_ref.py /path/to/AERIS-GB        (or AERIS_REFERENCE=/path/to/AERIS-GB)
 
 First the packaging route (``pip install --no-index --no-build-isolation --target baseline/_ref <checkout>``); the
 reference builds with hatchling, so where that backend is not installed pip stops before copying anything and the
@@ -18,12 +18,13 @@ DEST = os.path.join(HERE, "_ref")
 
 
 def main() -> int:
-    src = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AERIS_REFERENCE", "/root/reference")
-    if not os.path.isdir(os.path.join(src, "src", "aeris")):
-        print(f"no AERIS-GB checkout at {src}")
+    src = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AERIS_REFERENCE")
+    if not src or not os.path.isdir(os.path.join(src, "src", "aeris")):
+        print(f"no AERIS-GB checkout at {src!r}: pass its path as the argument or in AERIS_REFERENCE")
         return 1
     os.makedirs(DEST, exist_ok=True)
-    work = os.path.join("/tmp", "aeris_ref_build")          # pip may write into the tree it builds from
+    import tempfile
+    work = os.path.join(tempfile.gettempdir(), "aeris_ref_build")          # pip may write into the tree it builds from
     shutil.rmtree(work, ignore_errors=True)
     shutil.copytree(src, work)
     cmd = [sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps"]
