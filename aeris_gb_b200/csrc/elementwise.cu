@@ -346,16 +346,18 @@ modnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 //   * two rows share one block-wide reduction, whose cross-warp part is one shared-memory load and seven shuffles per
 //     thread (lane k * 8 + w holds value k of warp w) instead of 24 loads and adds;
 //   * 1 + scale is formed once per thread.
-__global__ void __launch_bounds__(192, 2)
+template <int RPI, int MINB>
+__global__ void __launch_bounds__(192, MINB)
 modnorm_bwd_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dh,
                         const __nv_bfloat16* __restrict__ dres, const float* __restrict__ scale,
                         const float* __restrict__ shift, const __nv_bfloat16* __restrict__ w,
                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dscale, float* __restrict__ dshift,
                         float* __restrict__ dw, int rows, int D, int mode, float eps, const float* __restrict__ wf) {
-  constexpr int RPI = 2;
-  __shared__ float red[2][32];
+  constexpr int NV = 2 * RPI;                    // values to reduce per iteration
+  constexpr int NL = (NV * 8 + 31) / 32;         // slot k * 8 + w holds value k of warp w; a lane sums NL of them
+  __shared__ float red[2][NL * 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < 64; i += blockDim.x) (&red[0][0])[i] = 0.f;   // slots of absent warps stay zero
+  for (int i = threadIdx.x; i < 2 * NL * 32; i += blockDim.x) (&red[0][0])[i] = 0.f;   // slots of absent warps stay zero
   const int c0 = threadIdx.x * 8;
   const bool active = c0 < D;
   uint64_t sc1[4], sh[4], wv[4], a_sc[4], a_sh[4], a_w[4];
@@ -449,12 +451,16 @@ modnorm_bwd_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
       for (int j = 0; j < 2 * RPI; ++j) red[parity][j * 8 + warp] = s[j];
     }
     __syncthreads();
-    float t = red[parity][lane];
-    t += __shfl_xor_sync(0xffffffffu, t, 4);
-    t += __shfl_xor_sync(0xffffffffu, t, 2);
-    t += __shfl_xor_sync(0xffffffffu, t, 1);
+    float t[NL];
 #pragma unroll
-    for (int j = 0; j < 2 * RPI; ++j) s[j] = __shfl_sync(0xffffffffu, t, j * 8);
+    for (int q = 0; q < NL; ++q) {
+      t[q] = red[parity][q * 32 + lane];
+      t[q] += __shfl_xor_sync(0xffffffffu, t[q], 4);
+      t[q] += __shfl_xor_sync(0xffffffffu, t[q], 2);
+      t[q] += __shfl_xor_sync(0xffffffffu, t[q], 1);
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) s[j] = __shfl_sync(0xffffffffu, t[j / 4], (j % 4) * 8);
     // ---- gradients
 #pragma unroll
     for (int k = 0; k < RPI; ++k) {
@@ -811,7 +817,9 @@ extern "C" int aeris_modnorm_bwd(const void* x, const void* dh, const void* dres
   const int grid = (rows + rpc - 1) / rpc;    // every CTA takes about rpc rows, interleaved with the others
   const int nt = row_threads(D);
   if (nt <= 192) {
-    modnorm_bwd_pair_kernel<<<grid, nt, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    // two rows per reduction and two CTAs per SM measured best (0.381 ms for 129600 x 1536; one row and three CTAs
+    // 0.430 ms, four rows and one CTA 0.398 ms, two rows under a 112-register cap spill: 0.822 ms)
+    modnorm_bwd_pair_kernel<2, 2><<<grid, nt, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(dh),
         reinterpret_cast<const __nv_bfloat16*>(dres), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
         reinterpret_cast<__nv_bfloat16*>(dx), dscale, dshift, dw, rows, D, mode, eps, w_f32);
