@@ -33,9 +33,9 @@ struct GemmParams {
   // EPI_RS_PUSH reuses scat_peers / scat_rank / scat_ld with scat_n_local = rows owned by one rank.
   void* scat_peers[8];
   int scat_rank, scat_n_local, scat_L, scat_sec_w, scat_own_w, scat_ld;
-  // All-gather fused into the A operand (one-CTA kernel only): A's rows are `ag_world` chunks of `ag_rows` rows. Chunk
-  // ag_rank is this rank's own and already in place in `ag_local`; copier warps PUSH it into every peer's buffer
-  // `ag_peers[p]` (same layout on every rank; posted stores, nearest consumer first) and then add 1 to word `ag_rank` of
+  // All-gather fused into the A operand (two-CTA kernel): A's rows are `ag_world` chunks of `ag_rows` rows. Chunk
+  // ag_rank is this rank's own and already in place in `ag_local`; a copier thread PUSHES it into every peer's buffer
+  // `ag_peers[p]` (same layout on every rank; bulk copies, nearest consumer first) and then adds 1 to word `ag_rank` of
   // that peer's counter array `ag_count_peers[p]`. Tiles of chunk c wait until the local word `ag_count[c]` reaches
   // `ag_expect` (counters only ever grow: expect = calls so far x CTAs per call).
   void* ag_peers[8];

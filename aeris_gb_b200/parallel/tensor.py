@@ -3,7 +3,7 @@
 The token rows are sharded over the ``tp`` ranks (the layout Ulysses sequence parallelism already gives the residual
 stream), ``w1`` is split by output features and ``w2`` by input features:
 
-    X_full = all_gather_rows(h)                 -- fused: copier warps of the w1 GEMM push this rank's rows to the peers
+    X_full = all_gather_rows(h)                 -- fused: a copier thread of the w1 GEMM pushes this rank's rows to the peers (bulk copies)
     U_r    = X_full @ w1_r^T ; act_r = silu(gate) * up          while its tiles start on the local rows
     Y      = reduce_scatter_rows(act_r @ w2_r^T)  -- fused: the w2 GEMM's epilogue stores each bf16 partial tile into
                                                     the owner rank's slot buffer; the owner sums its slots
