@@ -100,6 +100,33 @@ __device__ __forceinline__ void block_sum(float (&v)[NRED], float* red, int pari
   }
 }
 
+// Block-wide sums of FOUR values per thread for CTAs of at most eight warps, built for few instructions: inside a warp
+// the four values are folded by halving (lanes that differ in bit 4 split the values two and two, lanes that differ in
+// bit 3 one and one: 6 shuffles instead of 20), the four lane groups write value k of warp w to slot k * 8 + w, and
+// after one __syncthreads every lane sums one slot row with three more shuffles and fetches the four totals.
+// `red`: [2][32] floats zeroed at kernel start (slots of absent warps stay zero), double buffered by `parity`.
+__device__ __forceinline__ void block_sum4_shfl(float (&s)[4], float (*red)[32], int parity, int lane, int warp) {
+  const bool b4 = lane & 16, b3 = lane & 8;
+  float a0 = b4 ? s[2] : s[0], a1 = b4 ? s[3] : s[1];
+  const float g0 = b4 ? s[0] : s[2], g1 = b4 ? s[1] : s[3];
+  a0 += __shfl_xor_sync(0xffffffffu, g0, 16);
+  a1 += __shfl_xor_sync(0xffffffffu, g1, 16);
+  float c = b3 ? a1 : a0;
+  const float d = b3 ? a0 : a1;
+  c += __shfl_xor_sync(0xffffffffu, d, 8);
+  c += __shfl_xor_sync(0xffffffffu, c, 4);
+  c += __shfl_xor_sync(0xffffffffu, c, 2);
+  c += __shfl_xor_sync(0xffffffffu, c, 1);
+  if ((lane & 7) == 0) red[parity][(lane >> 3) * 8 + warp] = c;      // value index = 2 * bit4 + bit3 = lane >> 3
+  __syncthreads();
+  float t = red[parity][lane];
+  t += __shfl_xor_sync(0xffffffffu, t, 4);
+  t += __shfl_xor_sync(0xffffffffu, t, 2);
+  t += __shfl_xor_sync(0xffffffffu, t, 1);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) s[j] = __shfl_sync(0xffffffffu, t, j * 8);
+}
+
 // ------------------------------------------------------------------------------------------------ modulate + RMSNorm
 // One CTA streams over rows; thread t owns columns [8t, 8t+8). mode 0: h = RMSNorm(x*(1+scale)+shift)*w
 // (modulate -> norm); mode 1: h = (RMSNorm(x)*w)*(1+scale)+shift (norm -> modulate). scale/shift may be null
@@ -199,6 +226,117 @@ __global__ void modnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const ui
           for (int i = 0; i < 8; ++i) o[i] -= __bfloat162float(__float2bfloat16_rn(o[i]));
           store8(h_lo + static_cast<size_t>(rr) * D + c0, o);
         }
+      }
+    }
+  }
+}
+
+// The same forward for rows of up to 1536 columns (at most six warps), written for the instruction issue rate: the kernel
+// above executes 20.6 warp instructions per element and keeps the schedulers 64 % busy with no memory stall to speak
+// of. Here every per-element operation works on a column pair (`*.f32x2`), 1 + scale is formed once, the row mean uses
+// a multiplication, and the four rows' sums go through block_sum4_shfl.
+__global__ void __launch_bounds__(192, 3)
+modnorm_fwd_pair_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ gidx, PeerPtrs peers,
+                        __nv_bfloat16* __restrict__ x_out, const float* __restrict__ scale,
+                        const float* __restrict__ shift, const __nv_bfloat16* __restrict__ w,
+                        __nv_bfloat16* __restrict__ h, int rows, int D, int mode, float eps,
+                        const float* __restrict__ wf, __nv_bfloat16* __restrict__ h_lo) {
+  static_assert(FWD_RPI == 4, "block_sum4_shfl reduces four values");
+  __shared__ float red[2][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 64; i += blockDim.x) (&red[0][0])[i] = 0.f;
+  const int c0 = threadIdx.x * 8;
+  const bool active = c0 < D;
+  uint64_t sc1[4], sh[4], wv[4];
+  {
+    float t_sc[8], t_sh[8], t_w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { t_sc[i] = 0.f; t_sh[i] = 0.f; t_w[i] = 0.f; }
+    if (active) {
+      if (scale) loadf8(scale + c0, t_sc);
+      if (shift) loadf8(shift + c0, t_sh);
+      if (wf) loadf8(wf + c0, t_w); else load8(w + c0, t_w);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sc1[i] = f2_pack(1.f + t_sc[2 * i], 1.f + t_sc[2 * i + 1]);
+      sh[i] = f2_pack(t_sh[2 * i], t_sh[2 * i + 1]);
+      wv[i] = f2_pack(t_w[2 * i], t_w[2 * i + 1]);
+    }
+  }
+  __syncthreads();
+  const int r1 = rows;
+  const int stride = gridDim.x * FWD_RPI;
+  const float inv_d = 1.f / D;
+  uint4 nxt[FWD_RPI];
+  auto fetch = [&](int r) {
+#pragma unroll
+    for (int k = 0; k < FWD_RPI; ++k) {
+      const int rr = r + k;
+      nxt[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (active && rr < r1) {
+        const __nv_bfloat16* src;
+        bool ok = true;
+        if (gidx) {
+          const uint32_t code = gidx[rr];
+          ok = AERIS_GATHER_OK(peers, code);
+          src = peers.p[code >> 28] + static_cast<size_t>(code & 0x0fffffffu) * D + c0;
+        } else {
+          src = x + static_cast<size_t>(rr) * D + c0;
+        }
+        if (ok) nxt[k] = *reinterpret_cast<const uint4*>(src);
+      }
+    }
+  };
+  int parity = 0;
+  int r = blockIdx.x * FWD_RPI;
+  if (r < r1) fetch(r);
+  for (; r < r1; r += stride, parity ^= 1) {
+    uint64_t y[FWD_RPI][4];
+    float ss[FWD_RPI];
+    uint4 cur[FWD_RPI];
+#pragma unroll
+    for (int k = 0; k < FWD_RPI; ++k) cur[k] = nxt[k];
+    if (r + stride < r1) fetch(r + stride);
+#pragma unroll
+    for (int k = 0; k < FWD_RPI; ++k) {
+      const int rr = r + k;
+      const bool live = active && rr < r1;
+      if (live && x_out) *reinterpret_cast<uint4*>(x_out + static_cast<size_t>(rr) * D + c0) = cur[k];
+      const uint32_t w4[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
+      uint64_t p = 0ull;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint64_t v = f2_from_bf16x2(w4[i]);
+        y[k][i] = (mode == 0) ? f2_fma(v, sc1[i], sh[i]) : v;
+        p = f2_fma(y[k][i], y[k][i], p);
+      }
+      float p0, p1;
+      f2_unpack(p, p0, p1);
+      ss[k] = live ? p0 + p1 : 0.f;
+    }
+    block_sum4_shfl(ss, red, parity, lane, warp);
+#pragma unroll
+    for (int k = 0; k < FWD_RPI; ++k) {
+      const int rr = r + k;
+      if (!active || rr >= r1) continue;
+      const float rinv = rsqrtf(ss[k] * inv_d + eps);
+      const uint64_t rinv2 = f2_pack(rinv, rinv);
+      uint64_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint64_t n = f2_mul(f2_mul(y[k][i], rinv2), wv[i]);
+        o[i] = (mode == 0) ? n : f2_fma(n, sc1[i], sh[i]);
+      }
+      uint32_t hw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) hw[i] = f2_to_bf16x2(o[i]);
+      *reinterpret_cast<uint4*>(h + static_cast<size_t>(rr) * D + c0) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+      if (h_lo) {          // the part of the fp32 value that the bf16 value above does not hold
+        uint32_t lw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) lw[i] = f2_to_bf16x2(f2_sub(o[i], f2_from_bf16x2(hw[i])));
+        *reinterpret_cast<uint4*>(h_lo + static_cast<size_t>(rr) * D + c0) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
       }
     }
   }
@@ -441,26 +579,30 @@ modnorm_bwd_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
       s[2 * k + 1] = live ? b0 + b1 : 0.f;
     }
     // ---- block-wide sums
+    if constexpr (RPI == 2) {
+      block_sum4_shfl(s, red, parity, lane, warp);
+    } else {
 #pragma unroll
-    for (int j = 0; j < 2 * RPI; ++j) {
+      for (int j = 0; j < 2 * RPI; ++j) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
+        for (int o = 16; o > 0; o >>= 1) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < 2 * RPI; ++j) red[parity][j * 8 + warp] = s[j];
+      }
+      __syncthreads();
+      float t[NL];
+#pragma unroll
+      for (int q = 0; q < NL; ++q) {
+        t[q] = red[parity][q * 32 + lane];
+        t[q] += __shfl_xor_sync(0xffffffffu, t[q], 4);
+        t[q] += __shfl_xor_sync(0xffffffffu, t[q], 2);
+        t[q] += __shfl_xor_sync(0xffffffffu, t[q], 1);
+      }
+#pragma unroll
+      for (int j = 0; j < NV; ++j) s[j] = __shfl_sync(0xffffffffu, t[j / 4], (j % 4) * 8);
     }
-    if (lane == 0) {
-#pragma unroll
-      for (int j = 0; j < 2 * RPI; ++j) red[parity][j * 8 + warp] = s[j];
-    }
-    __syncthreads();
-    float t[NL];
-#pragma unroll
-    for (int q = 0; q < NL; ++q) {
-      t[q] = red[parity][q * 32 + lane];
-      t[q] += __shfl_xor_sync(0xffffffffu, t[q], 4);
-      t[q] += __shfl_xor_sync(0xffffffffu, t[q], 2);
-      t[q] += __shfl_xor_sync(0xffffffffu, t[q], 1);
-    }
-#pragma unroll
-    for (int j = 0; j < NV; ++j) s[j] = __shfl_sync(0xffffffffu, t[j / 4], (j % 4) * 8);
     // ---- gradients
 #pragma unroll
     for (int k = 0; k < RPI; ++k) {
@@ -801,6 +943,13 @@ extern "C" int aeris_modnorm_fwd(const void* x, const void* gidx, const void* co
   const int rpc = pick_rows_per_cta(rows);
   int grid = (rows + FWD_RPI - 1) / FWD_RPI;
   if (grid > aeris_num_sms() * 8) grid = aeris_num_sms() * 8;
+  if (row_threads(D) <= 192) {
+    modnorm_fwd_pair_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const uint32_t*>(gidx), pp,
+        reinterpret_cast<__nv_bfloat16*>(x_out), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
+        reinterpret_cast<__nv_bfloat16*>(h), rows, D, mode, eps, w_f32, reinterpret_cast<__nv_bfloat16*>(h_lo));
+    return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  }
   modnorm_fwd_kernel<<<grid, row_threads(D), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const uint32_t*>(gidx), pp,
       reinterpret_cast<__nv_bfloat16*>(x_out), scale, shift, reinterpret_cast<const __nv_bfloat16*>(w),
