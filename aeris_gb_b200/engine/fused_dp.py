@@ -138,10 +138,16 @@ class FusedShardedOptimizer:
         """Whole update. Returns the device scalar with the squared global gradient norm (after scaling).
         ``extra_sumsq``: squared norm (already scaled and complete) of gradients that another optimizer manages and
         that count towards the same clipping norm (tensor-parallel shards)."""
-        c, lib = self.cfg, L.lib()
-        self.step_count += 1
-        lr = lr_at(self.cur_nimg, c.lr, c)
-        beta = ema_beta_at(self.cur_nimg, batch_img, c) if c.use_ema else None
+        nsq = self.reduce_scatter(grad_scale)
+        if extra_sumsq is not None:
+            nsq += extra_sumsq.to(nsq.dtype)
+        return self.apply(batch_img, grad_scale, nsq)
+
+    def reduce_scatter(self, grad_scale: float) -> torch.Tensor:
+        """First half: every rank's shard of the summed, scaled gradient lands in ``gshard`` and the squared norm of the
+        whole reduced gradient (all segments, all ranks of the group) is returned as a device scalar. A caller that
+        clips over more than this group (pipeline stages) adds the other parts to it before :meth:`apply`."""
+        lib = L.lib()
         f = ctypes.c_float
         self._sumsq.zero_()
         self._sumsq_local.zero_()
@@ -158,8 +164,17 @@ class FusedShardedOptimizer:
         # the scalar reduction doubles as the barrier that says every rank has finished READING peer gradients
         dist.all_reduce(self._sumsq, group=self.group)
         self._sumsq += self._sumsq_local * (grad_scale * grad_scale)
-        if extra_sumsq is not None:
-            self._sumsq += extra_sumsq.to(self._sumsq.dtype)
+        return self._sumsq
+
+    def apply(self, batch_img: int, grad_scale: float, norm_sq: torch.Tensor) -> torch.Tensor:
+        """Second half: clip by ``norm_sq``, AdamW on the master shard, bf16 weights stored into every peer's buffer."""
+        c, lib = self.cfg, L.lib()
+        f = ctypes.c_float
+        self.step_count += 1
+        lr = lr_at(self.cur_nimg, c.lr, c)
+        beta = ema_beta_at(self.cur_nimg, batch_img, c) if c.use_ema else None
+        if norm_sq is not self._sumsq:
+            self._sumsq.copy_(norm_sq.to(self._sumsq.dtype).reshape(self._sumsq.shape))
         max_norm = c.grad_clip_max_norm if c.grad_clip else 0.0
         for s in self.segments:
             wd = c.weight_decay if s.decay else 0.0

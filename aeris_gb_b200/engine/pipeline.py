@@ -78,6 +78,11 @@ class ParallelEngine:
             assert not ecfg.dist_optimizer, "the sharded NCCL optimizer is not combined with tensor-parallel shards"
             self.opt = TPOptimizer(self.module, optim_cfg, self.device, self.groups.get("weight"), self.groups["tp"],
                                    self.groups.get("tp_ortho"))
+        elif ecfg.dist_optimizer and self.device.type == "cuda" and self.groups.get("weight") is not None:
+            # the sharded optimizer on this library's peer-memory kernels (reduce-scatter, clip, AdamW and the
+            # all-gather of the bf16 weights in two launches per segment); NCCL / gloo ranks take the class below
+            from .fused_dp import FusedShardedOptimizer
+            self.opt = FusedShardedOptimizer(self.module, optim_cfg, self.groups["weight"], self.device, False)
         elif ecfg.dist_optimizer:
             from .dist_optim import DistOptimizer
             self.opt = DistOptimizer(self.module, optim_cfg, self.groups.get("weight"), rs_grads=ecfg.rs_grads)
@@ -378,6 +383,15 @@ class ParallelEngine:
         if not self.dcfg.grad_scale_parity:
             scale /= self.grid.WP_Y * self.grid.WP_X * self.grid.SP
         self._scale = scale
+        if hasattr(self.opt, "reduce_scatter"):       # fused sharded optimizer: reduction and norm in one pass
+            nsq = self.opt.reduce_scatter(scale)
+            self._nsq = nsq
+            if self.ocfg.grad_clip:
+                self.stage_norm = float(nsq.item())
+                if self.groups.get("pp") is not None:
+                    dist.all_reduce(nsq, group=self.groups["pp"])
+                self.total_norm = float(nsq.item()) ** 0.5
+            return
         self.opt.reduce(self.groups.get("weight")) if hasattr(self.opt, "reduce") else self._allreduce_flat()
         if self.keep_grads:
             self.last_grads = {n: p.main_grad.clone() * scale for n, p in self.module.named_parameters()
@@ -399,7 +413,10 @@ class ParallelEngine:
             dist.all_reduce(b, group=g)
 
     def step(self):
-        self.opt.step(batch_img=self.GAS * self.grid.DP, grad_scale=self._scale, norm_sq=self._nsq)
+        if hasattr(self.opt, "reduce_scatter"):
+            self.opt.apply(self.GAS * self.grid.DP, self._scale, self._nsq)
+        else:
+            self.opt.step(batch_img=self.GAS * self.grid.DP, grad_scale=self._scale, norm_sq=self._nsq)
         self.cur_it += 1
 
     # schedule execution --------------------------------------------------------------------------------------------

@@ -1,7 +1,8 @@
 """Worker of the GPU pipeline-parallel test: the instruction-schedule engine with NCCL p2p between the stages (CUDA
 kernels in every block, peer-memory halo and Ulysses exchanges inside the stages) has to reproduce the losses and the
 updated weights of the same engine with every stage on one GPU. argv: overlap (1 = overlapped 1F1B schedule), PP,
-WP_X, SP, fused (defaults: 0, world, 1, 1, 0). fused = 1: the end stages run the fused noising + embedding and head +
+WP_X, SP, fused, distopt (defaults: 0, world, 1, 1, 0, 0). distopt = 1: the sharded optimizer on the peer-memory
+kernels in the split run. fused = 1: the end stages run the fused noising + embedding and head +
 loss kernels with their counter-based noise (the same field for any split); 0: PyTorch ends with injected noise."""
 import os
 import sys
@@ -34,12 +35,12 @@ def _block(img, eng):
     return img[:, eng.c.wp_y * hb:(eng.c.wp_y + 1) * hb, eng.c.wp_x * wb:(eng.c.wp_x + 1) * wb].contiguous()
 
 
-def build(grid, rank, dev, overlap, groups=None, fused=False):
+def build(grid, rank, dev, overlap, groups=None, fused=False, distopt=False):
     cfg = AerisConfig(img=IMG, window=(8, 8), in_channels=CH + CC, out_channels=CH, dim=256, heads=4, head_dim=64,
                       mlp_dim=256, n_layers=4, sublayers=1, norm_eps=1e-3, chunk_windows=5, wp=(grid.WP_Y, grid.WP_X),
                       sp=grid.SP)
     ecfg = EngineConfig(gas=4, overlap_p2p=overlap, checkpoint_every=10 ** 9, init_policy=dict(skip=True), seed=5,
-                        fused_io=fused)
+                        fused_io=fused, dist_optimizer=distopt)
     eng = ParallelEngine(cfg, OptimConfig(lr=1e-2, lr_rampup_img=0, grad_clip_max_norm=1.0, weight_decay=0.0),
                          DiffusionConfig(grad_scale_parity=False, cond_channels=CC), ecfg, grid, rank, dev,
                          data_fn=lambda e: (_block(_field(1000 + _idx(e), CC), e), _block(_field(2000 + _idx(e), CH), e)),
@@ -49,7 +50,10 @@ def build(grid, rank, dev, overlap, groups=None, fused=False):
         for k, v in sd.items():
             if v.dtype.is_floating_point and "inv_freq" not in k:
                 v.copy_((torch.randn(v.shape, generator=g) * 0.05).to(v.dtype))
-    eng.opt = type(eng.opt)(eng.module, eng.ocfg)
+    if distopt and hasattr(eng.opt, "reduce_scatter"):
+        eng.opt = type(eng.opt)(eng.module, eng.ocfg, eng.groups["weight"], dev, False)
+    else:
+        eng.opt = type(eng.opt)(eng.module, eng.ocfg)
     if not fused:
         eng.noise_fn = lambda e: _block(_field(3000 + _idx(e), CH), e)
     eng.t_fn = lambda e: torch.tensor([0.2 + 0.13 * (_idx(e) % 9)])
@@ -63,6 +67,7 @@ def main():
     WPX = int(sys.argv[3]) if len(sys.argv) > 3 else 1
     SP = int(sys.argv[4]) if len(sys.argv) > 4 else 1
     fused = bool(int(sys.argv[5])) if len(sys.argv) > 5 else False
+    distopt = bool(int(sys.argv[6])) if len(sys.argv) > 6 else False
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     import datetime
@@ -76,7 +81,7 @@ def main():
         ref_loss.append(float(ref.tot_loss))
     ref_sd = {st: {k: v.clone() for k, v in sd.items()} for st, sd in ref.module.logical_state_dicts().items()}
     del ref
-    eng = build(ProcessGrid(world, PP=PP, WP_X=WPX, SP=SP), rank, dev, overlap, fused=fused)
+    eng = build(ProcessGrid(world, PP=PP, WP_X=WPX, SP=SP), rank, dev, overlap, fused=fused, distopt=distopt)
     loss = []
     for _ in range(iters):
         eng.exec_schedule()

@@ -63,17 +63,18 @@ def test_pipeline_parallel_nccl(overlap):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
 
 
-@pytest.mark.parametrize("n,pp,wpx,sp", [(2, 2, 1, 1), (2, 1, 2, 1)])
-def test_pipeline_engine_with_fused_input_and_loss_kernels(n, pp, wpx, sp):
+@pytest.mark.parametrize("n,pp,wpx,sp,distopt", [(2, 2, 1, 1, 0), (2, 1, 2, 1, 0), (2, 1, 2, 1, 1)])
+def test_pipeline_engine_with_fused_input_and_loss_kernels(n, pp, wpx, sp, distopt):
     """The pipeline engine with its end stages on the fused kernels (noising + position encoding + partition +
     projection; head + TrigFlow loss + gradient) and their counter-based noise, split over pipeline stages or window
-    ranks, against the same engine on one GPU."""
+    ranks, against the same engine on one GPU. ``distopt``: the split run steps with the sharded optimizer on the
+    peer-memory kernels (gradient reduce-scatter + AdamW + weight all-gather)."""
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
     worker = os.path.join(os.path.dirname(__file__), "pp_worker.py")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-                        "--master-addr", "127.0.0.1", "--master-port", str(29590 + pp), worker, "1", str(pp), str(wpx),
-                        str(sp), "1"], capture_output=True, text=True, timeout=300)
+                        "--master-addr", "127.0.0.1", "--master-port", str(29590 + pp + 4 * distopt), worker, "1", str(pp),
+                        str(wpx), str(sp), "1", str(distopt)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
 
 
