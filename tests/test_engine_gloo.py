@@ -154,6 +154,14 @@ def test_pp2_wp2_with_tensor_parallel_mlp_matches_single_process(single):
     assert norm == pytest.approx(single[2], rel=1e-4)
 
 
+def test_sp2_with_tensor_parallel_mlp_over_the_sequence_pair_matches_single_process(single):
+    """SP 2 with the MLP weights split over the sequence-parallel pair (the tensor-parallel group is the SP group)."""
+    sd, loss, norm = _launch(2, PP=1, WP=(1, 1), SP=2, gas=4, iters=2, TP=2)
+    _assert_same(sd, single[0], tol=5e-5)
+    assert loss == pytest.approx(single[1], rel=1e-4)
+    assert norm == pytest.approx(single[2], rel=1e-4)
+
+
 def test_pp3_matches_single_process(single):
     sd, loss, norm = _launch(3, PP=3, WP=(1, 1), gas=4, iters=2)
     _assert_same(sd, single[0])
