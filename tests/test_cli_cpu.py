@@ -116,3 +116,17 @@ def test_train_cli_with_tensor_parallel_mlp(tmp_path):
     out = _run(args + ["trainer.benchmark_steps=6", "model.load=true"], nproc=2, port=29772)
     assert "loaded a checkpoint" in out
     assert len([l for l in out.splitlines() if " loss " in l]) == 2
+
+
+def test_tensor_parallel_with_data_parallel_replicas_matches_replicated_weights():
+    """Four ranks = DP 2 x WP 2 with ``model.TP=2``: every shard is held by two ranks (one per replica), so its
+    gradient is reduced over those two only while the replicated parameters are reduced over all four, with one clipping
+    norm. The loss curve has to equal the run with replicated MLP weights."""
+    args = ["aeris_gb_b200.cli.train", "experiment=tiny_cpu", "model.WP_X=2", "optimizer.lr=0.003",
+            "trainer.lr_rampup_kimg=0", "model.checkpoint_dir=null", "trainer.benchmark_steps=3", "model.grad_clip=true",
+            "model.grad_clip_max_norm=0.05"]
+    curves = []
+    for extra, port in ((["model.TP=2"], 29781), ([], 29782)):
+        out = _run(args + extra, nproc=4, port=port)
+        curves.append([float(l.split("loss ")[1].split()[0]) for l in out.splitlines() if " loss " in l])
+    assert len(curves[0]) == 3 and np.allclose(curves[0], curves[1], rtol=2e-4), curves
