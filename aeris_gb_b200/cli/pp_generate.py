@@ -81,6 +81,7 @@ def main(argv=None):
         cfg = C.compose("train", [f"experiment={a.experiment}"] + list(a.overrides))
     cfg.model.WP_Y, cfg.model.WP_X = a.WP_Y, a.WP_X
     mcfg = C.model_config(cfg)
+    mcfg.tp = 1       # inference holds whole MLP weights; checkpoints store full tensors whatever model.TP trained them
     if device.type == "cpu":
         mcfg.model_dtype = torch.float32
     grid = ProcessGrid(world, PP=a.PP, WP_Y=a.WP_Y, WP_X=a.WP_X)

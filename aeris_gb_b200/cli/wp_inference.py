@@ -69,6 +69,7 @@ def main(argv=None):
     wp = (1, 1) if a.member_parallel else (a.WP_Y, a.WP_X)
     cfg.model.WP_Y, cfg.model.WP_X = wp
     mcfg = C.model_config(cfg)
+    mcfg.tp = 1       # inference holds whole MLP weights; checkpoints store full tensors whatever model.TP trained them
     if device.type == "cpu":
         mcfg.model_dtype = torch.float32
     n_wp = wp[0] * wp[1]

@@ -116,6 +116,11 @@ def test_train_cli_with_tensor_parallel_mlp(tmp_path):
     out = _run(args + ["trainer.benchmark_steps=6", "model.load=true"], nproc=2, port=29772)
     assert "loaded a checkpoint" in out
     assert len([l for l in out.splitlines() if " loss " in l]) == 2
+    # the inference entry point holds whole MLP weights and takes the same files
+    out = _run(["aeris_gb_b200.cli.wp_inference", "--experiment", "tiny_cpu", "--checkpoint", str(tmp_path), "--members",
+                "2", "--rollout-steps", "1", "--sampler-steps", "2", "model.TP=2"])
+    rec = json.loads(out.strip().splitlines()[-1])
+    assert rec["rollout_steps"] == 1
 
 
 def test_tensor_parallel_with_data_parallel_replicas_matches_replicated_weights():
