@@ -162,8 +162,14 @@ def main(argv=None):
                 log0(f"loaded a checkpoint from {ckpt_dir} at {trainer.opt.cur_nimg} images")
         loader = make_loader(trainer.opt.cur_nimg)
         start = trainer.opt.cur_nimg // (gas * grid.DP)
+        # trainer.profile_steps=[first,last): torch.profiler Chrome trace of those iterations, one file per rank
+        from ..utils.timers import StepProfiler
+        ps = cfg.trainer.get("profile_steps")
+        prof = StepProfiler(tuple(int(v) for v in ps) if ps else None,
+                            os.path.join(ckpt_dir or ".", "traces"), rank)
         for it in range(start, total_steps):
             between_steps(it)
+            prof.before_step(it)
             batch = [next(loader) for _ in range(gas)]
             cond = torch.cat([b[0] for b in batch]).pin_memory() if device.type == "cuda" else torch.cat([b[0] for b in batch])
             tgt = torch.cat([b[1] for b in batch]).pin_memory() if device.type == "cuda" else torch.cat([b[1] for b in batch])
@@ -172,6 +178,9 @@ def main(argv=None):
             t0 = time.perf_counter()
             loss = trainer.train_step(tgt, cond, interval=interval)
             dt = time.perf_counter() - t0
+            trace = prof.after_step(it)
+            if trace:
+                log0(f"profiler trace written to {trace}")
             check_finite("loss", loss)
             tf = tflops_per_gpu(mcfg.flops_per_sample(), gas * grid.DP, dt, world)
             slow = watchdog.observe(dt)

@@ -65,6 +65,36 @@ class DeviceTimers:
         return out
 
 
+class StepProfiler:
+    """Optional ``torch.profiler`` capture of a window of training steps, exported as a Chrome trace (one file per
+    rank). ``steps = (first, last)`` are absolute iteration numbers, ``last`` exclusive; ``None`` disables it. The
+    kernels of this library appear under their own names; the NVTX ranges of :class:`DeviceTimers` nest around them."""
+
+    def __init__(self, steps: tuple[int, int] | None, out_dir: str, rank: int = 0):
+        self.steps, self.out_dir, self.rank = steps, out_dir, rank
+        self._prof = None
+        self.path = None
+
+    def before_step(self, it: int) -> None:
+        if self.steps is None or it != self.steps[0]:
+            return
+        from torch.profiler import ProfilerActivity, profile
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+        self._prof = profile(activities=acts, record_shapes=False)
+        self._prof.__enter__()
+
+    def after_step(self, it: int) -> str | None:
+        if self._prof is None or it + 1 < self.steps[1]:
+            return None
+        import os
+        self._prof.__exit__(None, None, None)
+        os.makedirs(self.out_dir, exist_ok=True)
+        self.path = os.path.join(self.out_dir, f"trace_rank{self.rank}_it{self.steps[0]}-{self.steps[1]}.json")
+        self._prof.export_chrome_trace(self.path)
+        self._prof = None
+        return self.path
+
+
 def tflops_per_gpu(flops_per_sample: float, samples: int, seconds: float, world_size: int) -> float:
     """TFLOP/s per GPU in the reference's metric: analytic training FLOPs / step time / ranks (train.py:291)."""
     return flops_per_sample * samples / seconds / 1e12 / world_size

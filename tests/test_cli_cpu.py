@@ -29,6 +29,14 @@ def test_train_cli_loss_goes_down_and_writes_run_config(tmp_path):
     assert (tmp_path / ".hydra" / "config.yaml").exists()
 
 
+def test_train_cli_writes_a_profiler_trace(tmp_path):
+    out = _run(["aeris_gb_b200.cli.train", "experiment=tiny_cpu", "trainer.benchmark_steps=3", "trainer.profile_steps=[1,2]",
+                f"model.checkpoint_dir={tmp_path}"])
+    assert "profiler trace written" in out
+    trace = tmp_path / "traces" / "trace_rank0_it1-2.json"
+    assert trace.exists() and "traceEvents" in trace.read_text()[:2000]
+
+
 def test_wp_inference_cli(tmp_path):
     out = _run(["aeris_gb_b200.cli.wp_inference", "--experiment", "tiny_cpu", "--members", "3", "--rollout-steps", "2",
                 "--sampler-steps", "2", "--random-init", "--out", str(tmp_path)])
