@@ -222,7 +222,10 @@ def model_config(cfg: Config):
         chunk_windows=int(m.get("chunk_windows", 64)), norm_eps=m.get("norm_eps"),
         shift_layers=m.get("shift_mode", "odd"), diffusion=bool(m.get("diffusion", True)),
         rit=bool(m.get("rit", False)), emb_norm=bool(m.get("emb_norm", False)) and bool(m.get("rit", False)),
-        tp=int(m.get("TP", 1)))
+        tp=int(m.get("TP", 1)),
+        # model.act_ckpt: per-block recompute on the PyTorch (CPU / oracle) path; the CUDA blocks always keep only
+        # their input
+        oracle_checkpoint=bool(m.get("act_ckpt", False)))
 
 
 def optim_config(cfg: Config):
