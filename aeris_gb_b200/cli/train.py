@@ -216,6 +216,7 @@ def main(argv=None):
 
         def data_fn(_eng):
             return next(holder["loader"])        # (condition, target[, interval])
+        mcfg.sp = SP
         eng = ParallelEngine(mcfg, ocfg, dcfg, ecfg, grid, rank, device, data_fn=data_fn)
         eng.warmup()
         if cfg.model.get("load"):

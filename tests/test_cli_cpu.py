@@ -143,3 +143,15 @@ def test_tensor_parallel_with_data_parallel_replicas_matches_replicated_weights(
         out = _run(args + extra, nproc=4, port=port)
         curves.append([float(l.split("loss ")[1].split()[0]) for l in out.splitlines() if " loss " in l])
     assert len(curves[0]) == 3 and np.allclose(curves[0], curves[1], rtol=2e-4), curves
+
+
+def test_train_cli_window_sequence_and_tensor_parallel_on_cpu_ranks():
+    """``experiment=b200_1p3b_wp4_sp2`` at toy size on four gloo ranks (WP 2 x SP 2, MLP weights split over each SP
+    pair): on CPU ranks sequence parallelism runs through the pipeline engine with one stage."""
+    out = _run(["aeris_gb_b200.cli.train", "experiment=b200_1p3b_wp4_sp2", "model.TP=2", "model.WP_X=2", "model.WP_Y=1",
+                "data.synthetic=true", "data.gas=2", "trainer.benchmark_steps=2", "model.dim=32", "model.heads=2",
+                "model.head_dim=16", "model.mlp_dim=64", "model.PP_stages=4", "model.window_size=[8,8]",
+                "model.img=[16,32]", "model.checkpoint_dir=null", "model.dtype=float32", "model.channels=6"],
+               nproc=4, port=29792)
+    losses = [float(l.split("loss ")[1].split()[0]) for l in out.splitlines() if " loss " in l]
+    assert len(losses) == 2 and all(0.5 < l < 2.0 for l in losses)
