@@ -103,3 +103,54 @@ def test_same_weights_same_function(name, one_rank_group):
         assert torch.allclose(p.grad, gr, atol=5e-5, rtol=2e-3), (k, (p.grad - gr).abs().max())
         checked += 1
     assert checked >= 10
+
+
+def test_reference_arm_harness_computes_the_objective_of_the_trainer(one_rank_group):
+    """The glue that ``bench.py --impl reference`` puts around the reference's modules (window partition, position
+    encoding, noising, latitude and variable weights, loss normalisation) against this package's trainer: same
+    weights, same sample, same noise level and noise field give the same training loss."""
+    from aeris_gb_b200.engine.optim import OptimConfig
+    from aeris_gb_b200.engine.trainer import DiffusionConfig, Trainer
+    from aeris_gb_b200.models.aeris import AerisConfig
+    C_C = C_IN - C_OUT
+    dims = dict(img=(H, W), window=WS, dim=D, heads=2, head_dim=16, mlp_dim=48, n_layers=3, in_ch=C_IN, out_ch=C_OUT,
+                chunk_windows=3)
+    ref = HN.ReferenceTrainer(dims, "cpu", group=None, seed=3)
+    for mod in [ref.inp, *ref.layers, ref.out]:                 # away from the zero / one initial values
+        for n, p in mod.named_parameters():
+            with torch.no_grad():
+                p.copy_(torch.randn(p.shape).to(p.dtype) * 0.05 + (1.0 if (p.dim() == 1 and "bias" not in n) else 0.0))
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(1, H, W, C_OUT, generator=g)
+    c = torch.randn(1, H, W, C_C, generator=g)
+    t = torch.tensor([[0.9]])
+    lay = ref.lay
+    z_tok = torch.randn(lay.nw, lay.L, C_OUT, generator=g)      # noise in the harness's token order
+    ref._noise = lambda _x: (t, z_tok)
+    # this package, with the weights the harness holds BEFORE its step
+    cfg = AerisConfig(img=(H, W), window=WS, in_channels=C_IN, out_channels=C_OUT, dim=D, heads=2, head_dim=16, mlp_dim=48,
+                      n_layers=3, sublayers=1, layerwise_t_emb=True, after_mod_norm=True, model_dtype=torch.bfloat16,
+                      ape_row_offset=1)
+    ours = Trainer(cfg, OptimConfig(), DiffusionConfig(cond_channels=C_C), "cpu")
+    # the harness builds position encoding and latitude weights on H + 1 rows and drops the first, which is what both
+    # sides do on the 720-row grid; on this toy grid the trainer is told to do the same
+    from aeris_gb_b200.diffusion import trigflow as TF
+    from aeris_gb_b200.models import layout as LY
+    wl = TF.latitude_weights(H, 0.01, drop_first_row=True).view(1, -1, 1, 1).expand(1, H, W, 1)
+    ours._w_lat_tok = LY.image_to_tokens(wl, ours.grid, (0, 0), 0)
+    sd = {f"input_stage.{k}": v for k, v in ref.inp.state_dict().items()}
+    for i, l in enumerate(ref.layers):
+        sd.update({f"layers.{i}.{k}": v for k, v in l.state_dict().items()})
+    sd.update({f"output_stage.{k}": v for k, v in ref.out.state_dict().items()})
+    own = ours.model.state_dict()
+    with torch.no_grad():
+        for k, v in sd.items():
+            if k in own:
+                own[k].copy_(v.to(own[k].dtype))
+    z_img = torch.empty(H * W, C_OUT)
+    z_img[lay.pixel_of] = z_tok.reshape(-1, C_OUT)
+    z_img = z_img.view(1, H, W, C_OUT)
+    with torch.no_grad():
+        mine = ours.loss_tokens(ours.block_to_tokens(x), ours.block_to_tokens(c), t.view(1), ours.block_to_tokens(z_img))
+    theirs = ref.train_step(x, c)
+    assert abs(float(mine) - theirs) <= 5e-3 * abs(theirs), (float(mine), theirs)      # bf16 blocks on both sides
