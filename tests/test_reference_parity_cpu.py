@@ -154,3 +154,29 @@ def test_reference_arm_harness_computes_the_objective_of_the_trainer(one_rank_gr
         mine = ours.loss_tokens(ours.block_to_tokens(x), ours.block_to_tokens(c), t.view(1), ours.block_to_tokens(z_img))
     theirs = ref.train_step(x, c)
     assert abs(float(mine) - theirs) <= 5e-3 * abs(theirs), (float(mine), theirs)      # bf16 blocks on both sides
+
+
+def test_reference_inference_arm_evaluates_the_same_network(one_rank_group):
+    """The inference arm of the reference comparison (the stages of the reference's ``LocalAERIS`` with the one-rank
+    shift of the harness) against this package's model with the same weights: one network evaluation."""
+    from aeris_gb_b200.models.aeris import AerisConfig, AerisModel
+    dims = dict(img=(H, W), window=WS, dim=D, heads=2, head_dim=16, mlp_dim=48, n_layers=3, in_ch=C_IN, out_ch=C_OUT)
+    ref = HN.ReferenceForecaster(dims, "cpu", sampler_steps=2)
+    with torch.no_grad():
+        for n, p in ref.model.named_parameters():
+            p.copy_(torch.randn(p.shape).to(p.dtype) * 0.05 + (1.0 if (p.dim() == 1 and "bias" not in n) else 0.0))
+    dtype = next(ref.model.layers.parameters()).dtype
+    cfg = AerisConfig(img=(H, W), window=WS, in_channels=C_IN, out_channels=C_OUT, dim=D, heads=2, head_dim=16, mlp_dim=48,
+                      n_layers=3, sublayers=1, layerwise_t_emb=True, after_mod_norm=True, model_dtype=dtype,
+                      ape_row_offset=1)
+    ours = AerisModel(cfg)
+    missing, unexpected = ours.load_state_dict(ref.model.state_dict(), strict=False)
+    assert not [m for m in missing if "1.norm" not in m and "latent_embed" not in m], missing
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(1, H, W, C_IN, generator=g)
+    s = torch.tensor([0.8])
+    y_ref = ref.model_eval(x.view(1, H * W, C_IN), s).float().view(H, W, C_OUT)
+    with torch.no_grad():
+        y = ours(x, s)[0]
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    assert (y - y_ref).norm() <= tol * y_ref.norm(), ((y - y_ref).norm() / y_ref.norm(), dtype)
