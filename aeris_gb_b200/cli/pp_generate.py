@@ -195,6 +195,10 @@ def main(argv=None):
     agg, scores = metrics.finalize()
     if writer is not None:
         writer.close()
+    if C_out in (69, 70):       # the named channel sets: scores of the nine headline variables (pp_generate.py:500-526)
+        from ..data.era5 import variable_names
+        print0("RMSE first member, RMSE ensemble mean, CRPS, spread/skill\n"
+               + metrics.headline_table(variable_names(73)[:C_out], interval=int(cfg.model.get("interval", 6))))
     if a.out and rank == 0:
         os.makedirs(a.out, exist_ok=True)
         np.save(os.path.join(a.out, "pp_rollout_err_aggregate.npy"), agg)

@@ -191,6 +191,10 @@ def main(argv=None):
     agg, scores = metrics.finalize()
     if writer is not None:
         writer.close()
+    if mcfg.out_channels in (69, 70):   # the named channel sets: scores of the nine headline variables
+        from ..data.era5 import variable_names
+        print0("RMSE first member, RMSE ensemble mean, CRPS, spread/skill\n"
+               + metrics.headline_table(variable_names(73)[:mcfg.out_channels], interval=int(cfg.model.get("interval", 6))))
     per_step = float(np.mean(np.diff(times))) if len(times) > 1 else float("nan")
     if a.out and rank == 0:
         os.makedirs(a.out, exist_ok=True)

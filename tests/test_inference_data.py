@@ -106,6 +106,8 @@ def test_wp_inference_cli_reads_the_file_and_writes_the_rollout(tmp_path):
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-3000:]
     rec = json.loads(r.stdout.strip().splitlines()[-1])
     assert rec["rollout_steps"] == 2
+    # the table of the nine headline variables (first-member RMSE, ensemble-mean RMSE, CRPS, spread/skill per lead time)
+    assert "6h" in r.stdout and "12h" in r.stdout and r.stdout.count(" z500:") == 2 and " t2m:" in r.stdout
     files = [f for f in os.listdir(out) if f.startswith("rollout-")]
     assert len(files) == 1
     roll = np.load(out / files[0])
