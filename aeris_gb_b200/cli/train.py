@@ -28,7 +28,7 @@ from ..utils import config as C
 from ..utils.dist_setup import setup, teardown
 from ..utils.fault import FaultInjector, Heartbeat, StepWatchdog, check_finite
 from ..utils.io import log0
-from ..utils.timers import tflops_per_gpu, wandb_payload
+from ..utils.timers import memory_report, tflops_per_gpu, wandb_payload
 
 
 def build_dataset(cfg, mcfg, wp_rank, channels):
@@ -185,7 +185,8 @@ def main(argv=None):
             tf = tflops_per_gpu(mcfg.flops_per_sample(), gas * grid.DP, dt, world)
             slow = watchdog.observe(dt)
             log0(f"it {it} loss {loss:.5f} |g| {trainer.grad_norm():.4f} {dt:.3f} s/it {tf:.1f} TFLOP/s/GPU"
-                 + (" SLOW STEP" if slow else ""))
+                 + (" SLOW STEP" if slow else "")
+                 + ((" " + memory_report(device)) if cfg.model.get("benchmark") else ""))
             phase = trainer.timers.resolve() if trainer.timers.enabled else None
             if phase:
                 log0("   device ms: " + str({k: round(v, 1) for k, v in phase.items()}))
@@ -230,8 +231,8 @@ def main(argv=None):
             tf = tflops_per_gpu(mcfg.flops_per_sample(), gas * grid.DP, dt, world)
             if eng.is_last_stage() and c.dp == 0 and c.wp_y == 0 and c.wp_x == 0 and c.sp == 0:
                 check_finite("loss", eng.tot_loss)
-                print(f"it {it} loss {eng.tot_loss:.5f} |g| {eng.total_norm:.4f} {dt:.3f} s/it {tf:.1f} TFLOP/s/GPU",
-                      flush=True)
+                print(f"it {it} loss {eng.tot_loss:.5f} |g| {eng.total_norm:.4f} {dt:.3f} s/it {tf:.1f} TFLOP/s/GPU"
+                      + ((" " + memory_report(device)) if cfg.model.get("benchmark") else ""), flush=True)
             report = bool(cfg.trainer.get("report_timings"))
             if report and rank in grid.stage_heads():
                 print(c.pp, "times:", {k: round(v, 4) for k, v in timers.items()}, flush=True)
@@ -248,6 +249,8 @@ def main(argv=None):
                 wandb.log(payload, step=it)
     if heart is not None:
         heart.mark_leaving()
+    if cfg.trainer.get("sleep_after_done"):     # keeps the job's allocation alive after the last step (train.py:350-351)
+        time.sleep(100000)
     teardown()
 
 

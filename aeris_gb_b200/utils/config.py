@@ -25,7 +25,7 @@ CONFIG_ROOT = Path(__file__).resolve().parent.parent.parent / "configs"
 UNREAD_KEYS = {
     "dry_run", "model.emb_init", "model.weight_init", "model.custom_decay2",
     "model.custom_decay3", "model.custom_decay4", "model.custom_decay6", "model.custom_high_wd", "model.P_mean",
-    "model.P_std", "model.emb_norm", "model.shift_size", "model.patch_size", "model.depth", "model.fp32_modulation",
+    "model.P_std", "model.shift_size", "model.patch_size", "model.depth", "model.fp32_modulation",
     "data.res_fix",
 }
 

@@ -95,6 +95,15 @@ class StepProfiler:
         return self.path
 
 
+def memory_report(device) -> str:
+    """Peak allocated and reserved device memory in GB, as the reference prints in benchmark mode (train.py:293-299,
+    where the reserved figure is mislabelled)."""
+    if torch.device(device).type != "cuda":
+        return ""
+    return (f"alloc: {torch.cuda.max_memory_allocated(device) / 2 ** 30:.1f}GB, "
+            f"res: {torch.cuda.max_memory_reserved(device) / 2 ** 30:.1f}GB")
+
+
 def tflops_per_gpu(flops_per_sample: float, samples: int, seconds: float, world_size: int) -> float:
     """TFLOP/s per GPU in the reference's metric: analytic training FLOPs / step time / ranks (train.py:291)."""
     return flops_per_sample * samples / seconds / 1e12 / world_size
@@ -105,6 +114,13 @@ def wandb_payload(it: int, nimg: int, tflops: float, dt_iter: float, loss: float
                   timers: dict | None = None, pp_rank: int = 0) -> dict:
     """Metric names as the reference logs them to wandb (train.py:311-348)."""
     d = {"train/iter": it, "train/nimg": nimg, "train/tflops_s_tile": tflops, "train/dt/iter": dt_iter}
+    try:                                   # resident host memory of this process in GiB (train.py:316)
+        import os
+
+        import psutil
+        d["train/mem/cpu"] = psutil.Process(os.getpid()).memory_info().rss / 2 ** 30
+    except Exception:
+        pass
     if loss is not None:
         d["train/loss"] = loss
     if total_norm is not None:
