@@ -43,17 +43,25 @@ def parse(argv=None):
     ap.add_argument("--WP-Y", type=int, default=1)
     ap.add_argument("--WP-X", type=int, default=1)
     ap.add_argument("--members", type=int, default=2)
-    ap.add_argument("--rollout-steps", type=int, default=2)
-    ap.add_argument("--sampler-steps", type=int, default=20)
-    ap.add_argument("--S-churn", type=float, default=0.0)
-    ap.add_argument("--S-min", type=float, default=0.0)
-    ap.add_argument("--S-max", type=float, default=float("inf"))
-    ap.add_argument("--S-noise", type=float, default=1.0)
+    # the second spelling of an option is the reference's (pp_generate.py:28-53)
+    ap.add_argument("--rollout-steps", "--steps", dest="rollout_steps", type=int, default=2)
+    ap.add_argument("--sampler-steps", "--diffusion-steps", dest="sampler_steps", type=int, default=20)
+    ap.add_argument("--S-churn", "--S_churn", dest="S_churn", type=float, default=0.0)
+    ap.add_argument("--S-min", "--S_min", dest="S_min", type=float, default=0.0)
+    ap.add_argument("--S-max", "--S_max", dest="S_max", type=float, default=float("inf"))
+    ap.add_argument("--S-noise", "--S_noise", dest="S_noise", type=float, default=1.0)
+    ap.add_argument("--sigma_max", "--sigma-max", dest="sigma_max", type=float, default=-1.0,
+                    help="largest noise level of the sampler (-1: the model's)")
+    ap.add_argument("--sigma_min", "--sigma-min", dest="sigma_min", type=float, default=-1.0)
+    ap.add_argument("--start-sample", type=int, default=-1, help="first initial condition of the file (-1: the first)")
+    ap.add_argument("--end-sample", type=int, default=-1, help="last initial condition (-1: as many as fit)")
+    ap.add_argument("--clamp-sst", action="store_true",
+                    help="accepted: land points of the sea-surface temperature are always filled before standardising")
     ap.add_argument("--euler", action="store_true")
-    ap.add_argument("--load-ema", action="store_true", help="take the EMA weights of the checkpoint (default: the model weights)")
+    ap.add_argument("--load-ema", "--use-ema", dest="load_ema", action="store_true", help="take the EMA weights of the checkpoint (default: the model weights)")
     ap.add_argument("--data", default=None, help="monolithic test file [T, 73, 721, 1440]")
     ap.add_argument("--data-root", default=None, help="folder with the normalize_*.npz statistics")
-    ap.add_argument("--stride-ic", type=int, default=1)
+    ap.add_argument("--stride-ic", "--stride", dest="stride_ic", type=int, default=1)
     ap.add_argument("--out", default=None)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("overrides", nargs="*")
@@ -120,7 +128,8 @@ def main(argv=None):
                              interval=int(cfg.model.get("interval", 6)), rollout_steps=a.rollout_steps,
                              out_channels=C_out, channels=73 if C_f > 0 else 69)
         stats = data.stats(device)
-        all_ic, my_ic = strided_indices(data.ds.ds.shape[0], a.rollout_steps, data.dt, a.stride_ic, c.dp, grid.DP)
+        all_ic, my_ic = strided_indices(data.ds.ds.shape[0], a.rollout_steps, data.dt, a.stride_ic, c.dp, grid.DP,
+                                        start=max(a.start_sample, 0), end=None if a.end_sample < 0 else a.end_sample)
         if a.out and head:
             stem = f"output-{len(all_ic)}i-{a.rollout_steps}s-{a.members}m-{a.sampler_steps}ds" + \
                 (f"_dp{c.dp}" if grid.DP > 1 else "")
@@ -129,7 +138,8 @@ def main(argv=None):
         stats = {k: torch.zeros(C_out, device=device) if "mean" in k else torch.ones(C_out, device=device)
                  for k in ("x_mean", "x_std", "t_mean", "t_std")}
         my_ic = [0]
-    ts = TF.sampler_schedule(a.sampler_steps, dcfg.sigma_min, dcfg.sigma_max, sd, device=device)
+    ts = TF.sampler_schedule(a.sampler_steps, dcfg.sigma_min if a.sigma_min < 0 else a.sigma_min,
+                             dcfg.sigma_max if a.sigma_max < 0 else a.sigma_max, sd, device=device)
     metrics = EnsembleMetrics(a.rollout_steps, C_out, H * W, device, group=eng.groups.get("wp"))
     w_lat = TF.latitude_weights(H, dcfg.w_lat_add)
     w_tok = LY.image_to_tokens(w_lat.view(1, -1, 1, 1).expand(1, H, W, 1), g, (0, 0), eng.wp_rank)

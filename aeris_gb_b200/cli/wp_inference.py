@@ -44,9 +44,21 @@ def parse(argv=None):
     ap.add_argument("--WP-X", type=int, default=1)
     ap.add_argument("--member-parallel", action="store_true")
     ap.add_argument("--members", type=int, default=1)
-    ap.add_argument("--rollout-steps", type=int, default=None)
-    ap.add_argument("--sampler-steps", type=int, default=None)
-    ap.add_argument("--stride-ic", type=int, default=1)
+    # the second spelling of an option is the reference's (aeris_wp_inference/inference.py:24-41)
+    ap.add_argument("--rollout-steps", "--steps", dest="rollout_steps", type=int, default=None)
+    ap.add_argument("--sampler-steps", "--diffusion-steps", dest="sampler_steps", type=int, default=None)
+    ap.add_argument("--stride-ic", "--stride", dest="stride_ic", type=int, default=1)
+    ap.add_argument("--start-sample", type=int, default=-1, help="first initial condition of the file (-1: the first)")
+    ap.add_argument("--end-sample", type=int, default=-1, help="last initial condition (-1: as many as fit)")
+    ap.add_argument("--sequence-parallel", type=int, default=None,
+                    help="accepted: the reference wants WP_Y x WP_X here; the window-parallel grid alone decides")
+    ap.add_argument("--S_churn", "--S-churn", dest="S_churn", type=float, default=0.0)
+    ap.add_argument("--S_min", "--S-min", dest="S_min", type=float, default=0.0)
+    ap.add_argument("--S_max", "--S-max", dest="S_max", type=float, default=float("inf"))
+    ap.add_argument("--S_noise", "--S-noise", dest="S_noise", type=float, default=1.0)
+    ap.add_argument("--sigma_max", "--sigma-max", dest="sigma_max", type=float, default=-1.0,
+                    help="largest noise level of the sampler (-1: the model's)")
+    ap.add_argument("--sigma_min", "--sigma-min", dest="sigma_min", type=float, default=-1.0)
     ap.add_argument("--data", default=None, help="monolithic test file [T, 73, 721, 1440]")
     ap.add_argument("--data-root", default=None)
     ap.add_argument("--out", default=None)
@@ -94,8 +106,10 @@ def main(argv=None):
     C_f = mcfg.in_channels - 2 * C_out
     steps = a.rollout_steps or int(cfg.model.get("rollout_steps", 4))
     sampler = SamplerConfig(n_steps=a.sampler_steps or int(cfg.model.get("sampler_steps", 20)),
-                            sigma_min=cfg.model.sigma_min, sigma_max=cfg.model.sigma_max,
-                            sigma_data=cfg.model.sigma_data, heun=not a.euler)
+                            sigma_min=cfg.model.sigma_min if a.sigma_min < 0 else a.sigma_min,
+                            sigma_max=cfg.model.sigma_max if a.sigma_max < 0 else a.sigma_max,
+                            sigma_data=cfg.model.sigma_data, heun=not a.euler, s_churn=a.S_churn, s_min=a.S_min,
+                            s_max=a.S_max, s_noise=a.S_noise)
     # members handled by this rank: all of them when window-parallel, a strided subset when member-parallel
     my_members = list(range(dp_rank, a.members, dp)) if a.member_parallel else list(range(a.members))
     M = len(my_members)
@@ -120,7 +134,8 @@ def main(argv=None):
         stats = data.stats(device)
         # window-parallel: the replicas share the initial conditions out; member-parallel: every rank sees all of them
         all_ic, my_ic = strided_indices(data.ds.ds.shape[0], steps, data.dt, a.stride_ic,
-                                        0 if a.member_parallel else dp_rank, 1 if a.member_parallel else dp)
+                                        0 if a.member_parallel else dp_rank, 1 if a.member_parallel else dp,
+                                        start=max(a.start_sample, 0), end=None if a.end_sample < 0 else a.end_sample)
     else:
         stats = {k: torch.zeros(C_out, device=device) if "mean" in k else torch.ones(C_out, device=device)
                  for k in ("x_mean", "x_std", "t_mean", "t_std")}

@@ -26,6 +26,7 @@ class SamplerConfig:
     s_churn: float = 0.0
     s_min: float = 0.0
     s_max: float = float("inf")
+    s_noise: float = 1.0            # scale of the fresh noise that the churn mixes in
 
 
 class Forecaster:
@@ -52,7 +53,7 @@ class Forecaster:
         s = self.s
         y = TF.sample(self.denoise, cond, state.shape, s.n_steps, s.sigma_min, s.sigma_max, s.sigma_data, s.rho,
                       heun=s.heun, generator=generator, s_churn=s.s_churn, s_min=s.s_min, s_max=s.s_max,
-                      x_init=x_init)
+                      x_init=x_init, s_noise=s.s_noise)
         return state + self.unstd_t(y)
 
     @torch.no_grad()
@@ -122,7 +123,7 @@ class DeviceForecaster(Forecaster):
                 gamma = min(s.s_churn / s.n_steps, math.sqrt(2) - 1)
                 hat = math.atan(math.tan(cur) * (1 + gamma))
                 rot = math.atan(max(math.tan(hat) - math.tan(cur), 0.0))
-                DF.noise_mix(x, math.cos(rot), math.sin(rot) * s.sigma_data, self._next_seed(), geom)
+                DF.noise_mix(x, math.cos(rot), math.sin(rot) * s.sigma_data * s.s_noise, self._next_seed(), geom)
                 cur = hat
             d = (nxt - cur) * s.sigma_data
             f_s = self.model.predict_images(x, c_img, level(cur), self.ctx, plan)

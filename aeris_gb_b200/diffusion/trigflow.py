@@ -90,22 +90,23 @@ def sampler_schedule(n_steps: int, sigma_min: float, sigma_max: float, sigma_dat
     return torch.cat([t, torch.zeros(1, dtype=t.dtype, device=device)]).float()
 
 
-def churn_form2(x_t: torch.Tensor, s_cur: float, gamma: float, sigma_data: float, generator=None):
+def churn_form2(x_t: torch.Tensor, s_cur: float, gamma: float, sigma_data: float, generator=None,
+                s_noise: float = 1.0):
     """Raise the noise level from s_cur to s_hat = atan(tan(s_cur) * (1 + gamma)) by rotating x_t toward fresh noise
     (pp_generate.py:228-241, 'form 2'): s_l = atan(tan s_hat - tan s_cur), x <- cos(s_l) x + sin(s_l) sigma_d eps,
-    a pure rotation in the (signal, noise) plane."""
+    a pure rotation in the (signal, noise) plane; ``s_noise`` scales the fresh noise (the reference's ``S_noise``)."""
     if gamma <= 0:
         return x_t, s_cur
     s_hat = math.atan(math.tan(s_cur) * (1 + gamma))
     s_l = math.atan(max(math.tan(s_hat) - math.tan(s_cur), 0.0))
     eps = torch.randn(x_t.shape, generator=generator, device=x_t.device, dtype=x_t.dtype) * sigma_data
-    return math.cos(s_l) * x_t + math.sin(s_l) * eps, s_hat
+    return math.cos(s_l) * x_t + math.sin(s_l) * s_noise * eps, s_hat
 
 
 @torch.no_grad()
 def sample(denoise, cond: torch.Tensor, shape, n_steps: int, sigma_min: float, sigma_max: float, sigma_data: float,
            rho: float = 10.0, heun: bool = True, generator=None, s_churn: float = 0.0, s_min: float = 0.0,
-           s_max: float = float("inf"), x_init: torch.Tensor | None = None) -> torch.Tensor:
+           s_max: float = float("inf"), x_init: torch.Tensor | None = None, s_noise: float = 1.0) -> torch.Tensor:
     """Deterministic TrigFlow sampler: Euler steps with a 2nd-order Heun correction on all but the last step
     (pp_generate.py:298-322). ``denoise(model_in [B,...,C+Cc], t [B]) -> F`` is the network.
     Returns the sample at t = 0 (same shape as ``shape``)."""
@@ -117,7 +118,7 @@ def sample(denoise, cond: torch.Tensor, shape, n_steps: int, sigma_min: float, s
         s, tn = float(ts[i]), float(ts[i + 1])
         if s_churn > 0:
             gamma = min(s_churn / n_steps, math.sqrt(2) - 1) if s_min <= math.tan(s) * sigma_data <= s_max else 0.0
-            x, s = churn_form2(x, s, gamma, sigma_data, generator)
+            x, s = churn_form2(x, s, gamma, sigma_data, generator, s_noise)
         d = tn - s
         f_s = denoise(torch.cat([x / sigma_data, cond], dim=-1), torch.full((B,), s, device=device))
         x_e = x + d * sigma_data * f_s

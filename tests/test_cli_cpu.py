@@ -155,3 +155,19 @@ def test_train_cli_window_sequence_and_tensor_parallel_on_cpu_ranks():
                nproc=4, port=29792)
     losses = [float(l.split("loss ")[1].split()[0]) for l in out.splitlines() if " loss " in l]
     assert len(losses) == 2 and all(0.5 < l < 2.0 for l in losses)
+
+
+def test_inference_clis_take_the_references_option_spellings():
+    """`--steps`, `--diffusion-steps`, `--stride`, `--use-ema`, `--S_churn` ... are accepted as the reference spells them
+    (pp_generate.py:28-53, aeris_wp_inference/inference.py:24-41), next to this package's own spellings."""
+    out = _run(["aeris_gb_b200.cli.wp_inference", "--experiment", "tiny_cpu", "--members", "2", "--steps", "1",
+                "--diffusion-steps", "2", "--stride", "5", "--S_churn", "0.5", "--S_min", "0", "--S_max", "100",
+                "--S_noise", "1.003", "--sigma_max", "80", "--sigma_min", "0.3", "--sequence-parallel", "1",
+                "--random-init"])
+    rec = json.loads(out.strip().splitlines()[-1])
+    assert rec["rollout_steps"] == 1 and rec["sampler_steps"] == 2
+    out = _run(["aeris_gb_b200.cli.pp_generate", "--experiment", "tiny_cpu", "--PP", "1", "--members", "2", "--steps", "1",
+                "--diffusion-steps", "2", "--S_churn", "0.5", "--S_noise", "1.003", "--sigma_max", "80", "--use-ema",
+                "--clamp-sst", "--start-sample", "0", "--end-sample", "3"])
+    rec = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
+    assert rec["rollout_steps"] == 1 and rec["ema"] is True and rec["S_churn"] == 0.5
