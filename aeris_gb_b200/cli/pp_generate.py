@@ -55,6 +55,8 @@ def parse(argv=None):
     ap.add_argument("--sigma_min", "--sigma-min", dest="sigma_min", type=float, default=-1.0)
     ap.add_argument("--start-sample", type=int, default=-1, help="first initial condition of the file (-1: the first)")
     ap.add_argument("--end-sample", type=int, default=-1, help="last initial condition (-1: as many as fit)")
+    ap.add_argument("--extra-name", default="", help="text in front of the checkpoint file names, e.g. it_5000_")
+    ap.add_argument("--extra-outname", default="", help="text appended to the name of the rollout files")
     ap.add_argument("--clamp-sst", action="store_true",
                     help="accepted: land points of the sea-surface temperature are always filled before standardising")
     ap.add_argument("--euler", action="store_true")
@@ -99,7 +101,7 @@ def main(argv=None):
     eng = InferenceEngine(mcfg, ocfg, dcfg, ecfg, grid, rank, device, members=a.members,
                           groups={} if world == 1 else None)
     if a.checkpoint:
-        assert eng.load_checkpoint(load_ema=a.load_ema), f"no usable checkpoint in {a.checkpoint}"
+        assert eng.load_checkpoint(load_ema=a.load_ema, prefix=a.extra_name), f"no usable checkpoint in {a.checkpoint}"
     c = eng.c
     g = eng.ctx.grid
     C_out, C_in = mcfg.out_channels, mcfg.in_channels
@@ -131,7 +133,7 @@ def main(argv=None):
         all_ic, my_ic = strided_indices(data.ds.ds.shape[0], a.rollout_steps, data.dt, a.stride_ic, c.dp, grid.DP,
                                         start=max(a.start_sample, 0), end=None if a.end_sample < 0 else a.end_sample)
         if a.out and head:
-            stem = f"output-{len(all_ic)}i-{a.rollout_steps}s-{a.members}m-{a.sampler_steps}ds" + \
+            stem = f"output-{len(all_ic)}i-{a.rollout_steps}s-{a.members}m-{a.sampler_steps}ds{a.extra_outname}" + \
                 (f"_dp{c.dp}" if grid.DP > 1 else "")
             writer = RolloutWriter(a.out, stem, (c.wp_y, c.wp_x), len(my_ic), a.rollout_steps, a.members, C_out, hb, wb)
     else:

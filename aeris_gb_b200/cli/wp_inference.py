@@ -50,6 +50,7 @@ def parse(argv=None):
     ap.add_argument("--stride-ic", "--stride", dest="stride_ic", type=int, default=1)
     ap.add_argument("--start-sample", type=int, default=-1, help="first initial condition of the file (-1: the first)")
     ap.add_argument("--end-sample", type=int, default=-1, help="last initial condition (-1: as many as fit)")
+    ap.add_argument("--extra-name", default="", help="text in front of the checkpoint file names, e.g. it_5000_")
     ap.add_argument("--sequence-parallel", type=int, default=None,
                     help="accepted: the reference wants WP_Y x WP_X here; the window-parallel grid alone decides")
     ap.add_argument("--S_churn", "--S-churn", dest="S_churn", type=float, default=0.0)
@@ -97,7 +98,8 @@ def main(argv=None):
     torch.manual_seed(a.seed)
     model = AerisModel(mcfg).to(device).eval()
     if a.checkpoint and not a.random_init:
-        convert_inference_checkpoint(a.checkpoint, mcfg.n_layers + 2, model, use_ema=not a.no_ema, strict=False)
+        convert_inference_checkpoint(a.checkpoint, mcfg.n_layers + 2, model, use_ema=not a.no_ema, strict=False,
+                                     prefix=a.extra_name)
     halo = HaloExchange(wp_group, device) if (n_wp > 1 and device.type == "cuda") else None
     grid = mcfg.grid()
     H, W = mcfg.img

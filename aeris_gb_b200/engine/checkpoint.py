@@ -23,8 +23,10 @@ import os
 import torch
 
 
-def _fname(directory, stage: int, it: int | None = None) -> str:
-    name = f"checkpoint_PP{stage}.pth" if it is None else f"it_{it}_checkpoint_PP{stage}.pth"
+def _fname(directory, stage: int, it: int | None = None, prefix: str = "") -> str:
+    """``prefix``: text in front of the file name, e.g. ``it_5000_`` for a numbered copy (the reference's
+    ``--extra-name``, sp_inference_engine.py:552-560)."""
+    name = f"{prefix}checkpoint_PP{stage}.pth" if it is None else f"it_{it}_checkpoint_PP{stage}.pth"
     return os.path.join(directory, name)
 
 
@@ -218,7 +220,8 @@ def load_stage_checkpoint(directory: str | None, module, opt, device) -> bool:
     return True
 
 
-def load_stage_weights(directory: str, module, use_ema: bool = True, tp: int = 1, tp_rank: int = 0) -> bool:
+def load_stage_weights(directory: str, module, use_ema: bool = True, tp: int = 1, tp_rank: int = 0,
+                       prefix: str = "") -> bool:
     """Inference: only the weights of the module's logical stages, from ``ema_state_dict`` (or ``model_state_dict``),
     as the reference's inference engine does (src/aeris/parallelism/sp_inference_engine.py:552-573). ``tp`` /
     ``tp_rank``: the module holds tensor-parallel shards of the stored full MLP weights."""
@@ -226,7 +229,7 @@ def load_stage_weights(directory: str, module, use_ema: bool = True, tp: int = 1
     new = {}
     try:
         for stage in _stage_ids(module):
-            ck = torch.load(_fname(directory, stage), map_location="cpu", weights_only=True)
+            ck = torch.load(_fname(directory, stage, prefix=prefix), map_location="cpu", weights_only=True)
             for k, t in (ck[which] if which in ck else ck["model_state_dict"]).items():
                 new[_key_for(module, stage, k)] = t
     except Exception as e:
@@ -245,7 +248,7 @@ def load_stage_weights(directory: str, module, use_ema: bool = True, tp: int = 1
 
 
 def convert_inference_checkpoint(path: str, n_logical: int, model, map_location="cpu", use_ema: bool = True,
-                                 strict: bool = True) -> dict:
+                                 strict: bool = True, prefix: str = "") -> dict:
     """Per-stage files -> one state dict for :class:`AerisModel`, then ``model.load_state_dict``. Takes
     ``ema_state_dict`` (or ``model_state_dict``). Keys the monolithic model does not have are skipped (the reference
     drops ``latent_embed*`` and ``*.1.norm*`` the same way, model.py:483,488)."""
@@ -253,7 +256,7 @@ def convert_inference_checkpoint(path: str, n_logical: int, model, map_location=
     own = model.state_dict()
     new = {}
     for stage in range(n_logical):
-        ck = torch.load(_fname(path, stage), map_location=map_location, weights_only=True)
+        ck = torch.load(_fname(path, stage, prefix=prefix), map_location=map_location, weights_only=True)
         sd = ck[which] if which in ck else ck["model_state_dict"]
         for k, t in sd.items():
             if stage == 0:

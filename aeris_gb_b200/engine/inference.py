@@ -37,10 +37,11 @@ class InferenceEngine(ParallelEngine):
             self.links.peer["result"] = self.last_rank if self.is_first_stage() else self.first_rank
         self._imap.update({SCH.SendResult: self.send_result, SCH.ReturnResult: self.return_result})
 
-    def load_checkpoint(self, load_ema: bool = True) -> bool:
-        """Weights only, the EMA copy by default (sp_inference_engine.py:552-573)."""
+    def load_checkpoint(self, load_ema: bool = True, prefix: str = "") -> bool:
+        """Weights only, the EMA copy by default (sp_inference_engine.py:552-573). ``prefix``: in front of the file
+        names, e.g. ``it_5000_`` for a numbered copy."""
         from .checkpoint import load_stage_weights
-        ok = load_stage_weights(self.ecfg.checkpoint_dir, self.module, use_ema=load_ema)
+        ok = load_stage_weights(self.ecfg.checkpoint_dir, self.module, use_ema=load_ema, prefix=prefix)
         if dist.is_initialized():
             dist.barrier()
         return ok

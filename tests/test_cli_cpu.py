@@ -129,6 +129,13 @@ def test_train_cli_with_tensor_parallel_mlp(tmp_path):
                 "2", "--rollout-steps", "1", "--sampler-steps", "2", "model.TP=2"])
     rec = json.loads(out.strip().splitlines()[-1])
     assert rec["rollout_steps"] == 1
+    # a numbered copy is addressed by the text in front of its file names (--extra-name)
+    for f in list(os.listdir(tmp_path)):
+        if f.startswith("checkpoint_PP"):
+            os.rename(tmp_path / f, tmp_path / ("it_7_" + f))
+    out = _run(["aeris_gb_b200.cli.wp_inference", "--experiment", "tiny_cpu", "--checkpoint", str(tmp_path), "--members",
+                "1", "--steps", "1", "--diffusion-steps", "2", "--extra-name", "it_7_"])
+    assert json.loads(out.strip().splitlines()[-1])["rollout_steps"] == 1
 
 
 def test_tensor_parallel_with_data_parallel_replicas_matches_replicated_weights():
