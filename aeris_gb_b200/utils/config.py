@@ -27,6 +27,11 @@ UNREAD_KEYS = {
     "model.custom_decay3", "model.custom_decay4", "model.custom_decay6", "model.custom_high_wd", "model.P_mean",
     "model.P_std", "model.shift_size", "model.patch_size", "model.depth", "model.fp32_modulation",
     "data.res_fix",
+    # read by the reference, without effect here: every rank loads its own block of a sample directly (no scatter, so
+    # neither `wp_load` nor `gpu_datamovement` has anything to choose), attention is always the flash kernel, blocks are
+    # always pre-norm, the clipping norm is the 2-norm, optimizer hyper-parameters always come from the configuration
+    "data.wp_load", "model.gpu_datamovement", "model.attn_fn", "model.norm", "model.grad_clip_norm_type",
+    "model.refresh_decay",
 }
 
 
