@@ -237,6 +237,13 @@ def optim_config(cfg: Config):
     from ..engine.optim import OptimConfig
     t, o, m = cfg.trainer, cfg.optimizer, cfg.model
     policy = "custom_decay5" if m.get("custom_decay5") else ("custom_decay" if m.get("custom_decay") else "all")
+    target = str(o.get("_target_", "torch.optim.AdamW"))
+    if target.rsplit(".", 1)[-1] not in ("AdamW", "Adam"):
+        raise ValueError(f"optimizer._target_ = {target}: the fused update implements Adam / AdamW")
+    if target.endswith(".Adam") and float(o.weight_decay) != 0.0:
+        # torch.optim.Adam adds weight_decay * w to the gradient (L2); the fused kernels decay the weights directly
+        warnings.warn("optimizer._target_ is torch.optim.Adam with a non-zero weight_decay: the decoupled (AdamW) "
+                      "form of the decay is applied")
     return OptimConfig(
         lr=o.lr, betas=tuple(o.betas), eps=o.eps, weight_decay=o.weight_decay, decay_policy=policy,
         grad_clip=bool(m.get("grad_clip", False)), grad_clip_max_norm=float(m.get("grad_clip_max_norm", 1.0)),
