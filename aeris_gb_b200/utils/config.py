@@ -136,9 +136,16 @@ def compose(config_name: str = "train", overrides: list[str] | None = None, conf
         path = root / group / f"{option}.yaml"
         text = path.read_text()
         body = yaml.safe_load(text) or {}
-        body.pop("defaults", None)
+        nested = body.pop("defaults", None) or []
         m = re.match(r"\s*#\s*@package\s+(\S+)", text)
         package = m.group(1) if m else group
+        # a group file may list siblings of its own group that it builds on (`defaults: [defaults]` in
+        # configs/data/era5-aurora.yaml): they are merged first, into the same package
+        for sib in nested:
+            if isinstance(sib, str) and sib != "_self_" and (root / group / f"{sib}.yaml").exists():
+                sib_body = _load_yaml(root / group / f"{sib}.yaml")
+                sib_body.pop("defaults", None)
+                _merge(cfg if package == "_global_" else cfg.setdefault(package, {}), sib_body)
         if package == "_global_":
             _merge(cfg, body)
         else:
