@@ -98,14 +98,34 @@ def _merge(dst: dict, src: dict) -> dict:
 
 def _load_yaml(path: Path) -> dict:
     with open(path) as f:
-        return yaml.safe_load(f) or {}
+        return _fix_floats(yaml.safe_load(f) or {})
+
+
+_SCI = re.compile(r"^[+-]?\d+(\.\d*)?[eE][+-]?\d+$")
+
+
+def _fix_floats(node):
+    """YAML 1.1 reads ``1e-08`` (no dot in the mantissa, as the reference's optimizer files write it) as a string."""
+    if isinstance(node, dict):
+        return {k: _fix_floats(v) for k, v in node.items()}
+    if isinstance(node, list):
+        return [_fix_floats(v) for v in node]
+    if isinstance(node, str) and _SCI.match(node):
+        return float(node)
+    return node
 
 
 def _parse_value(s: str):
     try:
-        return yaml.safe_load(s)
+        v = yaml.safe_load(s)
     except yaml.YAMLError:
         return s
+    if isinstance(v, str):          # YAML 1.1 reads `1e-3` (no dot) as a string; overrides mean the number
+        try:
+            return float(v)
+        except ValueError:
+            pass
+    return v
 
 
 def compose(config_name: str = "train", overrides: list[str] | None = None, config_root: Path | None = None) -> Config:
@@ -135,7 +155,7 @@ def compose(config_name: str = "train", overrides: list[str] | None = None, conf
         option = group_sel.get(group, option)
         path = root / group / f"{option}.yaml"
         text = path.read_text()
-        body = yaml.safe_load(text) or {}
+        body = _fix_floats(yaml.safe_load(text) or {})
         nested = body.pop("defaults", None) or []
         m = re.match(r"\s*#\s*@package\s+(\S+)", text)
         package = m.group(1) if m else group
