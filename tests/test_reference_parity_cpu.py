@@ -180,3 +180,24 @@ def test_reference_inference_arm_evaluates_the_same_network(one_rank_group):
         y = ours(x, s)[0]
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     assert (y - y_ref).norm() <= tol * y_ref.norm(), ((y - y_ref).norm() / y_ref.norm(), dtype)
+
+
+@pytest.mark.parametrize("img,batch,layers,c,dim,mlp,ws", [
+    ((720, 1440), 1, 40, 144, 1536, 4096, (30, 30)),
+    ((720, 1440), 20, 24, 144, 1536, 6144, (60, 60)),
+    ((32, 64), 3, 4, 10, 32, 48, (8, 8)),
+])
+def test_flop_model_and_embeddings_equal_the_references(img, batch, layers, c, dim, mlp, ws):
+    """The analytic FLOP count behind every TFLOP/s figure, the sinusoidal noise-level embedding and the additive
+    position encoding, against the reference's own functions."""
+    from aeris_gb_b200.models import oracle as O
+    SW, _ = HN._ref_modules()
+    ours = O.get_swin_flop_count(img, batch, layers, c, dim, mlp, (1, 1), ws)
+    theirs = SW.get_swin_flop_count(list(img), batch, layers, c, dim, mlp, [1, 1], list(ws))
+    assert ours == pytest.approx(theirs, rel=1e-12)
+    t = torch.tensor([0.05, 0.7, 1.5])
+    assert torch.allclose(O.timestep_embedding(t, dim, 10_000.0), SW.timestep_embedding(t, dim, 10_000), atol=1e-6)
+    if img[0] <= 64:
+        pe_ref = SW.PositionalEncoding2D(c)(torch.zeros(1, c, img[0], img[1]))[0]            # [C, H, W]
+        pe = O.positional_encoding_2d(c, img[0], img[1])
+        assert torch.allclose(pe.reshape(img[0], img[1], c), pe_ref.permute(1, 2, 0), atol=1e-6)
