@@ -179,3 +179,37 @@ def test_flat_optimizer_clips_by_the_global_norm_and_survives_nans():
         p.main_grad.fill_(float("nan"))
     opt.step(batch_img=1, grad_scale=1.0, norm_sq=torch.tensor([1.0], dtype=torch.float64))
     assert all(torch.isfinite(p).all() for p in a.parameters())          # NaN gradients are zeroed, not applied
+
+
+# ------------------------------------------------------------------------------------------------------ rollout
+def test_autoregressive_rollout_standardises_the_condition_and_adds_the_unstandardised_residual():
+    """A stand-in network that knows the residual exactly: y* = 0.1 * (standardised state) + (forcing channel). The
+    forecaster must feed it the standardised state and forcing, integrate to y*, and advance the physical state by
+    ``y* * t_std + t_mean`` (pp_generate.py:325-333), step after step."""
+    from aeris_gb_b200.diffusion.rollout import Forecaster, SamplerConfig
+    C, sd = 3, 1.0
+    stats = {"x_mean": torch.tensor([1.0, -2.0, 0.5]), "x_std": torch.tensor([2.0, 0.5, 1.5]),
+             "t_mean": torch.tensor([0.1, 0.0, -0.2]), "t_std": torch.tensor([0.3, 0.2, 0.1])}
+    seen = []
+
+    def denoise(model_in, t):
+        x_t, cond_state, forcing = model_in[..., :C] * sd, model_in[..., C:2 * C], model_in[..., 2 * C:]
+        seen.append((cond_state.clone(), forcing.clone()))
+        y_star = 0.1 * cond_state + forcing
+        tt = t.view(-1, 1, 1)
+        return (torch.cos(tt) * x_t - y_star) / (torch.sin(tt) * sd)
+    fc = Forecaster(denoise, stats, SamplerConfig(n_steps=16, sigma_min=0.02, sigma_max=80.0, sigma_data=sd), C)
+    assert fc.model_evals_per_forecast_step() == 31
+    g = torch.Generator().manual_seed(0)
+    state = torch.randn(2, 4, C, generator=g) * 3.0
+    forc = [torch.randn(2, 4, 1, generator=g).expand(2, 4, C).contiguous() for _ in range(2)]
+    steps = []
+    final = fc.rollout(state, lambda k: forc[k], 2, generator=g, on_step=lambda k, s: steps.append((k, s.clone())))
+    expect = state
+    for k in range(2):
+        cond = (expect - stats["x_mean"]) / stats["x_std"]
+        expect = expect + (0.1 * cond + forc[k]) * stats["t_std"] + stats["t_mean"]
+        assert torch.allclose(steps[k][1], expect, atol=5e-3), k
+    assert [k for k, _ in steps] == [0, 1] and torch.equal(final, steps[-1][1])
+    assert torch.allclose(seen[0][0], (state - stats["x_mean"]) / stats["x_std"], atol=1e-6)
+    assert torch.equal(seen[0][1], forc[0])
