@@ -57,6 +57,8 @@ def parse(argv=None):
     ap.add_argument("--end-sample", type=int, default=-1, help="last initial condition (-1: as many as fit)")
     ap.add_argument("--extra-name", default="", help="text in front of the checkpoint file names, e.g. it_5000_")
     ap.add_argument("--extra-outname", default="", help="text appended to the name of the rollout files")
+    ap.add_argument("--local-eval", action="store_true",
+                    help="print the running first-channel (2 m temperature) scores after every rollout step")
     ap.add_argument("--clamp-sst", action="store_true",
                     help="accepted: land points of the sea-surface temperature are always filled before standardising")
     ap.add_argument("--euler", action="store_true")
@@ -194,6 +196,8 @@ def main(argv=None):
                 members = [m + (y * stats["t_std"] + stats["t_mean"]) for m, y in zip(members, x)]
                 mem = torch.stack(members).permute(0, 2, 1).unsqueeze(-1)      # [M, C, rows, 1] "image" of token rows
                 metrics.update(k, mem, truth[k].t().unsqueeze(-1), w_tok)
+                if a.local_eval:
+                    print0(metrics.running_line(k, 0, int(cfg.model.get("interval", 6))))
                 if writer is not None:
                     writer.put(n, k + 1, to_block(torch.stack(members)))
         metrics.end_initial_condition()

@@ -68,6 +68,8 @@ def parse(argv=None):
     ap.add_argument("--euler", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--debug", action="store_true")
+    ap.add_argument("--local-eval", action="store_true",
+                    help="print the running first-channel (2 m temperature) scores after every rollout step")
     ap.add_argument("overrides", nargs="*")
     return ap.parse_args(argv)
 
@@ -177,6 +179,8 @@ def main(argv=None):
         else:
             mem = x.permute(0, 3, 1, 2)
         metrics.update(k, mem, cur["truth"](k), w_lat_blk)
+        if a.local_eval:
+            print0(metrics.running_line(k, 0, int(cfg.model.get("interval", 6))))
 
     t_start = time.perf_counter()
     times.append(t_start)

@@ -54,6 +54,14 @@ class EnsembleMetrics:
     def end_initial_condition(self):
         self.count += 1
 
+    def running_line(self, step: int, channel: int, interval: int = 6) -> str:
+        """Scores of one channel at one lead time over the initial conditions seen so far, the current one included
+        (the reference prints this for 2 m temperature after every rollout step, pp_generate.py:461-468)."""
+        e = (self.err[step, :, channel] / (self.count + 1)).tolist()
+        rmse_mean = max(e[1], 0.0) ** 0.5
+        return (f"{interval * (step + 1)}h scores at ic {self.count + 1}: {max(e[0], 0.0) ** 0.5:.4f}, {rmse_mean:.4f}, "
+                f"{e[2] - e[3]:.4f}, {e[4] / max(rmse_mean, 1e-30):.4f}")
+
     def finalize(self) -> tuple[np.ndarray, np.ndarray]:
         """(aggregate [steps, 5, C] raw sums, scores [steps, 4, C] = RMSE first, RMSE mean, CRPS, spread/skill)."""
         n = max(self.count, 1)
