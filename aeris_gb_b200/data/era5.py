@@ -96,6 +96,16 @@ class ERA5NRMDataset(Dataset):
     n_channels = property(lambda self: self.channels)
     img_resolution = property(lambda self: (721, 1440))
 
+    def get_lat_lon(self) -> tuple[np.ndarray, np.ndarray]:
+        """``lat.npy`` / ``lon.npy`` of the statistics folder (src/aeris/data/era5.py:300-303)."""
+        return (np.load(os.path.join(self.root, "lat.npy")).astype(np.float32),
+                np.load(os.path.join(self.root, "lon.npy")).astype(np.float32))
+
+    def get_time(self, idx: int, start: str = "1979-01-01T00", step_hours: int = 6) -> np.datetime64:
+        """Valid time of sample ``idx``. The monolithic array carries no time stamps (the reference reads them from its
+        per-step files, :338-341), so the time follows from the index on the 6-hourly axis that starts at ``start``."""
+        return np.datetime64(start) + np.timedelta64(int(idx) * step_hours, "h")
+
     def __len__(self):
         if self._samples is not None:
             return self._samples
