@@ -7,6 +7,7 @@ the same rules run as interleaved atomic steps chosen by hypothesis, and the saf
 leaves barrier k before everybody entered it, data written before a barrier is seen after it, a slow rank several
 epochs behind never lets a fast rank through, and the comparison survives the 32-bit wrap of the epoch."""
 import numpy as np
+import pytest
 from hypothesis import given, settings, strategies as st
 
 MASK = 0xFFFFFFFF
@@ -107,3 +108,27 @@ def test_arrival_counter_consumer_never_reads_a_chunk_early(n_chunks, schedule, 
             if arrived[cc] - call >= 0:
                 assert copied[cc], "consumer passed the wait before the chunk was copied"
                 cc += 1
+
+
+@pytest.mark.parametrize("world,rows", [(2, 32400), (4, 16200), (8, 8100), (8, 1000)])
+def test_reduce_scatter_tile_rotation_spreads_the_owners(world, rows):
+    """The reduce-scatter GEMM of rank r starts at the 256-row tile that holds the first row of rank r + 1 and walks
+    the tiles cyclically (``GemmParams::tm_rot``). Restated here: every rank still visits every tile once, ends on its
+    own rows, and at any position of the walk the ranks push to (almost always) different owners, so no GPU's
+    ingress carries everybody's traffic at once, which the unrotated order did."""
+    M = world * rows
+    m_tiles = (M + 255) // 256
+    order = {}
+    for r in range(world):
+        rot = (((r + 1) % world) * rows) // 256
+        order[r] = [(tm + rot) % m_tiles for tm in range(m_tiles)]
+        assert sorted(order[r]) == list(range(m_tiles))
+        first_owner = min(order[r][0] * 256, M - 1) // rows
+        assert first_owner in ((r + 1) % world, r)                      # a tile that straddles the boundary may start in r
+        assert (order[r][-1] * 256) // rows in (r, (r + 1) % world, (r - 1) % world) or world == 2
+
+    def owner(tile):
+        return min(tile * 256 + 128, M - 1) // rows                    # owner of the tile's middle row
+    rotated = sum(len({owner(order[r][i]) for r in range(world)}) for i in range(m_tiles)) / m_tiles
+    plain = sum(len({owner(i) for _ in range(world)}) for i in range(m_tiles)) / m_tiles
+    assert plain == 1.0 and rotated > 0.9 * world
