@@ -132,3 +132,32 @@ def test_reduce_scatter_tile_rotation_spreads_the_owners(world, rows):
     rotated = sum(len({owner(order[r][i]) for r in range(world)}) for i in range(m_tiles)) / m_tiles
     plain = sum(len({owner(i) for _ in range(world)}) for i in range(m_tiles)) / m_tiles
     assert plain == 1.0 and rotated > 0.9 * world
+
+
+def test_folded_four_value_block_reduction_lane_algebra():
+    """``block_sum4_shfl`` (csrc/elementwise.cu) restated with arrays for lanes: lanes that differ in bit 4 split the four
+    values two and two, lanes that differ in bit 3 one and one, three more exchanges finish the warp sum; value k of
+    warp w lands in slot k * 8 + w and one more three-step fold per slot row gives every lane all four block totals."""
+    rng = np.random.default_rng(0)
+    n_warps = 6
+    s = rng.standard_normal((n_warps, 32, 4))                      # [warp, lane, value]
+    lanes = np.arange(32)
+    red = np.zeros(32)
+    for w in range(n_warps):
+        v = s[w]
+        b4, b3 = (lanes & 16) != 0, (lanes & 8) != 0
+        a0, a1 = np.where(b4, v[:, 2], v[:, 0]), np.where(b4, v[:, 3], v[:, 1])
+        g0, g1 = np.where(b4, v[:, 0], v[:, 2]), np.where(b4, v[:, 1], v[:, 3])
+        a0, a1 = a0 + g0[lanes ^ 16], a1 + g1[lanes ^ 16]
+        c, d = np.where(b3, a1, a0), np.where(b3, a0, a1)
+        c = c + d[lanes ^ 8]
+        for o in (4, 2, 1):
+            c = c + c[lanes ^ o]
+        for lane in (0, 8, 16, 24):
+            red[(lane >> 3) * 8 + w] = c[lane]
+    t = red.copy()
+    for o in (4, 2, 1):
+        t = t + t[lanes ^ o]
+    totals = np.array([t[j * 8] for j in range(4)])
+    assert np.allclose(totals, s.sum(axis=(0, 1)))
+    assert all(np.allclose(t[j * 8:(j + 1) * 8], totals[j]) for j in range(4))     # every lane of a group holds it
