@@ -161,3 +161,43 @@ def test_folded_four_value_block_reduction_lane_algebra():
     totals = np.array([t[j * 8] for j in range(4)])
     assert np.allclose(totals, s.sum(axis=(0, 1)))
     assert all(np.allclose(t[j * 8:(j + 1) * 8], totals[j]) for j in range(4))     # every lane of a group holds it
+
+
+@pytest.mark.parametrize("rows,K,grid", [(32400, 1536, 148), (8100, 1536, 148), (1000, 512, 148), (129, 8, 148),
+                                         (16200, 4096, 132)])
+def test_all_gather_copier_slices_cover_the_chunk_in_aligned_pieces(rows, K, grid):
+    """``ag_push_chunk`` (csrc/gemm_ag.cuh): every CTA moves one contiguous slice of this rank's chunk in pieces of at
+    most 16 KB; bulk copies need 16-byte aligned addresses and sizes. Restated: the slices are disjoint, cover the
+    chunk exactly, and every piece starts and ends on a 16-byte boundary."""
+    total = rows * K * 2
+    assert total % 16 == 0                                             # checked on the host before the launch
+    per = ((total // 16 + grid - 1) // grid) * 16
+    covered = 0
+    for b in range(grid):
+        b0, b1 = per * b, min(total, per * (b + 1))
+        if b0 >= b1:
+            continue
+        assert b0 == covered and b0 % 16 == 0
+        pos = b0
+        while pos < b1:
+            n = min(16384, b1 - pos)
+            assert n % 16 == 0 and pos % 16 == 0 and 0 < n <= 16384
+            pos += n
+        covered = b1
+    assert covered == total
+
+
+def test_reduce_scatter_stage_pitch_is_conflict_free_for_quarter_warps():
+    """Linear staging of the reduce-scatter epilogue: 32 rows of 256 bytes at a pitch of 272 bytes. A 16-byte access of
+    lane l to chunk c of its own row touches banks ((272 l + 16 c) / 4 + 0..3) mod 32; the eight lanes of a quarter
+    warp (one shared-memory wavefront for 128-bit accesses) must fall into disjoint banks, and every row must start
+    on a 16-byte boundary for the bulk copy."""
+    pitch = 272
+    assert pitch % 16 == 0
+    for c in range(16):
+        for q in range(4):
+            banks = set()
+            for lane in range(8 * q, 8 * q + 8):
+                first = ((pitch * lane + 16 * c) // 4) % 32
+                banks.update((first + k) % 32 for k in range(4))
+            assert len(banks) == 32
