@@ -39,7 +39,6 @@ def test_overrides_group_selection_and_nested_group_defaults():
                    "optimizer.lr=1e-3")
     assert cfg.model.dim == 64 and cfg.trainer.benchmark_steps == 3 and cfg.model.extra_key == [1, 2]
     assert cfg.optimizer.lr == pytest.approx(1e-3)
-    # data=era5-aurora builds on configs/data/defaults.yaml (its own `defaults: [defaults]`); the experiment wins after it
     cfg = _compose("data=era5-aurora")
     assert cfg.data.dataset.split == "train" and cfg.data.get("synthetic") is False
     cfg = _compose("optimizer=adam", "experiment=b200_wp_inference")
@@ -73,6 +72,16 @@ def test_run_config_round_trip(tmp_path):
     C.save_run_config(cfg, tmp_path)
     back = C.load_run_config(tmp_path)
     assert back.model.dim == 96 and back.to_dict() == cfg.to_dict()
+
+
+def test_a_group_file_may_build_on_a_sibling_of_its_group(tmp_path):
+    """``defaults: [base]`` inside ``data/site.yaml`` merges ``data/base.yaml`` first, into the same package."""
+    (tmp_path / "data").mkdir()
+    (tmp_path / "train.yaml").write_text("defaults:\n  - _self_\n  - data: site\nseed: 1\n")
+    (tmp_path / "data" / "base.yaml").write_text("workers: 8\ndataset:\n  root: null\n  split: train\n")
+    (tmp_path / "data" / "site.yaml").write_text("defaults:\n  - base\ndataset:\n  root: /somewhere\n")
+    cfg = C.compose("train", [], config_root=tmp_path)
+    assert cfg.data.workers == 8 and cfg.data.dataset.root == "/somewhere" and cfg.data.dataset.split == "train"
 
 
 def test_numbers_in_scientific_notation_without_a_dot_are_numbers(tmp_path):
