@@ -22,6 +22,15 @@ class InferenceEngine(ParallelEngine):
         ecfg.gas = members
         super().__init__(*a, **kw)
         self.members = members
+        # forward only: the fp32 masters, gradient accumulators, Adam moments and EMA that the training engine set up
+        # for the bf16 parameters (16 to 20 bytes per parameter) are released; the parameters keep viewing the flat
+        # bf16 buffer, the fp32 ends keep their (small) master buffer because they view it
+        for seg in getattr(self.opt, "segments", []):
+            if getattr(seg, "low_precision", False) and getattr(seg, "model_flat", None) is not None:
+                for prm in seg.params:
+                    if hasattr(prm, "main_grad"):
+                        del prm.main_grad
+                seg.master = seg.grad = seg.m = seg.v = seg.ema = None
         self.schedule = SCH.EnsembleInferenceSchedule(members, self.PP, self.c.pp)
         nb = self.schedule.num_pipe_buffers()
         self.buf = {k: [None] * nb for k in self.buf}

@@ -287,3 +287,24 @@ def test_checkpoint_with_the_references_optimizer_layout_loads(tmp_path):
     before = {k: v.clone() for k, v in model3.state_dict().items()}
     assert not load_stage_checkpoint(str(tmp_path), model3, FlatOptimizer(model3, OptimConfig()), "cpu")
     assert all(torch.equal(v, before[k]) for k, v in model3.state_dict().items())
+
+
+def test_inference_engine_releases_the_training_state_of_its_bf16_parameters():
+    """Forward-only engine: fp32 masters, gradient buffers, Adam moments and EMA of the bf16 blocks are freed after
+    construction, the parameters keep their values, and a network evaluation still runs."""
+    from aeris_gb_b200.engine.inference import InferenceEngine
+    cfg = _cfg()
+    cfg.model_dtype = torch.bfloat16
+    grid = ProcessGrid(1, PP=1)
+    torch.manual_seed(0)
+    eng = InferenceEngine(cfg, OptimConfig(use_ema=False), DiffusionConfig(cond_channels=CC),
+                          EngineConfig(gas=1, init_policy=dict(skip=True)), grid, 0, "cpu", members=2, groups={})
+    lp = [s for s in eng.opt.segments if s.low_precision]
+    assert lp and all(s.master is None and s.grad is None and s.m is None and s.v is None for s in lp)
+    blocks = [p for n, p in eng.module.named_parameters() if "to_qkv" in n]
+    assert blocks and all(p.dtype == torch.bfloat16 and not hasattr(p, "main_grad") and p.abs().sum() > 0 for p in blocks)
+    rows = eng.tokens
+    g = torch.Generator().manual_seed(1)
+    out = eng.exec_schedule([torch.randn(rows, CH + CC, generator=g) for _ in range(2)], torch.tensor([0.7]))
+    assert len(out) == 2 and out[0].shape == (rows, CH) and torch.isfinite(out[0]).all()
+    assert not torch.equal(out[0], out[1])
