@@ -201,3 +201,30 @@ def test_flop_model_and_embeddings_equal_the_references(img, batch, layers, c, d
         pe_ref = SW.PositionalEncoding2D(c)(torch.zeros(1, c, img[0], img[1]))[0]            # [C, H, W]
         pe = O.positional_encoding_2d(c, img[0], img[1])
         assert torch.allclose(pe.reshape(img[0], img[1], c), pe_ref.permute(1, 2, 0), atol=1e-6)
+
+
+def _dp_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dims = dict(img=(H, W), window=WS, dim=D, heads=2, head_dim=16, mlp_dim=48, n_layers=2, in_ch=C_IN, out_ch=C_OUT,
+                chunk_windows=3)
+    tr = HN.ReferenceTrainer(dims, "cpu", group=dist.group.WORLD, seed=3)
+    before = torch.cat([m.reshape(-1) for m in tr.master]).clone()
+    g = torch.Generator().manual_seed(10 + rank)                     # every rank its own sample
+    loss = tr.train_step(torch.randn(1, H, W, C_OUT, generator=g), torch.randn(1, H, W, C_IN - C_OUT, generator=g))
+    after = torch.cat([m.reshape(-1) for m in tr.master])
+    torch.save({"loss": loss, "after": after, "moved": float((after - before).abs().max()), "nimg": tr.cur_nimg},
+               os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_reference_arm_data_parallel_step_keeps_the_replicas_identical(tmp_path):
+    """The reference arm at N > 1: one full sample per rank, gradients averaged with one all-reduce of the flat
+    buffer (parallel_engine.py:709), every rank's one-rank sequence-parallel group for the stock all-to-all path."""
+    import torch.multiprocessing as mp
+    from conftest import free_port
+    mp.spawn(_dp_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    a, b = (torch.load(tmp_path / f"r{r}.pt") for r in range(2))
+    assert torch.equal(a["after"], b["after"]) and a["moved"] > 0 and a["nimg"] == 2
+    assert a["loss"] != b["loss"] and all(l == l for l in (a["loss"], b["loss"]))
